@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Decode benchmark: Llama-2-7B architecture, INT4 (group 128) weight-only linears, fp16 KV cache,
+batch 1, context 512 -> 512+K (prompt 512, K decode steps), tensor parallel over --gpus.
+
+    python bench.py --gpus 1 --steps 256 --warmup 8            # this implementation (needs a B200)
+    python bench.py --impl reference --steps 2 --warmup 1      # CPU restatement of the reference path
+
+Prints ONE JSON line.  A "step" is one decode step (one new token per sequence).  `value` is decode
+tokens/s with weights, KV cache and ids resident in HBM; `e2e` is the same through LlamaDecoder's
+host-facing call (pinned host ids in, ids out, copies inside the timed region).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA7B = dict(n_layer=32, d_model=4096, n_head=32, ffn=11008, vocab=32000)
+PROMPT, MAX_LEN, GROUP = 512, 768, 128
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------ CPU baseline
+def cpu_baseline(steps, warmup, sample_layers=2, ctx=PROMPT):
+    """Times oracle/c/decode_ref.c (OpenMP, all host threads) on a bounded sample of the same workload:
+    `sample_layers` of the 32 transformer blocks plus the final norm + LM head, decode steps at context `ctx`;
+    the per-token time is (block time / sample_layers) * 32 + head time."""
+    from oracle import c_ref, llama_np
+    c_ref.build()
+    cfg = llama_np.LlamaConfig(**LLAMA7B, max_len=MAX_LEN, group=GROUP)
+    r = np.random.default_rng(0)
+    d, f, v = cfg.d_model, cfg.ffn, cfg.vocab
+    sd = {"model.embed_tokens.weight": (r.standard_normal((1024, d), dtype=np.float32) * 0.02).astype(np.float16)}
+    for i in range(sample_layers):
+        p = f"model.layers.{i}."
+        for nm, (o, k) in {"self_attn.q_proj": (d, d), "self_attn.k_proj": (d, d), "self_attn.v_proj": (d, d), "self_attn.o_proj": (d, d),
+                           "mlp.gate_proj": (f, d), "mlp.up_proj": (f, d), "mlp.down_proj": (d, f)}.items():
+            sd[p + nm + ".weight"] = r.integers(-128, 128, size=(o, k // 2), dtype=np.int8)
+            sd[p + nm + ".weight_scale"] = (r.random((o, k // GROUP), dtype=np.float32) * 0.004 + 0.004).astype(np.float16)
+        sd[p + "input_layernorm.weight"] = np.ones(d, np.float16)
+        sd[p + "post_attention_layernorm.weight"] = np.ones(d, np.float16)
+    sd["model.norm.weight"] = np.ones(d, np.float16)
+    sd["lm_head.weight"] = (r.standard_normal((v, d), dtype=np.float32) * 0.02).astype(np.float16)
+    orc = c_ref.LlamaOracleC(cfg, sd, 1, n_layer=sample_layers)
+    for kc in orc.keep:                      # a cache that is already `ctx` tokens deep
+        if kc.ndim == 4:
+            kc[:, :, :ctx] = (r.standard_normal((1, cfg.n_head, ctx, cfg.head_dim), dtype=np.float32) * 0.5).astype(np.float16)
+    L = c_ref.lib()
+    import ctypes
+    x = np.ascontiguousarray(orc.emb[[1]])
+    t_layers, t_head = [], []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        for s in orc.layers:
+            L.oracle_llama_layer_step(ctypes.byref(s), ctx + it, c_ref._p(x), c_ref._p(orc.scratch))
+        t1 = time.perf_counter()
+        L.oracle_llama_head(c_ref._p(x), c_ref._p(orc.norm), c_ref._p(orc.head), 1, d, v, cfg.eps, c_ref._p(orc.h), c_ref._p(orc.lg),
+                            c_ref._p(orc.nxt))
+        t2 = time.perf_counter()
+        if it >= warmup:
+            t_layers.append(t1 - t0); t_head.append(t2 - t1)
+    per_token = np.mean(t_layers) / sample_layers * cfg.n_layer + np.mean(t_head)
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count()
+    return {"value": 1.0 / per_token, "unit": "tokens/s", "cores": int(os.environ.get("OMP_NUM_THREADS", cores)), "kind": "port",
+            "sample": f"{sample_layers} of 32 transformer blocks + final norm + LM head of the same shapes, {steps} decode steps at "
+                      f"context {ctx}, block time scaled x{cfg.n_layer // sample_layers}",
+            "ms_per_token": per_token * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
+    cb = cpu_baseline(steps, warmup)
+    line = {"impl": "reference", "metric": "decode tokens/s (Llama-2-7B INT4 g128, batch 1, ctx 512->768)", "value": cb["value"],
+            "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": cb["ms_per_token"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate",
+            "data": "synthetic", "config": {"workload": "llama2-7b-int4-g128 decode b1 prompt512", "parallelism": "host cores (OpenMP)"},
+            "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------ this implementation
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from poptransformer_b200 import llama, ops, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU baseline")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+
+    batch = args.batch
+    cfg = llama.LlamaConfig(**LLAMA7B, max_len=MAX_LEN, int4_group=GROUP)
+    sd = synth.llama_state_dict(**LLAMA7B, seed=0, device=dev, int4_group=GROUP)
+    dec = llama.LlamaDecoder(cfg, sd, batch, device=dev, tp_rank=rank, tp_size=world)
+    del sd
+    torch.cuda.empty_cache()
+
+    # state as it is after the 512-token prompt: ids hold the prompt, caches hold 512 tokens
+    ids_host = synth.prompt_ids(batch, PROMPT, MAX_LEN, cfg.vocab, dec.pad_id, seed=0).pin_memory()
+    gen = torch.Generator(device=dev).manual_seed(1)
+    for kc in dec.caches:
+        kc.pool.copy_((torch.randn(kc.pool.shape, generator=gen, device=dev) * 0.5).to(torch.float16))
+
+    def set_state():
+        dec.ids.copy_(ids_host, non_blocking=True)
+        dec.step_t.fill_(PROMPT)
+
+    n0 = ops.launch_count()
+    dec.capture()
+    launches_per_step = (ops.launch_count() - n0) // 2      # capture() enqueues the step twice (warm-up + capture)
+    K, W = args.steps, max(3, args.warmup)
+    K = min(K, MAX_LEN - PROMPT)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    set_state()
+    for _ in range(W):
+        dec.step()
+    set_state()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        dec.step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if int(dec.error_flag.item()) != 0:
+        raise SystemExit("device-side bounded wait gave up during the timed region")
+
+    # ---- end to end through the host-facing call: pinned ids in, K steps, ids + step out
+    out_host = torch.empty_like(ids_host).pin_memory()
+    step_host = torch.empty(1, dtype=torch.int32).pin_memory()
+    e2e_t = []
+    for rep in range(3):
+        barrier()
+        t0 = time.perf_counter()
+        dec.ids.copy_(ids_host, non_blocking=True)
+        dec.step_t.fill_(PROMPT)
+        for _ in range(K):
+            dec.step()
+        out_host.copy_(dec.ids, non_blocking=True)
+        step_host.copy_(dec.step_t, non_blocking=True)
+        torch.cuda.synchronize()
+        e2e_t.append(time.perf_counter() - t0)
+    e2e_s = min(e2e_t[1:])
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    # ---- dominant kernel (INT4 streaming linear): every INT4 linear launch of one step, back to back, CUDA events
+    lin_bytes = sum(L[k].nbytes for L in dec.layers for k in ("qkv", "o", "gu", "down"))
+    n_lin = 4 * cfg.n_layer
+    reps = 20
+    dec.enqueue_linears_only()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        dec.enqueue_linears_only()
+    e1.record()
+    torch.cuda.synchronize()
+    lin_ms = e0.elapsed_time(e1) / (reps * n_lin)
+    peak, peak_src = peaks()
+    achieved = (lin_bytes / n_lin) / (lin_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_step = ms / K
+    ctx_mean = PROMPT + (K - 1) / 2.0
+    step_bytes = dec.weight_bytes_total() + batch * dec.kv_bytes_per_token_total() * (ctx_mean + 1)
+    line = {
+        "metric": "decode tokens/s (Llama-2-7B INT4 g128, batch %d, ctx 512->%d)" % (batch, PROMPT + K),
+        "value": batch * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"llama2-7b-int4-g128 decode b{batch} prompt512", "parallelism": f"tp{world}",
+                   "l2": "inputs_larger_than_L2 (3.6 GB of weights streamed per step)", "cuda_graph": True},
+        "clocks": clocks,
+        "e2e": {"value": batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": ids_host.numel() * 4 / K,
+                "d2h_bytes_per_step": (ids_host.numel() * 4 + 4) / K},
+        "gpu_launches": int(launches_per_step * K),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "kernel": "linear_kernel<INT4>", "peak_source": peak_src, "launch_us": lin_ms * 1e3,
+                     "bytes_per_launch": lin_bytes / n_lin},
+        "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9 / world,
+                          "frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / world / peak,
+                          "frac_of_8tbs": step_bytes / (ms_step * 1e-3) / 1e9 / world / 8000.0},
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(steps=3, warmup=1)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,240 @@
+/*
+ * pt_b200.h — C-ABI of libpt_b200.so: sm_100a CUDA kernels for the PopTransformer
+ * per-token decode step.
+ *
+ * This is the boundary a PopTransformer maintainer binds in place of
+ * `ctypes.cdll.LoadLibrary('../../custom_ops.so')`
+ * (poptransformer/ops/customized.py:17-18): one plain C function per custom op /
+ * fused decode stage, keyed by the same op names and attribute meanings.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the parameter name ends in `_host`;
+ *   - `stream` is a cudaStream_t passed as void*; calls only enqueue work;
+ *   - fp16 tensors are IEEE binary16 (`uint16_t` storage), row-major, innermost
+ *     dimension last;
+ *   - every function returns 0 on success or a negative PT_ERR_* code and records a
+ *     message retrievable with pt_last_error() (thread-local);
+ *   - shape/dtype violations the reference reports at graph-build time
+ *     (popart::error in each Op::setup) are reported here before any launch;
+ *   - the library allocates no device memory: caches, workspaces and outputs belong to
+ *     the caller.  `step` arguments named `step_dev` are read ON THE DEVICE so that a
+ *     captured CUDA graph can be replayed for every token.
+ */
+#ifndef PT_B200_H
+#define PT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PT_OK 0
+#define PT_ERR_INVALID (-1)   /* bad shape / argument (reference: popart::error at setup) */
+#define PT_ERR_CUDA (-2)      /* a CUDA runtime call failed                               */
+#define PT_ERR_UNSUPPORTED (-3)
+
+/* ---- library ---------------------------------------------------------------------- */
+const char *pt_last_error(void);
+int pt_version(void);
+/* Number of kernel launches this library has enqueued from the calling process. */
+uint64_t pt_launch_count(void);
+
+/* Weight formats understood by the streaming skinny-matmul kernels. */
+#define PT_W_INT4 0 /* signed nibbles, 2 per byte, high nibble = even k, fp16 group scales */
+#define PT_W_FP16 1
+#define PT_W_FP8 2  /* OCP E4M3, per-tensor fp32 scale                                    */
+
+/* Prologues fused in front of a linear layer (applied to the activation rows). */
+#define PT_PRO_NONE 0
+#define PT_PRO_RMSNORM 1   /* poptransformer/layers/rms_layer_norm.py:26-36 */
+#define PT_PRO_CAST_FP8 2  /* activations quantised to E4M3 with `act_scale` first */
+#define PT_PRO_RMSNORM_CAST_FP8 3
+
+/* Epilogues fused behind a linear layer. */
+#define PT_EPI_STORE 0        /* y = fp16(acc)                                         */
+#define PT_EPI_RESIDUAL 1     /* y = fp16(res + fp16(acc))           (ops.add)        */
+#define PT_EPI_SWIGLU 2       /* y = fp16(fp16(up) * swish(fp16(gate))) llama2/mlp.py:20-28 */
+#define PT_EPI_BIAS 3         /* y = fp16(fp16(acc) + bias)          layers/linear.py:42-46 */
+#define PT_EPI_BIAS_GELU 4    /* y = gelu(fp16(fp16(acc) + bias))    layers/mlp.py:34-41   */
+#define PT_EPI_BIAS_RESIDUAL 5/* y = fp16(res + fp16(fp16(acc) + bias))                  */
+
+/* ---- Int4ToHalf -------------------------------------------------------------------
+ * Replaces the `Int4ToHalf` custom op (poptransformer/ops/customized.py:115-124;
+ * custom_ops/int4_to_half_custom_op.cpp:168-380; codelets int4_to_half_codelets.cpp:18-73).
+ * axis 1: w int8 [n, m], scale fp16 [n] (group == 0) or [n, 2m/group] -> out fp16 [2m, n].
+ * axis 0: w int8 [n, m], scale fp16 [m] -> out fp16 [2n, m].  Bit-exact. */
+int pt_int4_to_half(const void *w, const void *scale, int n, int m, int axis, int group,
+                    void *out, void *stream);
+
+/* ---- linear layers ----------------------------------------------------------------
+ * Replaces Linear.__call__ -> ParamHandler.matmul -> (Int4ToHalf|CastToUint8) + matmul
+ * (poptransformer/layers/linear.py:42-46, utils/param_handler/param_handler.py:57-83,
+ * utils/param_handler/precision_strategy.py:56-81) for decode-sized batches.
+ *
+ * pt_linear_repack: one-time re-layout of a weight matrix W[n_out, k_in] stored with
+ * k contiguous (INT4: the reference's int8 [n_out, k_in/2] + fp16 scales [n_out, k_in/group])
+ * into the tile order the streaming kernel reads with 128-bit loads.
+ * Sizes of the outputs: pt_linear_packed_bytes / pt_linear_packed_scale_bytes.
+ * `interleave_rows` = 1 builds the SwiGLU layout from a [2*f, k] matrix whose first f rows
+ * are gate rows and last f rows are up rows (8 gate rows then 8 up rows per 16-row tile). */
+size_t pt_linear_packed_bytes(int wfmt, int n_out, int k_in);
+size_t pt_linear_packed_scale_bytes(int wfmt, int n_out, int k_in, int group);
+int pt_linear_repack(int wfmt, const void *w, const void *scale, int n_out, int k_in, int group,
+                     int interleave_rows, void *packed_w, void *packed_scale, void *stream);
+
+typedef struct pt_linear_args {
+  int wfmt;              /* PT_W_*                                                  */
+  int batch;             /* rows of x, 1..32                                        */
+  int n_out, k_in;       /* logical weight shape (n_out counts gate+up rows for SWIGLU) */
+  int group;             /* INT4 scale group along k (k_in for one scale per row)    */
+  int prologue, epilogue;
+  int ksplit;            /* 0 = let the library choose; >1 needs workspace          */
+  const void *x;         /* fp16 [batch, k_in]                                      */
+  const void *packed_w;  /* from pt_linear_repack                                   */
+  const void *packed_scale;
+  const void *norm_gamma;/* fp16 [k_in]   (PT_PRO_RMSNORM*)                        */
+  float norm_eps;
+  float act_scale;       /* FP8: activation scale (x ~ act_scale * e4m3)            */
+  float w_scale;         /* FP8: weight per-tensor scale                            */
+  const void *bias;      /* fp16 [n_out]                                            */
+  const void *residual;  /* fp16 [batch, n_out]; may alias `out`                    */
+  void *out;             /* fp16 [batch, n_out] (SWIGLU: [batch, n_out/2])          */
+  int out_ld;            /* row stride of `out` in elements; 0 = dense              */
+  void *workspace;       /* split-k partials + counters, pt_linear_workspace_bytes  */
+  size_t workspace_bytes;
+} pt_linear_args;
+
+size_t pt_linear_workspace_bytes(int batch, int n_out, int max_ksplit);
+int pt_linear(const pt_linear_args *args, void *stream);
+
+/* ---- norms ------------------------------------------------------------------------
+ * pt_norm_ce replaces the `NormCE` custom op (customized.py:69-102; custom_ops/NormCE.cpp:534-610):
+ * fp16 rows, LayerNorm over `dim`; rows == 1 takes the GetInPlaceNorm arithmetic
+ * (NormCECodelets.cpp:65-112), rows >= 2 the normInfKernel arithmetic (NormCECodelets.cpp:181-211).
+ * Errors like the reference: dim % 4 != 0, dim >= 8192. */
+int pt_norm_ce(const void *x, const void *gamma, const void *beta, int rows, int dim, float eps,
+               void *out, void *stream);
+/* RMSLayerNorm (layers/rms_layer_norm.py:26-36) with an optional fused residual add in front:
+ * if residual != NULL: sum = fp16(x + residual) is written to sum_out and normalised. */
+int pt_rms_norm(const void *x, const void *residual, const void *gamma, int rows, int dim, float eps,
+                void *out, void *sum_out, void *stream);
+
+/* ---- SoftmaxV3 --------------------------------------------------------------------
+ * Replaces `SoftmaxV3` (customized.py:57-65; custom_ops/softmax.cpp:41-83). dtype: 0 = fp16, 1 = fp32. */
+int pt_softmax(const void *x, int rows, int dim, int stable_mode, int dtype, void *out, void *stream);
+
+/* ---- KVCache (reference layout) -----------------------------------------------------
+ * Replaces `KVCache` (customized.py:21-35; custom_ops/kv_cache.cpp:94-187): `cache` is the op's
+ * persistent state, viewed as [outer, max_len, inner] fp16 (sequence axis in the middle);
+ * kv_new is [outer, step_len, inner].  cache <- concat(kv_new, (step==0 ? 0 : cache)[:max_len-step_len]).
+ * `scratch` must hold outer*max_len*inner fp16 (the reference's clone). Bit-exact. */
+int pt_kv_cache(const int32_t *step_dev, const void *kv_new, void *cache, void *scratch,
+                int64_t outer, int max_len, int step_len, int64_t inner, void *stream);
+/* `KVCachePipeline` (custom_ops/kv_cache_pipeline.cpp:374-451, kv_cache_codelet.cpp:18-212):
+ * `caches` is [max_bps, outer, max_len, inner]; all caches are zeroed when step == 0; cache
+ * step % max_bps receives the shifted insert and is copied to `out` [outer, max_len, inner]. */
+int pt_kv_cache_pipeline(const int32_t *step_dev, const void *kv_new, void *caches, void *out,
+                         int max_bps, int64_t outer, int max_len, int step_len, int64_t inner,
+                         void *stream);
+
+/* ---- paged KV cache + fused decode attention ---------------------------------------------
+ * Replaces, for one new token per sequence, the chain RoPE -> ops.kv_cache -> matmul(q,K^T) ->
+ * scale/mask -> softmax_ce -> matmul(P,V) -> transpose/reshape
+ * (llama2/attention.py:64-114; gpt2/attention.py:37-85; chatglm2/attention.py:166-312).
+ * The cache is paged: pool[page][2][n_kv][page_size][head_dim] fp16, page_table[batch][max_pages].
+ * Token t of sequence b lives in page page_table[b][t / page_size], slot t % page_size. */
+#define PT_ROPE_NONE 0
+#define PT_ROPE_LLAMA 1    /* rotate_half, table [max_len, head_dim/2]  (llama2/attention.py:28-56) */
+#define PT_ROPE_CHATGLM2 2 /* interleaved pairs on the first half of each head (chatglm2/attention.py:110-164) */
+#define PT_SOFTMAX_F32 0   /* scores cast to fp32, exp in fp32 (llama2/attention.py:103-107) */
+#define PT_SOFTMAX_F16 1   /* exp in fp16 (gpt2/attention.py:69, chatglm2/attention.py:289-291) */
+
+typedef struct pt_attn_args {
+  int batch, n_head, n_kv, head_dim; /* n_head % n_kv == 0                                   */
+  int page_size, max_pages;          /* max_pages = pages per sequence in page_table          */
+  int rope_mode, softmax_mode;
+  float score_scale;                 /* multiplied onto fp16(q.k) in fp16; 1.0 = pre-folded    */
+  const int32_t *step_dev;           /* position of the new token                             */
+  const void *qkv;                   /* fp16 [batch, (n_head + 2*n_kv) * head_dim]: q | k | v  */
+  const void *rope_sin, *rope_cos;   /* fp16 [max_len, rot_dim/2]                              */
+  void *pool;                        /* this layer's page pool                                */
+  const int32_t *page_table;         /* [batch, max_pages]                                    */
+  void *out;                         /* fp16 [batch, n_head*head_dim]                          */
+  int out_ld;                        /* row stride of `out` in elements; 0 = dense             */
+  void *workspace;                   /* pt_attn_workspace_bytes                               */
+  size_t workspace_bytes;
+  int32_t *error_flag;               /* device int, set non-zero if a bounded wait gave up     */
+} pt_attn_args;
+
+size_t pt_attn_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);
+int pt_kv_append_attn(const pt_attn_args *args, void *stream);
+/* Logical view of a paged cache in the reference op's layout [2, batch, n_kv, max_len, head_dim],
+ * newest token at index 0, zeros beyond `step` (custom_ops/kv_cache.cpp:118-132). */
+int pt_kv_export(const void *pool, const int32_t *page_table, const int32_t *step_dev, int batch,
+                 int n_kv, int head_dim, int page_size, int max_pages, int max_len, void *dense_out,
+                 void *stream);
+/* Beam reorder of a paged cache (no reference counterpart: the reference's BeamSearch op has no KV
+ * reorder).  Row r continues from row parent[r].  Full pages are immutable and are shared by
+ * permuting page-table rows; only the page that is still being filled (the one holding position
+ * *step_dev) is copied, into the row's spare page, which then swaps roles with the row's old page.
+ *   pt_kv_reorder_pages : per layer pool; copies the current page of row parent[r] into spare_pages[r].
+ *   pt_kv_reorder_table : once per step, after every layer's copy; rewrites page_table and spare_pages.
+ * `table_tmp` holds rows*max_pages int32. */
+int pt_kv_reorder_pages(void *pool, const int32_t *page_table, const int32_t *spare_pages,
+                        const int32_t *parent, const int32_t *step_dev, int rows, int n_kv, int head_dim,
+                        int page_size, int max_pages, void *stream);
+int pt_kv_reorder_table(int32_t *page_table, int32_t *table_tmp, int32_t *spare_pages, const int32_t *parent,
+                        const int32_t *step_dev, int rows, int page_size, int max_pages, void *stream);
+
+/* ---- top-k / LM-head ids / beam search --------------------------------------------------
+ * pt_topk replaces ops.topk (popart.py:135-137) on [rows, dim] fp16 or fp32 (dtype 0/1): values
+ * sorted descending, lowest index wins ties.  k <= 32. */
+int pt_topk(const void *x, int rows, int dim, int k, int dtype, void *vals, int32_t *ids, void *stream);
+/* Tensor-parallel LM head (layers/lm_head.py:75-116), k = 1.  pt_lm_head_local_topk: per-rank top-1 over the
+ * rank's vocabulary slice with exact-zero logits read as -10000 (:86-88) and ids offset by
+ * rank * ceil(V / tp) (:78-80, :90).  pt_lm_head_tp_pick: after the all-gather of (value, id) pairs laid out
+ * [tp, rows], takes the first maximum over ranks (:110-115). */
+int pt_lm_head_local_topk(const void *logits, int rows, int dim, int id_offset, void *vals, int32_t *ids, void *stream);
+int pt_lm_head_tp_pick(const void *vals, const int32_t *ids, int tp, int rows, int32_t *next_ids, void *stream);
+
+/* `BeamSearch` custom op (custom_ops/beam_search_custom_op.cpp:333-478): logits [b, beam, vocab]
+ * (dtype 0 fp16 / 1 fp32), hyp int32 [b, max_len, beam] (in/out), prob [b, beam] (in/out, dtype of
+ * logits), outputs next_id, global_best_id int32 [b, beam]; parent[b*beam] (optional) = flat cache
+ * row each output slot continues from, for pt_kv_reorder.  Ties resolve to the lowest index. */
+size_t pt_beam_search_workspace_bytes(int b, int beam, int max_len);
+int pt_beam_search(const void *logits, int32_t *hyp, void *prob, const int32_t *step_dev, int b, int beam,
+                   int vocab, int max_len, int dtype, int32_t *next_id, int32_t *global_best_id,
+                   int32_t *parent, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- FP8 -----------------------------------------------------------------------------
+ * `CastToUint8WithoutShapeInfer` (customized.py:127-135; custom_ops/cast_to_uint8.cpp:107-127) in the
+ * OCP E4M3 + per-tensor fp32 scale form: out[i] = e4m3_rne_sat(x[i] / scale). */
+int pt_cast_fp8(const void *x, float scale, int64_t n, void *out, void *stream);
+/* `FP8MatMulWithoutShapeInfer` (customized.py:137-148; custom_ops/matmul_fp8.cpp:885-1091):
+ * a e4m3 [m, k] (row-major), b e4m3 [n, k] (k contiguous), out fp16 [m, n] = (a.b^T) * sa * sb. */
+int pt_fp8_matmul(const void *a, const void *b, float scale_a, float scale_b, int m, int n, int k,
+                  void *out, void *stream);
+
+/* ---- RWKV WKV ------------------------------------------------------------------------
+ * poptransformer/models/rwkv/attention.py:66-105: k, v fp16 [b, c]; time_first/time_decay fp32 [c];
+ * num/den/max fp32 [b, c] updated in place; out fp16 [b, c] = fp16(wkv). */
+int pt_wkv(const void *k, const void *v, const float *time_first, const float *time_decay, float *num,
+           float *den, float *max_state, int b, int c, void *out, void *stream);
+
+/* ---- loop-carry and small ops ----------------------------------------------------------
+ * Embedding gather (layers/embedding.py:34-36): out[b] = table[ids[b*ids_stride + *step_dev]]. */
+int pt_embedding(const void *table, const int32_t *ids, int ids_stride, const int32_t *step_dev,
+                 int batch, int dim, int vocab, void *out, void *stream);
+/* step_containers + step_loop_cond (models/base_model.py:313-355): step' = step+1; slot
+ * ids[b, step'] takes next_ids[b] where it holds pad_id; stop_mask[b] |= (id == eos_id). */
+int pt_step_containers(int32_t *ids, int batch, int max_len, int32_t *step_dev, const int32_t *next_ids,
+                       int pad_id, int eos_id, int32_t *stop_mask, void *stream);
+/* Elementwise fp16: out = fp16(a + b) (ops.add). */
+int pt_add_f16(const void *a, const void *b, int64_t n, void *out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PT_B200_H */

@@ -1,0 +1,24 @@
+// Library-level entry points: error string, version, launch counter.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace pt {
+static thread_local char g_err[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+int set_error(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+}  // namespace pt
+
+extern "C" const char *pt_last_error(void) { return pt::g_err; }
+extern "C" int pt_version(void) { return 100; }
+extern "C" uint64_t pt_launch_count(void) { return pt::g_launches.load(std::memory_order_relaxed); }

@@ -1,0 +1,310 @@
+"""Llama-2 per-token decode on the B200 kernels.
+
+Host-side mirror of the reference's LLAMA2DecModel loop body
+(poptransformer/models/llama2/model.py:162-197, llama2/attention.py:64-122, llama2/mlp.py:20-28,
+layers/lm_head.py:47-116, models/base_model.py:313-355): one `step()` is one iteration of the
+reference's on-device Loop, i.e. one token per sequence (prompt tokens are consumed one per step, like
+the reference).  The step is five kernels per layer,
+
+    [RMSNorm ->] fused QKV linear -> RoPE + KV append + attention -> o_proj (+ residual)
+    [RMSNorm ->] gate|up linear with SwiGLU epilogue -> down_proj (+ residual)
+
+captured once in a CUDA graph and replayed per token; `step`, the id container and all activations
+live on the device, so nothing crosses the host boundary between tokens.
+
+Tensor parallelism follows the reference's TP layers (llama2/attention.py:125-144, llama2/mlp.py:31-48,
+utils/param_handler/tensor_parallel_strategy.py:21-109): q/k/v/gate/up are column-parallel ('start':
+output features split, so heads and FFN channels are split), o/down are row-parallel ('end': input
+features split) followed by an all-reduce, the LM head is vocabulary-parallel with a top-1 merge.
+One process per GPU; rank r keeps slice r.
+"""
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import ops
+
+
+class LlamaConfig:
+    def __init__(self, n_layer, d_model, n_head, ffn, vocab, eps=1e-5, max_len=128, int4_group=0):
+        self.n_layer, self.d_model, self.n_head, self.ffn = n_layer, d_model, n_head, ffn
+        self.vocab, self.eps, self.max_len, self.int4_group = vocab, eps, max_len, int4_group
+        self.head_dim = d_model // n_head
+
+
+def rope_tables(max_len, head_dim, device):
+    """sin/cos tables with the reference's fp16 recipe (llama2/attention.py:28-38): inv_freq rounded to
+    fp16, angle = fp16(fp16(step) * inv_freq), sin/cos of the fp16 angle rounded to fp16."""
+    inv_freq = np.array([1.0 / (10000 ** (i / head_dim)) for i in range(0, head_dim, 2)]).astype(np.float16)
+    steps = np.arange(max_len, dtype=np.int32).astype(np.float16)
+    ang = (steps.astype(np.float32)[:, None] * inv_freq.astype(np.float32)[None, :]).astype(np.float16)
+    sin = np.sin(ang.astype(np.float32)).astype(np.float16)
+    cos = np.cos(ang.astype(np.float32)).astype(np.float16)
+    return torch.from_numpy(sin).to(device), torch.from_numpy(cos).to(device)
+
+
+def _rows(t, r, n):
+    """'start' strategy: split the output features (rows of the [out, in] matrix)."""
+    per = t.shape[0] // n
+    if per * n != t.shape[0]:
+        raise ops.PtError(f"out_features={t.shape[0]} not divisible by tp={n}")
+    return t[r * per:(r + 1) * per]
+
+
+class _KSlice:
+    """'end' strategy: split the input features.  For INT4 group scales the rank's k-range [k0, k1) is widened
+    to group boundaries [a0, a1); weights outside [k0, k1) are zero nibbles, and the producer of the activation
+    writes at column offset k0 - a0 of a zero-initialised buffer of width a1 - a0."""
+
+    def __init__(self, k_total, r, n, align):
+        per = k_total // n
+        if per * n != k_total:
+            raise ops.PtError(f"in_features={k_total} not divisible by tp={n}")
+        self.k0, self.k1 = r * per, (r + 1) * per
+        self.a0 = (self.k0 // align) * align
+        self.a1 = -(-self.k1 // align) * align
+        self.offset, self.width = self.k0 - self.a0, self.a1 - self.a0
+
+
+class LlamaDecoder:
+    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, fuse_norm=None, pad_id=None, eos_id=-1,
+                 tp_rank=0, tp_size=1, group=None):
+        self.cfg, self.batch, self.device = cfg, batch, device
+        self.tp, self.rank, self.group = tp_size, tp_rank, group
+        c = cfg
+        if c.n_head % tp_size:
+            raise ops.PtError(f"n_head={c.n_head} not divisible by tp={tp_size} (llama2/attention.py:130)")
+        self.pad_id = c.vocab - 1 if pad_id is None else pad_id
+        self.eos_id = eos_id
+        self.fuse_norm = (batch <= 8) if fuse_norm is None else fuse_norm
+        dev = device
+        tp, r = tp_size, tp_rank
+        d, f = c.d_model, c.ffn
+        self.d_loc, self.f_loc, self.h_loc = d // tp, f // tp, c.n_head // tp
+
+        def t(key):
+            return state_dict[key].to(dev)
+
+        def col_parallel(keys, interleave=False):
+            ws = [_rows(t(k), r, tp) for k in keys]
+            if ws[0].dtype == torch.int8:
+                sc = [_rows(t(k + "_scale").reshape(t(k).shape[0], -1), r, tp) for k in keys]
+                grp = (ws[0].shape[1] * 2) // sc[0].shape[1]
+                return ops.PackedLinear(ops.W_INT4, torch.cat(ws, 0), torch.cat(sc, 0), group=grp, interleave_gate_up=interleave)
+            return ops.PackedLinear(ops.W_FP16, torch.cat(ws, 0).to(torch.float16), interleave_gate_up=interleave)
+
+        def row_parallel(key, k_total):
+            w = t(key)
+            if w.dtype == torch.int8:
+                sc = t(key + "_scale").reshape(w.shape[0], -1)
+                grp = k_total // sc.shape[1]
+                ks = _KSlice(k_total, r, tp, max(grp, 128) if grp < k_total else 128)
+                if grp == k_total:                      # one scale per output row: any 128-aligned window works
+                    loc_s, grp_loc = sc, ks.width
+                else:
+                    loc_s, grp_loc = sc[:, ks.a0 // grp: ks.a1 // grp], grp
+                loc = w[:, ks.a0 // 2: ks.a1 // 2].clone()
+                loc[:, : ks.offset // 2] = 0            # nibble pairs outside the rank's range contribute exactly 0
+                loc[:, (ks.k1 - ks.a0) // 2:] = 0
+                return ops.PackedLinear(ops.W_INT4, loc.contiguous(), loc_s.contiguous(), group=grp_loc), ks
+            ks = _KSlice(k_total, r, tp, 32)
+            loc = torch.zeros((w.shape[0], ks.width), dtype=torch.float16, device=dev)
+            loc[:, ks.offset: ks.offset + (ks.k1 - ks.k0)] = w[:, ks.k0: ks.k1]
+            return ops.PackedLinear(ops.W_FP16, loc), ks
+
+        self.emb = t("model.embed_tokens.weight").to(torch.float16).contiguous()   # replicated: one row is read per token
+        self.layers = []
+        for i in range(c.n_layer):
+            p = f"model.layers.{i}."
+            o, o_ks = row_parallel(p + "self_attn.o_proj.weight", d)
+            down, down_ks = row_parallel(p + "mlp.down_proj.weight", f)
+            self.layers.append({
+                "ln1": t(p + "input_layernorm.weight").contiguous(),
+                "ln2": t(p + "post_attention_layernorm.weight").contiguous(),
+                "qkv": col_parallel([p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"]),
+                "o": o, "gu": col_parallel([p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], interleave=True), "down": down,
+            })
+        self.o_ks, self.down_ks = o_ks, down_ks
+        self.norm = t("model.norm.weight").contiguous()
+        self.vocab_loc = math.ceil(c.vocab / tp)
+        head = t("lm_head.weight").to(torch.float16)
+        if tp > 1:
+            pad = self.vocab_loc * tp - c.vocab
+            if pad:
+                head = torch.cat([head, torch.zeros((pad, d), dtype=torch.float16, device=dev)], 0)   # shard() zero-pads
+            head = head[r * self.vocab_loc:(r + 1) * self.vocab_loc]
+        self.head = ops.PackedLinear(ops.W_FP16, head.contiguous())
+        self.sin, self.cos = rope_tables(c.max_len, c.head_dim, dev)
+        self.score_scale = float(np.float16(1 / math.sqrt(c.head_dim)))
+
+        B = batch
+        f16 = dict(dtype=torch.float16, device=dev)
+        self.ids = torch.full((B, c.max_len), self.pad_id, dtype=torch.int32, device=dev)
+        self.step_t = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.stop_mask = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.x = torch.empty((B, d), **f16)
+        self.h = torch.empty((B, d), **f16)
+        self.part = torch.empty((B, d), **f16)                       # row-parallel partial sums (tp > 1)
+        self.qkv = torch.empty((B, 3 * self.d_loc), **f16)
+        self.attn = torch.zeros((B, self.o_ks.width), **f16)         # zero pads outside the rank's k-range stay zero
+        self.act = torch.zeros((B, self.down_ks.width), **f16)
+        self.logits = torch.empty((B, self.vocab_loc if tp > 1 else c.vocab), **f16)
+        self.next_val = torch.empty((B, 1), **f16)
+        self.next_ids = torch.empty((B, 1), dtype=torch.int32, device=dev)
+        if tp > 1:
+            self.gather_val = torch.empty((tp, B), **f16)
+            self.gather_ids = torch.empty((tp, B), dtype=torch.int32, device=dev)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        page_table = None
+        self.caches = []
+        for _ in range(c.n_layer):
+            kc = ops.PagedKVCache(B, self.h_loc, c.head_dim, c.max_len, page_size, dev, page_table)
+            page_table = kc.page_table
+            self.caches.append(kc)
+        self.attn_ws = ops.attn_workspace(B, self.h_loc, c.head_dim, self.caches[0].max_pages, dev)
+        self.lin_ws = ops.linear_workspace(B, max(3 * self.d_loc, 2 * self.f_loc, d, self.logits.shape[1]), 16, dev)
+        self.graph = None
+        torch.cuda.synchronize()
+
+    # ---- accounting -------------------------------------------------------------------------
+    def weight_bytes(self):
+        """Algorithmic weight bytes this rank streams per step (every linear once, norm weights)."""
+        n = sum(L[k].nbytes for L in self.layers for k in ("qkv", "o", "gu", "down")) + self.head.nbytes
+        return n + (2 * self.cfg.n_layer + 1) * self.cfg.d_model * 2
+
+    def weight_bytes_total(self):
+        """The same for the whole model (all ranks), counted from the logical shapes."""
+        c = self.cfg
+        lin = c.n_layer * (4 * c.d_model * c.d_model + 3 * c.d_model * c.ffn)
+        g = self.layers[0]["qkv"].group
+        per_w = (0.5 + 2.0 / g) if self.layers[0]["qkv"].wfmt == ops.W_INT4 else 2.0
+        return int(lin * per_w + c.vocab * c.d_model * 2 + (2 * c.n_layer + 1) * c.d_model * 2)
+
+    def kv_bytes_per_token_total(self):
+        """KV bytes per cached token per sequence over all layers and heads (read once per step)."""
+        c = self.cfg
+        return 2 * c.n_layer * c.n_head * c.head_dim * 2
+
+    # ---- one loop iteration -------------------------------------------------------------------
+    def _all_reduce(self, tns):
+        if self.tp > 1:
+            torch.distributed.all_reduce(tns, group=self.group)
+
+    def _norm_linear(self, x, gamma, pl, out, epilogue=ops.EPI_STORE, out_ld=0):
+        if self.fuse_norm:
+            ops.linear(x, pl, out, prologue=ops.PRO_RMSNORM, gamma=gamma, eps=self.cfg.eps, epilogue=epilogue, workspace=self.lin_ws,
+                       out_ld=out_ld)
+        else:
+            L = ops._lib.lib()
+            ops.check(L.pt_rms_norm(ops._ptr(x), None, ops._ptr(gamma), x.shape[0], x.shape[1], self.cfg.eps, ops._ptr(self.h), None,
+                                    ops._stream()), "pt_rms_norm")
+            ops.linear(self.h, pl, out, epilogue=epilogue, workspace=self.lin_ws, out_ld=out_ld)
+
+    def _row_parallel(self, x_in, pl):
+        """x <- fp16(x + all_reduce(fp16(x_in . W_r^T)))  (Linear 'end' + ops.add, llama2/model.py:42,45)."""
+        if self.tp == 1:
+            ops.linear(x_in, pl, self.x, epilogue=ops.EPI_RESIDUAL, residual=self.x, workspace=self.lin_ws)
+        else:
+            ops.linear(x_in, pl, self.part, workspace=self.lin_ws)
+            self._all_reduce(self.part)
+            L = ops._lib.lib()
+            ops.check(L.pt_add_f16(ops._ptr(self.x), ops._ptr(self.part), self.x.numel(), ops._ptr(self.x), ops._stream()), "pt_add_f16")
+
+    def enqueue_step(self):
+        c = self.cfg
+        L_ = ops._lib.lib()
+        ops.embedding(self.emb, self.ids, self.step_t, out=self.x)
+        attn_out = self.attn.data_ptr() + 2 * self.o_ks.offset      # column offset inside the zero-padded k-window
+        act_out = self.act.data_ptr() + 2 * self.down_ks.offset
+        for li, L in enumerate(self.layers):
+            self._norm_linear(self.x, L["ln1"], L["qkv"], self.qkv)
+            a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_LLAMA, ops.SOFTMAX_F32, self.score_scale,
+                              self.sin, self.cos, self.attn_ws, self.error_flag)
+            a.out = attn_out
+            a.out_ld = self.attn.shape[1]
+            ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
+            self._row_parallel(self.attn, L["o"])
+            self._norm_linear_raw(self.x, L["ln2"], L["gu"], act_out, self.act.shape[1])
+            self._row_parallel(self.act, L["down"])
+        self._norm_linear(self.x, self.norm, self.head, self.logits)
+        if self.tp == 1:
+            ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids),
+                                 ops._stream()), "topk")
+        else:
+            ops.check(L_.pt_lm_head_local_topk(ops._ptr(self.logits), self.batch, self.vocab_loc, self.rank * self.vocab_loc,
+                                               ops._ptr(self.next_val), ops._ptr(self.next_ids), ops._stream()), "pt_lm_head_local_topk")
+            torch.distributed.all_gather_into_tensor(self.gather_val, self.next_val.view(1, -1), group=self.group)
+            torch.distributed.all_gather_into_tensor(self.gather_ids, self.next_ids.view(1, -1), group=self.group)
+            ops.check(L_.pt_lm_head_tp_pick(ops._ptr(self.gather_val), ops._ptr(self.gather_ids), self.tp, self.batch,
+                                            ops._ptr(self.next_ids), ops._stream()), "pt_lm_head_tp_pick")
+        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
+
+    def _norm_linear_raw(self, x, gamma, pl, out_ptr, out_ld):
+        """gate|up linear with the SwiGLU epilogue writing at a column offset of the (zero-padded) activation buffer."""
+        L_ = ops._lib.lib()
+        src = x
+        pro = ops.PRO_RMSNORM
+        if not self.fuse_norm:
+            ops.check(L_.pt_rms_norm(ops._ptr(x), None, ops._ptr(gamma), x.shape[0], x.shape[1], self.cfg.eps, ops._ptr(self.h), None,
+                                     ops._stream()), "pt_rms_norm")
+            src, pro = self.h, ops.PRO_NONE
+        a = ops.linear_args(src, pl, self.act, prologue=pro, gamma=gamma if pro else None, eps=self.cfg.eps, epilogue=ops.EPI_SWIGLU,
+                            workspace=self.lin_ws, out_ld=out_ld)
+        a.out = out_ptr
+        ops.check(L_.pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
+
+    def enqueue_linears_only(self):
+        """Every INT4/FP16 transformer linear of one step, back to back (used to time the dominant kernel alone)."""
+        for L in self.layers:
+            self._norm_linear(self.x, L["ln1"], L["qkv"], self.qkv)
+            ops.linear(self.attn, L["o"], self.part, workspace=self.lin_ws)
+            self._norm_linear_raw(self.x, L["ln2"], L["gu"], self.act.data_ptr(), self.act.shape[1])
+            ops.linear(self.act, L["down"], self.part, workspace=self.lin_ws)
+
+    def capture(self):
+        """Captures one loop iteration in a CUDA graph (one eager iteration first so lazy initialisation is done)."""
+        saved = (self.ids.clone(), self.step_t.clone())
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.enqueue_step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.ids.copy_(saved[0])
+        self.step_t.copy_(saved[1])
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.enqueue_step()
+        self.graph = g
+        self.ids.copy_(saved[0])
+        self.step_t.copy_(saved[1])
+        torch.cuda.synchronize()
+
+    def reset(self, input_ids):
+        """input_ids int32 [batch, max_len] (host or device), right-padded with pad_id; step <- 0."""
+        ids = torch.as_tensor(input_ids, dtype=torch.int32)
+        self.ids.copy_(ids.to(self.device, non_blocking=True))
+        self.step_t.zero_()
+        self.stop_mask.zero_()
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.enqueue_step()
+
+    def run(self, input_ids, max_loop=None):
+        """Session.run equivalent (poptransformer/sessions.py:47-49): feeds the id container, runs `max_loop`
+        loop iterations on the device and returns the reference's anchors {'Loop:0': ids, 'Loop:1': step}."""
+        n = self.cfg.max_len if max_loop is None else max_loop
+        if n > self.cfg.max_len:
+            raise ops.PtError(f"max_loop={n} exceeds max_length={self.cfg.max_len}")
+        self.reset(input_ids)
+        for _ in range(n):
+            self.step()
+        out = {"Loop:0": self.ids.cpu().numpy(), "Loop:1": self.step_t.cpu().numpy()}
+        if int(self.error_flag.item()) != 0:
+            raise ops.PtError("a bounded device-side wait gave up during decode (error flag set)")
+        return out

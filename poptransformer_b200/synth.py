@@ -1,0 +1,50 @@
+"""Seeded synthetic checkpoints with the benchmark configurations' shapes and value distributions
+(no tokenizer or pretrained weights are available offline).  Keys follow the HF / reference naming
+that the reference layers look up (e.g. llama2/model.py:114-132 via layers/linear.py:28-40);
+INT4 linears are stored as int8 `<key>` + fp16 `<key>_scale` like the reference's int4 checkpoints."""
+import torch
+
+from .quant import quantize_int4
+
+
+def _normal(shape, gen, device, std=0.02):
+    return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).to(torch.float16)
+
+
+def llama_state_dict(n_layer, d_model, n_head, ffn, vocab, seed=0, device="cpu", int4_group=0):
+    """Llama-2 architecture, weights ~ N(0, 0.02) fp16, RMSNorm weights 1 + N(0, 0.02).
+    int4_group > 0 quantises every transformer linear (not the embedding / LM head)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    sd = {}
+
+    def lin(key, out_f, in_f):
+        w = _normal((out_f, in_f), gen, device)
+        if int4_group:
+            sd[key], sd[key + "_scale"] = quantize_int4(w, int4_group)
+        else:
+            sd[key] = w
+
+    sd["model.embed_tokens.weight"] = _normal((vocab, d_model), gen, device)
+    for i in range(n_layer):
+        p = f"model.layers.{i}."
+        sd[p + "input_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+        sd[p + "post_attention_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+        for nm in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            lin(p + f"self_attn.{nm}.weight", d_model, d_model)
+        lin(p + "mlp.gate_proj.weight", ffn, d_model)
+        lin(p + "mlp.up_proj.weight", ffn, d_model)
+        lin(p + "mlp.down_proj.weight", d_model, ffn)
+    sd["model.norm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+    sd["lm_head.weight"] = _normal((vocab, d_model), gen, device)
+    return sd
+
+
+def prompt_ids(batch, prompt_len, max_len, vocab, pad_id, seed=0):
+    """Uniform-random prompt ids excluding pad_id, right-padded to max_len with pad_id (int32, CPU)."""
+    gen = torch.Generator().manual_seed(seed)
+    ids = torch.full((batch, max_len), pad_id, dtype=torch.int32)
+    p = torch.randint(0, vocab - 1, (batch, prompt_len), generator=gen, dtype=torch.int32)
+    p = torch.where(p >= pad_id, p + 1, p)
+    ids[:, :prompt_len] = p
+    return ids

@@ -1,0 +1,141 @@
+"""CPU checks: the oracle's known answers read off the reference sources, and the product's host-side
+logic (quantiser, RoPE tables, synthetic checkpoints) against the oracle."""
+import numpy as np
+import torch
+
+from oracle import llama_np
+from oracle import ops_np as O
+
+
+def test_int4_lut_matches_reference_table():
+    """custom_ops/int4_to_half_custom_op.cpp:139-166: table[2i] = float(char(i) >> 4), table[2i+1] = float(char(i << 4) >> 4)."""
+    w = np.arange(256, dtype=np.uint8).view(np.int8).reshape(256, 1)
+    out = O.int4_to_half(w, np.ones(256, np.float16), axis=1)         # [2, 256]
+    assert out[0, 0x7F] == 7 and out[1, 0x7F] == -1
+    assert out[0, 0x80] == -8 and out[1, 0x80] == 0
+    assert out[0, 0xF8] == -1 and out[1, 0xF8] == -8
+    assert out[0, 0x12] == 1 and out[1, 0x12] == 2
+    rt = O.int4_unpack(O.int4_pack(np.arange(-8, 8).reshape(1, 16)))
+    assert np.array_equal(rt, np.arange(-8, 8).reshape(1, 16))
+
+
+def test_kv_cache_is_shift_right_newest_first():
+    st = O.KVCacheState()
+    for step in range(5):
+        kv = np.full((1, 1, 2), step + 1, np.float16)
+        c = O.kv_cache(st, step, kv, 4, 1, 1)
+    assert c[0, :, 0].tolist() == [5, 4, 3, 2]       # newest at index 0, oldest dropped at max_len
+    c = O.kv_cache(st, 0, np.full((1, 1, 2), 9, np.float16), 4, 1, 1)
+    assert c[0, :, 0].tolist() == [9, 0, 0, 0]       # step 0 zeroes the clone (kv_cache.cpp:118-124)
+
+
+def test_softmax_v3_unstable_equals_stable_in_safe_range():
+    x = (np.random.default_rng(0).standard_normal((4, 64)) * 2).astype(np.float32)
+    a, b = O.softmax_v3(x, False), O.softmax_v3(x, True)
+    np.testing.assert_allclose(a, b, rtol=1e-5)
+    np.testing.assert_allclose(a.sum(-1), 1.0, rtol=1e-5)
+
+
+def test_masked_positions_contribute_exactly_zero():
+    """Skipping masked cache slots equals the reference's additive -10000 over a zero tail (Q6)."""
+    r = np.random.default_rng(1)
+    B, N, L, H, step = 1, 2, 16, 8, 5
+    q = r.standard_normal((B, N, 1, H)).astype(np.float16)
+    K = np.zeros((B, N, L, H), np.float16); V = np.zeros((B, N, L, H), np.float16)
+    K[:, :, : step + 1] = r.standard_normal((B, N, step + 1, H)); V[:, :, : step + 1] = r.standard_normal((B, N, step + 1, H))
+    full = O.attention_decode(q, K, V, O.decode_mask(B, L, step), H, "float32")
+    short = O.attention_decode(q, K[:, :, : step + 1], V[:, :, : step + 1], np.zeros((B, step + 1), np.float16), H, "float32")
+    assert np.array_equal(full, short)
+    full16 = O.attention_decode(q, K, V, O.decode_mask(B, L, step), H, "float16")
+    short16 = O.attention_decode(q, K[:, :, : step + 1], V[:, :, : step + 1], np.zeros((B, step + 1), np.float16), H, "float16")
+    assert np.array_equal(full16, short16)
+
+
+def test_e4m3_roundtrip_and_saturation():
+    t = O.E4M3_TABLE
+    finite = np.array([b for b in range(256) if not np.isnan(t[b])], dtype=np.uint8)
+    enc = O.e4m3_encode(t[finite])
+    assert np.array_equal(t[enc], t[finite])                     # every representable value encodes to itself (-0 -> -0)
+    assert t[O.e4m3_encode(np.array([1e6, -1e6], np.float32))].tolist() == [448.0, -448.0]
+    # ties to even: 17 is halfway between 16 and 18 (spacing 2) -> 16; 19 -> 20
+    assert t[O.e4m3_encode(np.array([17.0, 19.0], np.float32))].tolist() == [16.0, 20.0]
+    # agrees with torch's e4m3fn conversion inside the finite range
+    x = np.random.default_rng(2).standard_normal(10000).astype(np.float32) * 50
+    x = np.clip(x, -448, 448)
+    tb = torch.from_numpy(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(O.e4m3_encode(x), tb)
+
+
+def test_beam_search_first_step_and_parent_rule():
+    r = np.random.default_rng(3)
+    B, beam, V = 2, 3, 50
+    logits = r.standard_normal((B, beam, V)).astype(np.float32)
+    hyp = np.zeros((B, 6, beam), np.int32); prob = np.zeros((B, beam), np.float32)
+    nid, gid, hyp, prob = O.beam_search_step(logits, hyp, prob, 0, beam)
+    assert np.array_equal(nid, np.argsort(-logits[:, 0], axis=-1, kind="stable")[:, :beam])
+    assert np.array_equal(hyp[:, 0], nid)
+    logits2 = r.standard_normal((B, beam, V)).astype(np.float32)
+    nid2, gid2, hyp2, prob2 = O.beam_search_step(logits2, hyp, prob, 1, beam)
+    for b in range(B):
+        for k in range(beam):
+            par = gid2[b, k] // beam
+            assert hyp2[b, 0, k] == hyp[b, 0, par] and hyp2[b, 1, k] == nid2[b, k]
+            assert np.isclose(prob2[b, k], prob[b, par] + logits2[b, par, nid2[b, k]])
+
+
+def test_norm_ce_single_row_and_multi_row_paths_differ_only_in_statistics():
+    r = np.random.default_rng(4)
+    x = r.standard_normal((2, 768)).astype(np.float16)
+    g = np.ones(768, np.float16); b = np.zeros(768, np.float16)
+    multi = O.norm_ce(x, g, b, 1e-5)
+    single = np.stack([O.norm_ce(x[i:i + 1], g, b, 1e-5)[0] for i in range(2)])
+    assert np.abs(multi.astype(np.float32) - single.astype(np.float32)).max() < 4e-3
+    np.testing.assert_allclose(multi.astype(np.float32).std(axis=1), 1.0, atol=2e-2)
+
+
+def test_product_quantiser_and_tables_match_oracle():
+    from poptransformer_b200 import quant
+    from poptransformer_b200.llama import rope_tables
+    w = torch.randn(32, 512, generator=torch.Generator().manual_seed(0)) * 0.02
+    for group in (128, 512):
+        p, s = quant.quantize_int4(w, group)
+        po, so = O.quantize_int4(w.numpy(), group)
+        assert np.array_equal(p.numpy(), po) and np.array_equal(s.numpy().view(np.uint16), so.view(np.uint16))
+    sin, cos = rope_tables(768, 128, "cpu")
+    so, co = O.llama_rope_tables(768, 128)
+    assert np.array_equal(sin.numpy().view(np.uint16), so.view(np.uint16)) and np.array_equal(cos.numpy().view(np.uint16), co.view(np.uint16))
+    q8, sc = quant.quantize_fp8(w)
+    assert np.array_equal(q8.numpy(), O.e4m3_encode(w.numpy() / np.float32(sc)))
+
+
+def test_llama_oracle_tp_equals_single_rank_within_tolerance():
+    from poptransformer_b200 import synth
+    cfgd = dict(n_layer=2, d_model=256, n_head=2, ffn=512, vocab=1000)
+    sd = {k: v.numpy() for k, v in synth.llama_state_dict(**cfgd, seed=0, device="cpu", int4_group=0).items()}
+    cfg = llama_np.LlamaConfig(**cfgd, max_len=16)
+    ids = synth.prompt_ids(1, 4, 16, 1000, 999, seed=0).numpy()
+    a = llama_np.LlamaOracle(cfg, sd, 1, tp=1).generate(ids, 10, 999)
+    b = llama_np.LlamaOracle(cfg, sd, 1, tp=2).generate(ids, 10, 999)
+    assert np.array_equal(a[:, :4], ids[:, :4])
+    assert (a == b).mean() > 0.8
+
+
+def test_c_restatement_matches_numpy_oracle():
+    """oracle/c/decode_ref.c (timed CPU baseline) against oracle/llama_np.py on the same weights: the two
+    differ only in float32 summation order."""
+    from oracle import c_ref
+    from poptransformer_b200 import synth
+    cfgd = dict(n_layer=2, d_model=256, n_head=2, ffn=512, vocab=1000)
+    for group in (128, 0):
+        sd = {k: v.numpy() for k, v in synth.llama_state_dict(**cfgd, seed=1, device="cpu", int4_group=group).items()}
+        cfg = llama_np.LlamaConfig(**cfgd, max_len=24, group=group)
+        ids = synth.prompt_ids(2, 24, 24, 1000, 999, seed=3).numpy()
+        a = llama_np.LlamaOracle(cfg, sd, 2)
+        b = c_ref.LlamaOracleC(cfg, sd, 2)
+        for step in range(24):
+            la, _ = a.logits(ids[:, step], step)
+            lb, nb = b.logits(ids[:, step], step)
+            np.testing.assert_allclose(la.astype(np.float32), lb.astype(np.float32), rtol=1e-2, atol=5e-3, err_msg=f"step {step}")
+        ka, kb = a.kv[0][0].cache[0], b.kcache(0)        # layer-0 K cache: same values up to fp16 rounding flips of the matmul sums
+        assert (ka.view(np.uint16) == kb.view(np.uint16)).mean() > 0.97
+        np.testing.assert_allclose(ka.astype(np.float32), kb.astype(np.float32), rtol=4e-3, atol=1e-3)
