@@ -75,14 +75,13 @@ int pt_int4_to_half(const void *w, const void *scale, int n, int m, int axis, in
  *
  * pt_linear_repack: one-time re-layout of a weight matrix W[n_out, k_in] stored with
  * k contiguous (INT4: the reference's int8 [n_out, k_in/2] + fp16 scales [n_out, k_in/group])
- * into the tile order the streaming kernel reads with 128-bit loads.
- * Sizes of the outputs: pt_linear_packed_bytes / pt_linear_packed_scale_bytes.
+ * into the tile order the streaming kernel fetches with bulk async copies (INT4 tiles carry
+ * their group scales).  Size of the output: pt_linear_packed_bytes.
  * `interleave_rows` = 1 builds the SwiGLU layout from a [2*f, k] matrix whose first f rows
  * are gate rows and last f rows are up rows (8 gate rows then 8 up rows per 16-row tile). */
 size_t pt_linear_packed_bytes(int wfmt, int n_out, int k_in);
-size_t pt_linear_packed_scale_bytes(int wfmt, int n_out, int k_in, int group);
 int pt_linear_repack(int wfmt, const void *w, const void *scale, int n_out, int k_in, int group,
-                     int interleave_rows, void *packed_w, void *packed_scale, void *stream);
+                     int interleave_rows, void *packed_w, void *stream);
 
 typedef struct pt_linear_args {
   int wfmt;              /* PT_W_*                                                  */
@@ -93,7 +92,6 @@ typedef struct pt_linear_args {
   int ksplit;            /* 0 = let the library choose; >1 needs workspace          */
   const void *x;         /* fp16 [batch, k_in]                                      */
   const void *packed_w;  /* from pt_linear_repack                                   */
-  const void *packed_scale;
   const void *norm_gamma;/* fp16 [k_in]   (PT_PRO_RMSNORM*)                        */
   float norm_eps;
   float act_scale;       /* FP8: activation scale (x ~ act_scale * e4m3)            */
@@ -102,8 +100,14 @@ typedef struct pt_linear_args {
   const void *residual;  /* fp16 [batch, n_out]; may alias `out`                    */
   void *out;             /* fp16 [batch, n_out] (SWIGLU: [batch, n_out/2])          */
   int out_ld;            /* row stride of `out` in elements; 0 = dense              */
-  void *workspace;       /* split-k partials + counters, pt_linear_workspace_bytes  */
+  int pdl;               /* 1: launch with programmatic dependent launch: the kernel may start while the
+                            preceding kernel of the stream is still running; it prefetches its (constant)
+                            weights, then waits for that kernel to complete before it touches x, residual,
+                            out or the workspace.  Safe after any kernel.                              */
+  void *workspace;       /* split-k partials + counters (zeroed once by the caller; every launch
+                            leaves the counters at zero), pt_linear_workspace_bytes             */
   size_t workspace_bytes;
+  int32_t *error_flag;   /* optional device int, set non-zero if a bounded wait gave up        */
 } pt_linear_args;
 
 size_t pt_linear_workspace_bytes(int batch, int n_out, int max_ksplit);
@@ -166,6 +170,7 @@ typedef struct pt_attn_args {
   void *workspace;                   /* pt_attn_workspace_bytes                               */
   size_t workspace_bytes;
   int32_t *error_flag;               /* device int, set non-zero if a bounded wait gave up     */
+  int pdl;                           /* 1: programmatic dependent launch (see pt_linear_args.pdl) */
 } pt_attn_args;
 
 size_t pt_attn_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);

@@ -20,10 +20,10 @@ class LinearArgs(ctypes.Structure):
     _fields_ = [
         ("wfmt", c_int), ("batch", c_int), ("n_out", c_int), ("k_in", c_int), ("group", c_int),
         ("prologue", c_int), ("epilogue", c_int), ("ksplit", c_int),
-        ("x", c_void_p), ("packed_w", c_void_p), ("packed_scale", c_void_p), ("norm_gamma", c_void_p),
+        ("x", c_void_p), ("packed_w", c_void_p), ("norm_gamma", c_void_p),
         ("norm_eps", c_float), ("act_scale", c_float), ("w_scale", c_float),
-        ("bias", c_void_p), ("residual", c_void_p), ("out", c_void_p), ("out_ld", c_int),
-        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("bias", c_void_p), ("residual", c_void_p), ("out", c_void_p), ("out_ld", c_int), ("pdl", c_int),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p),
     ]
 
 
@@ -34,7 +34,7 @@ class AttnArgs(ctypes.Structure):
         ("score_scale", c_float),
         ("step_dev", c_void_p), ("qkv", c_void_p), ("rope_sin", c_void_p), ("rope_cos", c_void_p),
         ("pool", c_void_p), ("page_table", c_void_p), ("out", c_void_p), ("out_ld", c_int),
-        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("pdl", c_int),
     ]
 
 
@@ -45,8 +45,7 @@ SIGNATURES = {
     "pt_launch_count": (ctypes.c_uint64, []),
     "pt_int4_to_half": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_linear_packed_bytes": (c_size_t, [c_int, c_int, c_int]),
-    "pt_linear_packed_scale_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
-    "pt_linear_repack": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "pt_linear_repack": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "pt_linear": (c_int, [ctypes.POINTER(LinearArgs), c_void_p]),
     "pt_norm_ce": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),

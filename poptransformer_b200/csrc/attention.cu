@@ -15,7 +15,7 @@
 namespace pt {
 
 struct AttnParams {
-  int B, n_head, n_kv, qpk, H, page, max_pages, rope_mode, softmax_mode, rot_half, out_ld;
+  int B, n_head, n_kv, qpk, H, page, max_pages, rope_mode, softmax_mode, rot_half, out_ld, pdl;
   __half scale_h;
   int use_scale;
   const int *step;
@@ -100,6 +100,11 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pg = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  if (p.pdl) {
+    // let the next kernel start prefetching its weights; everything this kernel reads was produced upstream
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
   const int step = *p.step;
   const int n_active = step / PAGE + 1;
   if (pg >= n_active) return;
@@ -360,21 +365,32 @@ extern "C" int pt_kv_append_attn(const pt_attn_args *a, void *stream) {
   p.ws_ml = (float2 *)ws; ws += align256(heads * a->max_pages * sizeof(float2));
   p.ws_o = (float *)ws;
   p.error_flag = a->error_flag;
+  p.pdl = a->pdl ? 1 : 0;
 
   const size_t smem = (size_t)2 * p.page * p.H * sizeof(__half) + (size_t)p.qpk * p.H * sizeof(__half) +
                       (size_t)p.qpk * p.page * sizeof(float) + (size_t)p.qpk * 2 * sizeof(float);
   PT_REQUIRE(smem <= 200 * 1024, "pt_kv_append_attn: tile needs %zu bytes of shared memory", smem);
-  dim3 grid(a->max_pages, a->n_kv, a->batch);
-  cudaStream_t st = as_stream(stream);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a->max_pages, a->n_kv, a->batch);
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = as_stream(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  cudaError_t le;
   if (p.H == 128) {
     static bool set128 = false;
     if (!set128) { PT_CUDA(cudaFuncSetAttribute(kv_append_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set128 = true; }
-    kv_append_attn_kernel<128><<<grid, kAttnThreads, smem, st>>>(p);
+    le = cudaLaunchKernelEx(&cfg, kv_append_attn_kernel<128>, p);
   } else {
     static bool set64 = false;
     if (!set64) { PT_CUDA(cudaFuncSetAttribute(kv_append_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set64 = true; }
-    kv_append_attn_kernel<64><<<grid, kAttnThreads, smem, st>>>(p);
+    le = cudaLaunchKernelEx(&cfg, kv_append_attn_kernel<64>, p);
   }
+  if (le != cudaSuccess) return pt::set_error(PT_ERR_CUDA, "pt_kv_append_attn: %s", cudaGetErrorString(le));
   PT_LAUNCH_CHECK("pt_kv_append_attn");
   return PT_OK;
 }

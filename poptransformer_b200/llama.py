@@ -70,9 +70,10 @@ class _KSlice:
 
 class LlamaDecoder:
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, fuse_norm=None, pad_id=None, eos_id=-1,
-                 tp_rank=0, tp_size=1, group=None):
+                 tp_rank=0, tp_size=1, group=None, pdl=True):
         self.cfg, self.batch, self.device = cfg, batch, device
         self.tp, self.rank, self.group = tp_size, tp_rank, group
+        self.pdl = 1 if pdl else 0
         c = cfg
         if c.n_head % tp_size:
             raise ops.PtError(f"n_head={c.n_head} not divisible by tp={tp_size} (llama2/attention.py:130)")
@@ -195,19 +196,19 @@ class LlamaDecoder:
     def _norm_linear(self, x, gamma, pl, out, epilogue=ops.EPI_STORE, out_ld=0):
         if self.fuse_norm:
             ops.linear(x, pl, out, prologue=ops.PRO_RMSNORM, gamma=gamma, eps=self.cfg.eps, epilogue=epilogue, workspace=self.lin_ws,
-                       out_ld=out_ld)
+                       out_ld=out_ld, pdl=self.pdl)
         else:
             L = ops._lib.lib()
             ops.check(L.pt_rms_norm(ops._ptr(x), None, ops._ptr(gamma), x.shape[0], x.shape[1], self.cfg.eps, ops._ptr(self.h), None,
                                     ops._stream()), "pt_rms_norm")
-            ops.linear(self.h, pl, out, epilogue=epilogue, workspace=self.lin_ws, out_ld=out_ld)
+            ops.linear(self.h, pl, out, epilogue=epilogue, workspace=self.lin_ws, out_ld=out_ld, pdl=self.pdl)
 
     def _row_parallel(self, x_in, pl):
         """x <- fp16(x + all_reduce(fp16(x_in . W_r^T)))  (Linear 'end' + ops.add, llama2/model.py:42,45)."""
         if self.tp == 1:
-            ops.linear(x_in, pl, self.x, epilogue=ops.EPI_RESIDUAL, residual=self.x, workspace=self.lin_ws)
+            ops.linear(x_in, pl, self.x, epilogue=ops.EPI_RESIDUAL, residual=self.x, workspace=self.lin_ws, pdl=self.pdl)
         else:
-            ops.linear(x_in, pl, self.part, workspace=self.lin_ws)
+            ops.linear(x_in, pl, self.part, workspace=self.lin_ws, pdl=self.pdl)
             self._all_reduce(self.part)
             L = ops._lib.lib()
             ops.check(L.pt_add_f16(ops._ptr(self.x), ops._ptr(self.part), self.x.numel(), ops._ptr(self.x), ops._stream()), "pt_add_f16")
@@ -221,7 +222,7 @@ class LlamaDecoder:
         for li, L in enumerate(self.layers):
             self._norm_linear(self.x, L["ln1"], L["qkv"], self.qkv)
             a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_LLAMA, ops.SOFTMAX_F32, self.score_scale,
-                              self.sin, self.cos, self.attn_ws, self.error_flag)
+                              self.sin, self.cos, self.attn_ws, self.error_flag, pdl=self.pdl)
             a.out = attn_out
             a.out_ld = self.attn.shape[1]
             ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
@@ -251,7 +252,7 @@ class LlamaDecoder:
                                      ops._stream()), "pt_rms_norm")
             src, pro = self.h, ops.PRO_NONE
         a = ops.linear_args(src, pl, self.act, prologue=pro, gamma=gamma if pro else None, eps=self.cfg.eps, epilogue=ops.EPI_SWIGLU,
-                            workspace=self.lin_ws, out_ld=out_ld)
+                            workspace=self.lin_ws, out_ld=out_ld, pdl=self.pdl)
         a.out = out_ptr
         ops.check(L_.pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
 

@@ -80,16 +80,14 @@ class PackedLinear:
         else:
             self.group = 0
         nbytes = L.pt_linear_packed_bytes(wfmt, self.n_out, self.k_in)
-        sbytes = L.pt_linear_packed_scale_bytes(wfmt, self.n_out, self.k_in, self.group)
         self.packed_w = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
-        self.packed_scale = torch.empty(max(sbytes, 16), dtype=torch.uint8, device=w.device)
         check(L.pt_linear_repack(wfmt, _ptr(w.contiguous()), _ptr(scale) if scale is not None else None, self.n_out, self.k_in,
-                                 self.group, 1 if interleave_gate_up else 0, _ptr(self.packed_w), _ptr(self.packed_scale), _stream()),
-              "pt_linear_repack")
+                                 self.group, 1 if interleave_gate_up else 0, _ptr(self.packed_w), _stream()), "pt_linear_repack")
 
     @property
     def nbytes(self):
-        """Algorithmic bytes one launch streams from HBM (weights + scales)."""
+        """Algorithmic bytes one launch streams from HBM: weights plus one fp16 scale per row and group.  (The
+        packed tiles repeat a scale for every 128-k chunk of its group, so the buffer itself can be larger.)"""
         sb = self.n_out * (self.k_in // self.group) * 2 if self.wfmt == W_INT4 else 0
         wb = self.n_out * self.k_in // 2 if self.wfmt == W_INT4 else self.n_out * self.k_in * (2 if self.wfmt == W_FP16 else 1)
         return wb + sb
@@ -103,13 +101,14 @@ def linear_workspace(batch, n_out_max, max_ksplit=16, device="cuda"):
 
 
 def linear_args(x, pl, out, prologue=PRO_NONE, epilogue=EPI_STORE, gamma=None, eps=0.0, act_scale=0.0, bias=None,
-                residual=None, workspace=None, ksplit=0, out_ld=0):
+                residual=None, workspace=None, ksplit=0, out_ld=0, pdl=0, error_flag=None):
     a = LinearArgs()
     a.wfmt, a.batch, a.n_out, a.k_in, a.group = pl.wfmt, x.shape[0], pl.n_out, pl.k_in, pl.group
     a.prologue, a.epilogue, a.ksplit = prologue, epilogue, ksplit
-    a.x, a.packed_w, a.packed_scale = _ptr(x), _ptr(pl.packed_w), _ptr(pl.packed_scale)
+    a.x, a.packed_w = _ptr(x), _ptr(pl.packed_w)
     a.norm_gamma, a.norm_eps, a.act_scale, a.w_scale = _ptr(gamma), eps, act_scale, pl.w_scale
-    a.bias, a.residual, a.out, a.out_ld = _ptr(bias), _ptr(residual), _ptr(out), out_ld
+    a.bias, a.residual, a.out, a.out_ld, a.pdl = _ptr(bias), _ptr(residual), _ptr(out), out_ld, pdl
+    a.error_flag = _ptr(error_flag)
     a.workspace = _ptr(workspace)
     a.workspace_bytes = workspace.numel() if workspace is not None else 0
     return a
@@ -245,7 +244,7 @@ def attn_workspace(batch, n_head, head_dim, max_pages, device="cuda"):
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
-def attn_args(qkv, step, cache, out, n_head, rope_mode, softmax_mode, score_scale, rope_sin, rope_cos, workspace, error_flag):
+def attn_args(qkv, step, cache, out, n_head, rope_mode, softmax_mode, score_scale, rope_sin, rope_cos, workspace, error_flag, pdl=0):
     a = AttnArgs()
     a.batch, a.n_head, a.n_kv, a.head_dim = qkv.shape[0], n_head, cache.n_kv, cache.head_dim
     a.page_size, a.max_pages, a.rope_mode, a.softmax_mode = cache.page_size, cache.max_pages, rope_mode, softmax_mode
@@ -254,6 +253,7 @@ def attn_args(qkv, step, cache, out, n_head, rope_mode, softmax_mode, score_scal
     a.pool, a.page_table, a.out, a.out_ld = _ptr(cache.pool), _ptr(cache.page_table), _ptr(out), 0
     a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
     a.error_flag = _ptr(error_flag)
+    a.pdl = pdl
     return a
 
 

@@ -41,6 +41,6 @@ def test_argument_checks_run_without_a_gpu():
     assert rc == -1 and b"8192" in L.pt_last_error()
     rc = L.pt_int4_to_half(ctypes.c_void_p(16), ctypes.c_void_p(16), 4, 4, 2, 0, ctypes.c_void_p(16), None)
     assert rc == -1 and b"axis" in L.pt_last_error()
-    assert L.pt_linear_packed_bytes(0, 4096, 4096) == 4096 * 2048
-    assert L.pt_linear_packed_scale_bytes(0, 4096, 4096, 128) == 4096 * 32 * 2
+    assert L.pt_linear_packed_bytes(0, 4096, 4096) == 256 * 32 * 1056     # 16-row x 128-k tiles: 1 KB of nibbles + 32 B of scales
+    assert L.pt_linear_packed_bytes(1, 4096, 4096) == 4096 * 4096 * 2
     assert L.pt_linear_workspace_bytes(1, 4096, 4) >= 4 * 4096 * 4

@@ -76,7 +76,7 @@ def test_linear_int4(cuda, batch, n, k, group):
         got = ops.linear(dev(x, cuda), pl, workspace=ws, ksplit=ksplit).cpu().numpy().astype(np.float32)
         # exact fp16 products, fp32 accumulation in a different order than numpy: tiny relative error + fp16 output rounding
         np.testing.assert_allclose(got, exp.astype(np.float16).astype(np.float32), rtol=2e-3, atol=2e-3 * np.abs(exp).max())
-    assert torch.count_nonzero(ws[:1024]).item() == 0, "split-k counters must return to zero"
+    assert torch.count_nonzero(ws[:256]).item() == 0, "split-k counters must return to zero"
 
 
 @pytest.mark.parametrize("batch,n,k", [(1, 32000, 512), (4, 50257, 768), (2, 100, 1600), (16, 300, 64)])
@@ -168,11 +168,35 @@ def test_norm_ce(cuda, rows, dim):
     b = (0.1 * r.standard_normal(dim)).astype(np.float16)
     got = ops.layer_norm_ce(dev(x, cuda), dev(g, cuda), dev(b, cuda), 1e-5).cpu().numpy()
     exp = O.norm_ce(x, g, b, 1e-5)
-    # fp32 statistics are summed in a different order; the fp16 chain is identical, so outputs agree except where the
-    # fp16 rounding of mean / inv-std flips (<= 1 fp16 ulp of those scalars)
+    # The fp32 statistics are summed in a different order than numpy's.  The fp16 chain after them is identical, so a row
+    # differs only when the fp16 rounding of its mean or inverse std-dev flips by one ulp, which moves the elements of that
+    # row by at most a few fp16 ulps of the output.
     diff = np.abs(got.astype(np.float32) - exp.astype(np.float32))
     assert diff.max() <= 4e-3
-    assert (got.view(np.uint16) == exp.view(np.uint16)).mean() > 0.99
+    # with the kernel's own rounded statistics recovered from its output, the fp16 chain must be reproducible exactly:
+    # re-run the oracle's chain with (m, r) perturbed by at most one ulp and require one combination to match bit for bit
+    xf = x.astype(np.float32)
+    for row in range(rows):
+        n = dim
+        if rows == 1:
+            mean = xf[row].sum(dtype=np.float32) / np.float32(n)
+            var = (xf[row] * xf[row]).sum(dtype=np.float32) / np.float32(n) - mean * mean + np.float32(1e-5)
+            m0 = np.float16(mean)
+        else:
+            m0 = np.float16(xf[row].sum(dtype=np.float32) / np.float32(n))
+            var = max((xf[row] * xf[row]).sum(dtype=np.float32) / np.float32(n) - np.float32(m0) ** 2, np.float32(0)) + np.float32(1e-5)
+        r0 = np.float16(np.float32(1.0) / np.sqrt(np.float32(var)))
+        found = False
+        for dm in (0, 1, -1):
+            for dr in (0, 1, -1):
+                m = (m0.view(np.uint16) + np.uint16(dm)).view(np.float16) if dm else m0
+                r = (r0.view(np.uint16) + np.uint16(dr)).view(np.float16) if dr else r0
+                t = (xf[row] - np.float32(m)).astype(np.float16)
+                t = (t.astype(np.float32) * np.float32(r)).astype(np.float16)
+                t = (t.astype(np.float32) * g.astype(np.float32)).astype(np.float16)
+                t = (t.astype(np.float32) + b.astype(np.float32)).astype(np.float16)
+                found |= np.array_equal(t.view(np.uint16), got[row].view(np.uint16))
+        assert found, f"row {row}: fp16 chain not reproducible from statistics within one ulp"
 
 
 def test_norm_ce_rejects_like_reference(cuda):
