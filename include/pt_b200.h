@@ -193,6 +193,38 @@ int pt_kv_reorder_pages(void *pool, const int32_t *page_table, const int32_t *sp
 int pt_kv_reorder_table(int32_t *page_table, int32_t *table_tmp, int32_t *spare_pages, const int32_t *parent,
                         const int32_t *step_dev, int rows, int page_size, int max_pages, void *stream);
 
+/* ---- persistent decode step (Llama architecture) ------------------------------------------------
+ * One cooperative launch executes a whole iteration of the reference's decode loop body
+ * (poptransformer/models/llama2/model.py:162-197, models/base_model.py:313-355) for batch <= 2: embedding, every
+ * transformer block (INT4 linears packed by pt_linear_repack with PT_W_INT4; q|k|v fused, gate|up interleaved), final
+ * RMSNorm, fp16 LM head (PT_W_FP16), greedy id and the loop-carry update (ids container, step, stop mask).
+ * Same arithmetic as the per-op kernels; one block per SM streams its share of all weights through a shared-memory
+ * ring so that HBM stays busy across the phase barriers.  `layers` is a DEVICE array of n_layer entries.
+ * The workspace must be zeroed once before the first launch. */
+typedef struct pt_llama_layer {
+  const void *qkv, *o, *gu, *down; /* packed INT4 weights                     */
+  const void *ln1, *ln2;           /* fp16 RMSNorm weights [d_model]           */
+  void *pool;                      /* this layer's KV page pool                */
+} pt_llama_layer;
+
+typedef struct pt_llama_step_args {
+  int batch, d_model, n_head, head_dim, ffn, vocab, n_layer, max_len, page_size, max_pages, pad_id, eos_id;
+  float norm_eps, score_scale;
+  const pt_llama_layer *layers;
+  const void *norm, *head, *emb;     /* final RMSNorm weight, packed fp16 LM head, fp16 embedding table [vocab, d_model] */
+  const void *rope_sin, *rope_cos;   /* fp16 [max_len, head_dim/2]                                                   */
+  int32_t *ids, *step_dev, *stop_mask, *next_ids; /* ids [batch, max_len]; stop_mask optional                          */
+  const int32_t *page_table;         /* [batch, max_pages]                                                          */
+  void *x, *qkv, *attn, *act;        /* fp16 scratch: [batch, d_model], [batch, 3 d_model], [batch, d_model], [batch, ffn] */
+  void *logits;                      /* optional fp16 [batch, vocab]                                                */
+  void *workspace;                   /* pt_llama_step_workspace_bytes, zeroed once                                  */
+  size_t workspace_bytes;
+  int32_t *error_flag;               /* set non-zero if a bounded wait gave up                                      */
+} pt_llama_step_args;
+
+size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);
+int pt_llama_decode_step(const pt_llama_step_args *args, void *stream);
+
 /* ---- top-k / LM-head ids / beam search --------------------------------------------------
  * pt_topk replaces ops.topk (popart.py:135-137) on [rows, dim] fp16 or fp32 (dtype 0/1): values
  * sorted descending, lowest index wins ties.  k <= 32. */

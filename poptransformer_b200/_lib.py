@@ -38,6 +38,18 @@ class AttnArgs(ctypes.Structure):
     ]
 
 
+class LlamaLayer(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in ("qkv", "o", "gu", "down", "ln1", "ln2", "pool")]
+
+
+class LlamaStepArgs(ctypes.Structure):
+    _fields_ = [(n, c_int) for n in ("batch", "d_model", "n_head", "head_dim", "ffn", "vocab", "n_layer", "max_len", "page_size",
+                                     "max_pages", "pad_id", "eos_id")] + [("norm_eps", c_float), ("score_scale", c_float)] + \
+               [(n, c_void_p) for n in ("layers", "norm", "head", "emb", "rope_sin", "rope_cos", "ids", "step_dev", "stop_mask", "next_ids",
+                                        "page_table", "x", "qkv", "attn", "act", "logits", "workspace")] + \
+               [("workspace_bytes", c_size_t), ("error_flag", c_void_p)]
+
+
 # name -> (restype, argtypes); mirrors include/pt_b200.h one to one
 SIGNATURES = {
     "pt_last_error": (ctypes.c_char_p, []),
@@ -58,6 +70,8 @@ SIGNATURES = {
     "pt_kv_export": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_kv_reorder_pages": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pt_kv_reorder_table": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "pt_llama_step_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "pt_llama_decode_step": (c_int, [ctypes.POINTER(LlamaStepArgs), c_void_p]),
     "pt_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_lm_head_local_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_lm_head_tp_pick": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),

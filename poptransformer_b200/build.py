@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpt_b200.so")
-SOURCES = ["api.cu", "linear.cu", "attention.cu", "ops.cu"]
+SOURCES = ["api.cu", "linear.cu", "attention.cu", "ops.cu", "decode_llama.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

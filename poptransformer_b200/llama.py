@@ -70,7 +70,7 @@ class _KSlice:
 
 class LlamaDecoder:
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, fuse_norm=None, pad_id=None, eos_id=-1,
-                 tp_rank=0, tp_size=1, group=None, pdl=True):
+                 tp_rank=0, tp_size=1, group=None, pdl=True, persistent=None, keep_logits=True):
         self.cfg, self.batch, self.device = cfg, batch, device
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         self.pdl = 1 if pdl else 0
@@ -167,6 +167,33 @@ class LlamaDecoder:
         self.attn_ws = ops.attn_workspace(B, self.h_loc, c.head_dim, self.caches[0].max_pages, dev)
         self.lin_ws = ops.linear_workspace(B, max(3 * self.d_loc, 2 * self.f_loc, d, self.logits.shape[1]), 16, dev)
         self.graph = None
+        # The persistent whole-step kernel covers the single-GPU, INT4, batch <= 2 case; everything else takes the per-op kernels.
+        can_persist = (tp == 1 and batch <= 2 and c.head_dim == 128 and page_size == 64 and self.layers[0]["qkv"].wfmt == ops.W_INT4
+                       and d % 128 == 0 and f % 128 == 0)
+        self.persistent = can_persist if persistent is None else (persistent and can_persist)
+        if self.persistent:
+            L = ops._lib.lib()
+            arr = (ops._lib.LlamaLayer * c.n_layer)()
+            for i, lay in enumerate(self.layers):
+                arr[i].qkv, arr[i].o = lay["qkv"].packed_w.data_ptr(), lay["o"].packed_w.data_ptr()
+                arr[i].gu, arr[i].down = lay["gu"].packed_w.data_ptr(), lay["down"].packed_w.data_ptr()
+                arr[i].ln1, arr[i].ln2 = lay["ln1"].data_ptr(), lay["ln2"].data_ptr()
+                arr[i].pool = self.caches[i].pool.data_ptr()
+            self.mk_layers = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(dev)
+            self.mk_ws = torch.zeros(L.pt_llama_step_workspace_bytes(B, c.n_head, c.head_dim, self.caches[0].max_pages), dtype=torch.uint8, device=dev)
+            a = ops._lib.LlamaStepArgs()
+            a.batch, a.d_model, a.n_head, a.head_dim, a.ffn, a.vocab, a.n_layer = B, d, c.n_head, c.head_dim, f, c.vocab, c.n_layer
+            a.max_len, a.page_size, a.max_pages, a.pad_id, a.eos_id = c.max_len, page_size, self.caches[0].max_pages, self.pad_id, self.eos_id
+            a.norm_eps, a.score_scale = c.eps, self.score_scale
+            a.layers, a.norm, a.head, a.emb = self.mk_layers.data_ptr(), self.norm.data_ptr(), self.head.packed_w.data_ptr(), self.emb.data_ptr()
+            a.rope_sin, a.rope_cos = self.sin.data_ptr(), self.cos.data_ptr()
+            a.ids, a.step_dev, a.stop_mask, a.next_ids = self.ids.data_ptr(), self.step_t.data_ptr(), self.stop_mask.data_ptr(), self.next_ids.data_ptr()
+            a.page_table = self.caches[0].page_table.data_ptr()
+            a.x, a.qkv, a.attn, a.act = self.x.data_ptr(), self.qkv.data_ptr(), self.attn.data_ptr(), self.act.data_ptr()
+            a.logits = self.logits.data_ptr() if keep_logits else None
+            a.workspace, a.workspace_bytes = self.mk_ws.data_ptr(), self.mk_ws.numel()
+            a.error_flag = self.error_flag.data_ptr()
+            self.mk_args = a
         torch.cuda.synchronize()
 
     # ---- accounting -------------------------------------------------------------------------
@@ -216,6 +243,9 @@ class LlamaDecoder:
     def enqueue_step(self):
         c = self.cfg
         L_ = ops._lib.lib()
+        if self.persistent:
+            ops.check(L_.pt_llama_decode_step(ctypes.byref(self.mk_args), ops._stream()), "pt_llama_decode_step")
+            return
         ops.embedding(self.emb, self.ids, self.step_t, out=self.x)
         attn_out = self.attn.data_ptr() + 2 * self.o_ks.offset      # column offset inside the zero-padded k-window
         act_out = self.act.data_ptr() + 2 * self.down_ks.offset

@@ -14,21 +14,24 @@ pytestmark = pytest.mark.gpu
 TINY = dict(n_layer=2, d_model=256, n_head=2, ffn=512, vocab=1000)
 
 
-def _setup(cuda, batch, max_len, int4_group, seed=0):
+def _setup(cuda, batch, max_len, int4_group, seed=0, persistent=None):
     from poptransformer_b200 import llama, synth
     sd = synth.llama_state_dict(**TINY, seed=seed, device="cpu", int4_group=int4_group)
     cfg = llama.LlamaConfig(**TINY, max_len=max_len, int4_group=int4_group)
-    dec = llama.LlamaDecoder(cfg, sd, batch, device=cuda)
+    dec = llama.LlamaDecoder(cfg, sd, batch, device=cuda, persistent=persistent)
     ocfg = llama_np.LlamaConfig(**TINY, max_len=max_len, group=int4_group)
     orc = llama_np.LlamaOracle(ocfg, {k: v.numpy() for k, v in sd.items()}, batch)
     return dec, orc
 
 
-@pytest.mark.parametrize("batch,int4_group", [(1, 128), (2, 0), (1, 256), (16, 128)])
-def test_logits_teacher_forced(cuda, batch, int4_group):
+@pytest.mark.parametrize("batch,int4_group,persistent", [(1, 128, True), (2, 128, True), (1, 128, False), (2, 0, False), (1, 256, False),
+                                                        (16, 128, False)])
+def test_logits_teacher_forced(cuda, batch, int4_group, persistent):
+    """persistent=True: the whole-step kernel; False: the per-op kernels.  Both against the oracle."""
     from poptransformer_b200 import synth
-    max_len = 40
-    dec, orc = _setup(cuda, batch, max_len, int4_group)
+    max_len = 72 if persistent else 40          # more than one KV page for the persistent kernel
+    dec, orc = _setup(cuda, batch, max_len, int4_group, persistent=persistent)
+    assert dec.persistent == persistent
     ids = synth.prompt_ids(batch, max_len, max_len, TINY["vocab"], dec.pad_id, seed=1)     # all prompt: every step is forced
     dec.reset(ids)
     orc.reset()
@@ -47,11 +50,11 @@ def test_logits_teacher_forced(cuda, batch, int4_group):
     np.testing.assert_allclose(dense.astype(np.float32), ref.astype(np.float32), rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("use_graph", [False, True])
-def test_greedy_stream(cuda, use_graph):
+@pytest.mark.parametrize("use_graph,persistent", [(False, False), (True, False), (False, True), (True, True)])
+def test_greedy_stream(cuda, use_graph, persistent):
     from poptransformer_b200 import synth
     batch, max_len, prompt = 2, 48, 8
-    dec, orc = _setup(cuda, batch, max_len, 128, seed=3)
+    dec, orc = _setup(cuda, batch, max_len, 128, seed=3, persistent=persistent)
     ids = synth.prompt_ids(batch, prompt, max_len, TINY["vocab"], dec.pad_id, seed=2)
     if use_graph:
         dec.capture()
