@@ -200,7 +200,11 @@ int pt_kv_reorder_table(int32_t *page_table, int32_t *table_tmp, int32_t *spare_
  * RMSNorm, fp16 LM head (PT_W_FP16), greedy id and the loop-carry update (ids container, step, stop mask).
  * Same arithmetic as the per-op kernels; one block per SM streams its share of all weights through a shared-memory
  * ring so that HBM stays busy across the phase barriers.  `layers` is a DEVICE array of n_layer entries.
- * The workspace must be zeroed once before the first launch. */
+ * The workspace must be zeroed once before the first launch.
+ * Weights: every matrix (q|k|v, o, gate|up, down, LM head) is first packed with pt_linear_repack and then re-ordered
+ * with pt_llama_stream_permute into the order in which each SM's consumer warps read it (a permutation of the
+ * packed tiles inside every SM's share; same size). */
+int pt_llama_stream_permute(int wfmt, const void *packed, void *out, int n_out, int k_in, void *stream);
 typedef struct pt_llama_layer {
   const void *qkv, *o, *gu, *down; /* packed INT4 weights                     */
   const void *ln1, *ln2;           /* fp16 RMSNorm weights [d_model]           */
@@ -220,6 +224,8 @@ typedef struct pt_llama_step_args {
   void *workspace;                   /* pt_llama_step_workspace_bytes, zeroed once                                  */
   size_t workspace_bytes;
   int32_t *error_flag;               /* set non-zero if a bounded wait gave up                                      */
+  uint64_t *trace;                   /* optional [n_sm, n_layer, 16] global-timer stamps (ns) of each phase boundary */
+  int debug;                         /* profiling aid; bit 0: consume the weight tiles without doing the tile math  */
 } pt_llama_step_args;
 
 size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);

@@ -6,7 +6,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libpt_b200.so")
+LIB_PATH = os.environ.get("PT_B200_LIB", os.path.join(HERE, "libpt_b200.so"))
 
 c_void_p, c_int, c_float, c_size_t, c_int64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_int64
 
@@ -47,7 +47,7 @@ class LlamaStepArgs(ctypes.Structure):
                                      "max_pages", "pad_id", "eos_id")] + [("norm_eps", c_float), ("score_scale", c_float)] + \
                [(n, c_void_p) for n in ("layers", "norm", "head", "emb", "rope_sin", "rope_cos", "ids", "step_dev", "stop_mask", "next_ids",
                                         "page_table", "x", "qkv", "attn", "act", "logits", "workspace")] + \
-               [("workspace_bytes", c_size_t), ("error_flag", c_void_p)]
+               [("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("trace", c_void_p), ("debug", c_int)]
 
 
 # name -> (restype, argtypes); mirrors include/pt_b200.h one to one
@@ -70,6 +70,7 @@ SIGNATURES = {
     "pt_kv_export": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_kv_reorder_pages": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pt_kv_reorder_table": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "pt_llama_stream_permute": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "pt_llama_step_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "pt_llama_decode_step": (c_int, [ctypes.POINTER(LlamaStepArgs), c_void_p]),
     "pt_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

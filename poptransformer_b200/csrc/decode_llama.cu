@@ -24,17 +24,24 @@
 namespace pt {
 namespace mk {
 
-constexpr int NCW = 16;                 // consumer warps
+#ifndef PT_MK_WARPS
+#define PT_MK_WARPS 16
+#endif
+constexpr int NCW = PT_MK_WARPS;        // consumer warps
 constexpr int NCT = NCW * 32;           // consumer threads
 constexpr int THREADS = NCT + 32;       // + the producer warp
+constexpr int NGRP = NCW / 4;           // 4-warp attention groups
 constexpr int TILE_I4 = 1056, TILE_F16 = 1024;
-constexpr int STAGE_BYTES = NCW * TILE_I4;  // 16896
+constexpr int STAGE_TILES = NCW;                  // one tile per consumer warp per stage
+constexpr int STAGE_BYTES = ((STAGE_TILES * TILE_I4 + 127) / 128 * 128) > 33792 ? ((STAGE_TILES * TILE_I4 + 127) / 128 * 128) : 33792;
+constexpr int V_OFFSET = 16896;                   // a K page and a V page (2 x 16 KB) share one attention stage
+constexpr int MAXU = 8;                           // attention units handled per SM per pass
 constexpr int BMAX = 2;
 constexpr int H = 128, PAGE = 64;
 constexpr int SPIN_LIMIT = 1 << 22;
 
 struct Params {
-  int B, d, n_head, ffn, vocab, n_layer, max_len, max_pages, ns, xs_stride, pad_id, eos_id;
+  int B, d, n_head, ffn, vocab, n_layer, max_len, max_pages, ns, xs_stride, pad_id, eos_id, debug;
   float eps;
   __half score_scale;
   const pt_llama_layer *layers;
@@ -50,6 +57,7 @@ struct Params {
   int *cand_idx;
   unsigned *barrier;  // [0], [1]: counters used by alternate launches; [2]: which one the next launch uses
   int *error_flag;
+  unsigned long long *trace;  // optional: [grid][n_layer][12] global-timer stamps of the phase boundaries
 };
 
 // ------------------------------------------------------------------------------------------ small helpers
@@ -63,35 +71,41 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                "r"(bar)
                : "memory");
 }
-// Bounded wait; gives up at once when the block has already recorded a failure, so that after an error every loop of the
-// kernel still runs its normal trip count (all named barriers stay matched) but finishes quickly.
+// Bounded wait.  Each try_wait carries a suspend-time hint, so a waiting warp sleeps in hardware instead of burning issue
+// slots that the working warps (and the producer) need.  The wait gives up early when the block has already recorded a
+// failure, so that after an error every loop of the kernel still runs its normal trip count (all named barriers stay
+// matched) but finishes quickly.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int *abort_flag) {
-  for (int it = 0; it < SPIN_LIMIT; ++it) {
+  for (int it = 0; it < (1 << 18); ++it) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok)
-                 : "r"(bar), "r"(parity)
+                 : "r"(bar), "r"(parity), "r"(2000u)
                  : "memory");
     if (ok) return true;
-    if (*abort_flag) return false;
+    if ((it & 7) == 7 && *abort_flag) return false;
   }
   return false;
+}
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 
 struct Shared {           // fixed-size part, placed after the ring / activations
-  float red[2][NCW][32][4];
+  float red[NCW][2][32][4];  // per warp: partial sums of the first / last row tile of its tile range
   float corr[96][8];      // [chunk][batch column], up to 96 chunks of 128 k
-  __half qs[H], newk[H], newv[H];
-  float ps[PAGE + 1];
-  float o4[4][H];
+  __half qs[MAXU][H], newk[MAXU][H], newv[MAXU][H];
+  float ps[NGRP][PAGE];   // one row per 4-warp attention group
+  float ml[NGRP][2];
+  int last[MAXU];
   float stat[BMAX];
-  float wred[NCW];
-  float bestv[NCW][BMAX];
-  int besti[NCW][BMAX];
-  float ml[2];
+  float wred[32];
+  float bestv[32][BMAX];
+  int besti[32][BMAX];
   volatile int abort;
-  int last;
   uint64_t full[16], empty[16];
 };
 
@@ -103,6 +117,7 @@ struct Ctx {
   unsigned *bar_ctr;
   unsigned bar_target;
   uint32_t gs;  // global stage counter (same sequence in producer and consumers)
+  unsigned long long *tr;  // optional fine-grained stamps of the current layer
 };
 
 // Grid barrier over all blocks (consumer threads only).  Bounded: on time-out the error flag is set and the block
@@ -141,11 +156,21 @@ __device__ __forceinline__ float consumer_sum(Ctx &c, float v) {  // sum over th
   return t;
 }
 
+// RMSNorm weights of the next phase, requested before the grid barrier so that their (HBM) latency hides behind it.
+struct Gamma { uint4 v[3]; };
+__device__ __forceinline__ Gamma load_gamma(const __half *gamma, int K) {
+  Gamma g;
+#pragma unroll
+  for (int q = 0; q < 3; ++q)
+    g.v[q] = (gamma && (int)threadIdx.x + q * NCT < K / 8) ? __ldg(reinterpret_cast<const uint4 *>(gamma) + threadIdx.x + q * NCT) : make_uint4(0, 0, 0, 0);
+  return g;
+}
+
 // Stage activations src[B, K] (global, written by other SMs: read through L2) into shared memory for the next linear phase.
 // INT4 phases use the per-chunk swizzle of linear.cu ([chunk][w][tig] 16-byte units) and produce the offset corrections;
-// the fp16 phase (LM head) keeps the natural order.  gamma != nullptr applies RMSNorm first.
+// the fp16 phase (LM head) keeps the natural order.  gamma != nullptr applies RMSNorm first (weights in `gm`).
 template <bool INT4>
-__device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma) {
+__device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma, const Gamma &gm) {
   const Params &p = c.p;
   const int tid = threadIdx.x;
   const int units = K / 8;
@@ -155,6 +180,7 @@ __device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma) {
 #pragma unroll
     for (int q = 0; q < 3; ++q) v[q] = (tid + q * NCT < units) ? __ldcg(xr + tid + q * NCT) : make_uint4(0, 0, 0, 0);
     __half rb = __half(0);
+    if (c.tr && tid == 0 && b == 0) { c.tr[13] = gtime(); c.tr[14] = (unsigned long long)(v[0].x); c.tr[14] = gtime(); }
     if (gamma) {
       float ss = 0.f;
 #pragma unroll
@@ -168,6 +194,7 @@ __device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma) {
       }
       ss = consumer_sum(c, ss);
       rb = __float2half_rn(1.0f / sqrtf(ss / (float)K + p.eps));
+      if (c.tr && tid == 0 && b == 0) c.tr[15] = gtime();
     }
 #pragma unroll
     for (int q = 0; q < 3; ++q) {
@@ -175,8 +202,7 @@ __device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma) {
       const bool valid = u < units;
       __half *h = reinterpret_cast<__half *>(&v[q]);
       if (gamma && valid) {
-        const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(gamma) + u);
-        const __half *gh = reinterpret_cast<const __half *>(&gv);
+        const __half *gh = reinterpret_cast<const __half *>(&gm.v[q]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) h[j] = h_mul(h_mul(h[j], rb), gh[j]);
       }
@@ -210,7 +236,56 @@ enum { EPI_QKV = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_HEAD = 3 };
 
 struct Best { float v[BMAX]; int i[BMAX]; };
 
-// One linear phase over this SM's row tiles [r0, r1) of a matrix with `nchunks` tiles per row tile.
+// How the T tiles of an SM's share of a matrix (its row tiles, [row tile][chunk] order) are dealt to the consumer warps:
+// warp w owns the contiguous range [start(w), start(w) + len(w)), ranges differ by at most one tile.
+struct Split {
+  int base, rem;
+  __device__ __forceinline__ Split(int T) : base(T / NCW), rem(T % NCW) {}
+  __device__ __forceinline__ int len(int w) const { return base + (w < rem ? 1 : 0); }
+  __device__ __forceinline__ int start(int w) const { return w * base + min(w, rem); }
+  __device__ __forceinline__ int owner(int q) const {  // warp whose range holds tile q
+    const int big = rem * (base + 1);
+    if (q < big) return q / (base + 1);
+    return base > 0 ? rem + (q - big) / base : NCW - 1;
+  }
+  __device__ __forceinline__ int stages() const { return base + (rem ? 1 : 0); }
+};
+
+template <int EPI>
+__device__ __forceinline__ void tile_epilogue(const Params &p, const float (&v)[4], int rt, int lane, __half *out, int N, Best *best) {
+  const int g = lane >> 2, tig = lane & 3;
+  if (tig != 0) return;  // batch columns 0 and 1 live in the tig == 0 lanes
+#pragma unroll
+  for (int jb = 0; jb < 2; ++jb) {
+    const int b = jb;
+    if (b >= p.B) continue;
+    const float lo = v[jb], hi = v[2 + jb];  // rows g and g + 8
+    if (EPI == EPI_SWIGLU) {
+      const int n = rt * 8 + g;
+      if (n < N / 2) out[(size_t)b * (N / 2) + n] = h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo)));
+    } else {
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        const int n = rt * 16 + g + 8 * hr;
+        if (n >= N) continue;
+        __half y = __float2half_rn(hr ? hi : lo);
+        if (EPI == EPI_RESID) y = h_add(__ldcg(out + (size_t)b * N + n), y);
+        if (EPI == EPI_HEAD) {
+          const float f = __half2float(y);
+          if (f > best->v[b] || (f == best->v[b] && n < best->i[b])) { best->v[b] = f; best->i[b] = n; }
+          if (out) out[(size_t)b * N + n] = y;
+        } else {
+          out[(size_t)b * N + n] = y;
+        }
+      }
+    }
+  }
+}
+
+// One linear phase over this SM's row tiles [r0, r1) of a matrix with `nchunks` tiles per row tile.  The SM's tiles arrive
+// in "stream order": stage j holds tile start(w) + j of every warp w that still has one (see pt_llama_stream_permute), so
+// each warp accumulates a contiguous run of chunks in registers and there is no synchronisation inside the phase.  Row
+// tiles that are split between warps are summed after one barrier, in warp order (deterministic).
 template <int WFMT, int EPI>
 __device__ void linear_phase(Ctx &c, int n_rt, int nchunks, __half *out, int N, Best *best) {
   constexpr int TILE = WTraits<WFMT>::kTileBytes;
@@ -219,108 +294,96 @@ __device__ void linear_phase(Ctx &c, int n_rt, int nchunks, __half *out, int N, 
   const Params &p = c.p;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   const int r0 = (int)((long long)c.sm * n_rt / c.G), r1 = (int)((long long)(c.sm + 1) * n_rt / c.G);
-  const int total = (r1 - r0) * nchunks;
-  int cur = 0, buf = 0;  // row tile (local index) whose partial sums `acc` holds
+  const int m = r1 - r0, total = m * nchunks;
+  const Split sp(total);
+  const int len = sp.len(warp), start = sp.start(warp), nstages = sp.stages();
+  const int first_rt = start / nchunks;
+  int rt = first_rt, ch = start - first_rt * nchunks;
+  const int ch_first = ch;  // chunk at which this warp enters its first row tile
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t ring_s = smem_addr(c.ring) + warp * TILE + lane * 16;
+  const uint32_t xs_s = smem_addr(c.xs) + tig * 16 + g * p.xs_stride;
+  const uint32_t corr_s = smem_addr(&c.sh->corr[0][0]) + 8 * tig;
 
-  auto flush = [&](int rt_l) {
-    float4 *slot = reinterpret_cast<float4 *>(&c.sh->red[buf][warp][lane][0]);
-    *slot = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    consumer_sync();
-    if (warp == (rt_l & (NCW - 1))) {
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int w = 0; w < NCW; ++w) {
-        const float4 t = *reinterpret_cast<const float4 *>(&c.sh->red[buf][w][lane][0]);
-        v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
-      }
-      const int rt = r0 + rt_l;
-      if (tig == 0) {  // batch columns 0 and 1 live in the tig == 0 lanes
-#pragma unroll
-        for (int jb = 0; jb < 2; ++jb) {
-          const int b = jb;
-          if (b >= p.B) continue;
-          const float lo = v[jb], hi = v[2 + jb];  // rows g and g + 8
-          if (EPI == EPI_SWIGLU) {
-            const int n = rt * 8 + g;
-            if (n < N / 2) out[(size_t)b * (N / 2) + n] = h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo)));
-          } else {
-#pragma unroll
-            for (int hr = 0; hr < 2; ++hr) {
-              const int n = rt * 16 + g + 8 * hr;
-              if (n >= N) continue;
-              __half y = __float2half_rn(hr ? hi : lo);
-              if (EPI == EPI_RESID) y = h_add(__ldcg(out + (size_t)b * N + n), y);
-              if (EPI == EPI_HEAD) {
-                const float f = __half2float(y);
-                if (f > best->v[b] || (f == best->v[b] && n < best->i[b])) { best->v[b] = f; best->i[b] = n; }
-                if (out) out[(size_t)b * N + n] = y;
-              } else {
-                out[(size_t)b * N + n] = y;
-              }
-            }
-          }
-        }
-      }
-    }
-    buf ^= 1;
+  auto store_partial = [&](int slot) {
+    *reinterpret_cast<float4 *>(&c.sh->red[warp][slot][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
   };
 
-  for (int t0 = 0; t0 < total; t0 += NCW, ++c.gs) {
-    const int t = t0 + warp;
+  // Software pipeline: the tile of stage j + 1 is pulled into registers (and its stage released to the producer) before
+  // the tile of stage j is multiplied, so the registers act as one more ring stage and refills start earlier.
+  uint4 va = make_uint4(0, 0, 0, 0), vb = va, na = va, nb = va;
+  float2 sf = make_float2(1.f, 1.f), nsf = sf;
+  auto fetch = [&](int j, uint4 &a4, uint4 &b4, float2 &s2) {  // stage j of this phase (global stage c.gs) -> registers
     const int slot = c.gs % p.ns;
     const bool got = mbar_wait(smem_addr(&c.sh->full[slot]), (c.gs / p.ns) & 1, &c.sh->abort);
     if (!got) {
       c.sh->abort = 1;
       if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 4);
     }
-    uint4 va = make_uint4(0, 0, 0, 0), vb = va;
-    float2 sf = make_float2(1.f, 1.f);
-    const bool have = t < total;
-    if (have && got) {
-      const unsigned char *tile = c.ring + (size_t)slot * STAGE_BYTES + (size_t)warp * TILE;
-      va = *reinterpret_cast<const uint4 *>(tile + lane * 16);
-      vb = *reinterpret_cast<const uint4 *>(tile + 512 + lane * 16);
-      if (WFMT == PT_W_INT4) sf = __half22float2(*reinterpret_cast<const __half2 *>(tile + 1024 + g * 4));
+    if (j < len && got) {
+      const uint32_t t_s = ring_s + slot * STAGE_BYTES;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a4.x), "=r"(a4.y), "=r"(a4.z), "=r"(a4.w) : "r"(t_s));
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b4.x), "=r"(b4.y), "=r"(b4.z), "=r"(b4.w) : "r"(t_s + 512));
+      if (WFMT == PT_W_INT4) {
+        uint32_t sraw;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sraw) : "r"(t_s - lane * 16 + 1024 + g * 4));
+        s2 = __half22float2(*reinterpret_cast<__half2 *>(&sraw));
+      }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_addr(&c.sh->empty[slot]));  // this warp's tile is in registers
-    if (!have) continue;
-    const int rt_l = t / nchunks, ch = t - rt_l * nchunks;
-    while (cur < rt_l) {  // every warp flushes every row tile exactly once, in order (zeros if it had no tile of it)
-      flush(cur);
-      ++cur;
-      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-    }
-    float cc[4] = {0.f, 0.f, 0.f, 0.f};
-    const unsigned char *xc = c.xs + (size_t)ch * CHUNK_X_BYTES + tig * 16;
+    ++c.gs;
+  };
+  if (nstages > 0) fetch(0, va, vb, sf);
+  for (int j = 0; j < nstages; ++j) {
+    if (j + 1 < nstages) fetch(j + 1, na, nb, nsf);
+    if (j < len && !(p.debug & 1)) {
+      float cc[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t x_s = xs_s + ch * CHUNK_X_BYTES;
 #pragma unroll
-    for (int u = 0; u < UNITS; ++u) {
-      uint32_t fa[4], fb[4];
-      expand8<WFMT>(va, u, fa);
-      expand8<WFMT>(vb, u, fb);
-      uint4 xv = make_uint4(0, 0, 0, 0);
-      if (g < p.B) xv = *reinterpret_cast<const uint4 *>(xc + (size_t)g * p.xs_stride + u * 64);
-      if (WFMT == PT_W_INT4) {
+      for (int u = 0; u < UNITS; ++u) {
+        uint32_t fa[4], fb[4];
+        expand8<WFMT>(va, u, fa);
+        expand8<WFMT>(vb, u, fb);
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (g < p.B) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w) : "r"(x_s + u * 64));
         mma16816(cc, fa[0], fb[0], fa[1], fb[1], xv.x, xv.y);
         mma16816(cc, fa[2], fb[2], fa[3], fb[3], xv.z, xv.w);
+      }
+      if (WFMT == PT_W_INT4) {
+        float2 co;
+        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(co.x), "=f"(co.y) : "r"(corr_s + ch * 32));
+        acc[0] += sf.x * (cc[0] - co.x);
+        acc[1] += sf.x * (cc[1] - co.y);
+        acc[2] += sf.y * (cc[2] - co.x);
+        acc[3] += sf.y * (cc[3] - co.y);
       } else {
-        mma16816(acc, fa[0], fb[0], fa[1], fb[1], xv.x, xv.y);
-        mma16816(acc, fa[2], fb[2], fa[3], fb[3], xv.z, xv.w);
+        acc[0] += cc[0]; acc[1] += cc[1]; acc[2] += cc[2]; acc[3] += cc[3];
+      }
+      if (++ch == nchunks) {  // this warp reached the end of row tile rt
+        if (rt == first_rt && ch_first != 0) store_partial(0);                  // entered it midway: another warp holds the beginning
+        else tile_epilogue<EPI>(p, acc, r0 + rt, lane, out, N, best);           // had all of it
+        ch = 0;
+        ++rt;
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
       }
     }
-    if (WFMT == PT_W_INT4) {
-      const float2 co = *reinterpret_cast<const float2 *>(&c.sh->corr[ch][2 * tig]);
-      acc[0] += sf.x * (cc[0] - co.x);
-      acc[1] += sf.x * (cc[1] - co.y);
-      acc[2] += sf.y * (cc[2] - co.x);
-      acc[3] += sf.y * (cc[3] - co.y);
-    }
+    va = na; vb = nb; sf = nsf;
   }
-  while (cur < r1 - r0) {
-    flush(cur);
-    ++cur;
-    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+  if (len > 0 && ch != 0) store_partial(rt == first_rt ? 0 : 1);  // the range ended inside a row tile
+  consumer_sync();
+  // ---- row tiles shared by several warps: warp (r % NCW) sums the pieces in warp order
+  for (int r = warp; r < m; r += NCW) {
+    const int q0 = r * nchunks, q1 = q0 + nchunks - 1;
+    const int w_lo = sp.owner(q0), w_hi = sp.owner(q1);
+    if (w_lo == w_hi) continue;  // one warp had the whole row tile and already wrote it
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int w = w_lo; w <= w_hi; ++w) {
+      const int s_w = (sp.start(w) / nchunks == r) ? 0 : 1;  // r is the first row tile of w's range, or its last
+      const float4 t = *reinterpret_cast<const float4 *>(&c.sh->red[w][s_w][lane][0]);
+      v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+    }
+    tile_epilogue<EPI>(p, v, r0 + r, lane, out, N, best);
   }
 }
 
@@ -330,126 +393,166 @@ __device__ __forceinline__ void rope_pair(const __half *x, const __half *sin_r, 
   dst[i] = h_add(h_mul(a, co), h_mul(__hneg(b), s));
   dst[i + H / 2] = h_add(h_mul(b, co), h_mul(a, s));
 }
+__device__ __forceinline__ void group_sync(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory"); }
 
-// Attention phase: units (b, head, page) are dealt round-robin to the SMs; the producer has queued K and V tiles.
+// Attention phase.  Units (b, head, page) are dealt round-robin to the SMs (unit u -> SM u % G); the producer has queued
+// one stage per unit that has cached tokens (K page at offset 0, V page at V_OFFSET).  The consumer warps form NGRP
+// groups of four warps; group q handles this SM's units q, q + NGRP, ... on its own (scores with 8 lanes per token, softmax
+// statistics by warp shuffles, P.V with one thread per channel), so units of an SM run concurrently.
 __device__ void attention_phase(Ctx &c, const pt_llama_layer &L) {
   const Params &p = c.p;
   Shared *sh = c.sh;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gt = tid & 127;
+  const int grp = (warp >> 2) < NGRP ? (warp >> 2) : -1;  // warps beyond the last full group only release stages
   const int step = c.step, n_active = step / PAGE + 1;
   const int n_units = p.B * p.n_head * n_active;
   const int row_elems = 3 * p.d;
   const __half *sin_r = p.sin_t + (size_t)step * (H / 2), *cos_r = p.cos_t + (size_t)step * (H / 2);
-  for (int u = c.sm; u < n_units; u += c.G) {
-    const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
-    const int n_valid = min(PAGE, step + 1 - pg * PAGE);
-    const bool owner = (pg == n_active - 1);
-    const int n_load = owner ? n_valid - 1 : n_valid;
-    const __half *qrow = p.qkv + (size_t)b * row_elems;
-    if (tid < H / 2) rope_pair(qrow + (size_t)head * H, sin_r, cos_r, tid, sh->qs);
-    if (owner) {
-      if (tid >= 64 && tid < 64 + H / 2) rope_pair(qrow + p.d + (size_t)head * H, sin_r, cos_r, tid - 64, sh->newk);
-      if (tid >= 128 && tid < 128 + H) sh->newv[tid - 128] = __ldcg(qrow + 2 * p.d + (size_t)head * H + tid - 128);
-    }
-    const __half *Ks = nullptr, *Vs = nullptr;
-    int slotK = 0, slotV = 0;
-    if (n_load > 0) {
-      slotK = c.gs % p.ns;
-      const bool g1 = mbar_wait(smem_addr(&sh->full[slotK]), (c.gs / p.ns) & 1, &sh->abort);
-      ++c.gs;
-      slotV = c.gs % p.ns;
-      const bool g2 = mbar_wait(smem_addr(&sh->full[slotV]), (c.gs / p.ns) & 1, &sh->abort);
-      ++c.gs;
-      if (!(g1 && g2)) {
-        sh->abort = 1;
-        if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 5);
-      }
-      Ks = reinterpret_cast<const __half *>(c.ring + (size_t)slotK * STAGE_BYTES);
-      Vs = reinterpret_cast<const __half *>(c.ring + (size_t)slotV * STAGE_BYTES);
-    }
-    consumer_sync();  // q (and the new k, v) staged
-    if (owner && !sh->abort) {  // append the new token to the pool
-      const int phys = p.page_table[(size_t)b * p.max_pages + pg];
-      __half *gK = (__half *)L.pool + (((size_t)phys * 2 + 0) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
-      __half *gV = (__half *)L.pool + (((size_t)phys * 2 + 1) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
-      if (tid < H) gK[tid] = sh->newk[tid];
-      else if (tid < 2 * H) gV[tid - H] = sh->newv[tid - H];
-    }
-    // scores: 8 lanes per cached token, all 64 tokens of the page in one pass
+  for (int u0 = c.sm; u0 < n_units; u0 += MAXU * c.G) {
+    const int nu = min(MAXU, (n_units - u0 + c.G - 1) / c.G);  // units of this pass: u0 + k G
+    // ---- q (and the new token's k, v) of every unit in one go: one L2 round trip for the whole pass
     {
-      const int sub = lane & 7, t = tid >> 3;
-      float s = 0.f;
-      if (t < n_valid && !sh->abort) {
-        const __half *kr = (t < n_load) ? Ks + (size_t)t * H : sh->newk;
+      const int k = tid >> 6, i = tid & 63;
+      if (k < nu) {
+        const int u = u0 + k * c.G;
+        const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
+        const __half *qrow = p.qkv + (size_t)b * row_elems;
+        rope_pair(qrow + (size_t)head * H, sin_r, cos_r, i, sh->qs[k]);
+        if (pg == n_active - 1) {
+          rope_pair(qrow + p.d + (size_t)head * H, sin_r, cos_r, i, sh->newk[k]);
+          sh->newv[k][i] = __ldcg(qrow + 2 * p.d + (size_t)head * H + i);
+          sh->newv[k][i + 64] = __ldcg(qrow + 2 * p.d + (size_t)head * H + i + 64);
+        }
+      }
+    }
+    consumer_sync();
+    // stage index of each unit of the pass (units without cached tokens have none)
+    uint32_t gs_unit[MAXU];
+    {
+      uint32_t g0 = c.gs;
+      for (int k = 0; k < nu; ++k) {
+        const int u = u0 + k * c.G;
+        const int pg = u % n_active;
+        const int n_valid = min(PAGE, step + 1 - pg * PAGE);
+        const int n_load = (pg == n_active - 1) ? n_valid - 1 : n_valid;
+        gs_unit[k] = g0;
+        if (n_load > 0) ++g0;
+      }
+      c.gs = g0;
+    }
+    for (int k = 0; k < nu; ++k) {
+      const int u = u0 + k * c.G;
+      const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
+      const int n_valid = min(PAGE, step + 1 - pg * PAGE);
+      const bool owner = (pg == n_active - 1);
+      const int n_load = owner ? n_valid - 1 : n_valid;
+      const int slot = gs_unit[k] % p.ns;
+      if ((k % NGRP) != grp) {  // not this group's unit: release the stage at once
+        if (n_load > 0 && lane == 0) {
+          // the arrival only counts once the stage is full, so wait for it first (keeps phases aligned)
+          mbar_wait(smem_addr(&sh->full[slot]), (gs_unit[k] / p.ns) & 1, &sh->abort);
+          mbar_arrive(smem_addr(&sh->empty[slot]));
+        }
+        continue;
+      }
+      const __half *Ks = nullptr, *Vs = nullptr;
+      if (n_load > 0) {
+        if (!mbar_wait(smem_addr(&sh->full[slot]), (gs_unit[k] / p.ns) & 1, &sh->abort)) {
+          sh->abort = 1;
+          if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 5);
+        }
+        Ks = reinterpret_cast<const __half *>(c.ring + (size_t)slot * STAGE_BYTES);
+        Vs = reinterpret_cast<const __half *>(c.ring + (size_t)slot * STAGE_BYTES + V_OFFSET);
+      }
+      if (owner && !sh->abort) {  // append the new token to the pool
+        const int phys = p.page_table[(size_t)b * p.max_pages + pg];
+        __half *gK = (__half *)L.pool + (((size_t)phys * 2 + 0) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
+        __half *gV = (__half *)L.pool + (((size_t)phys * 2 + 1) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
+        gK[gt] = sh->newk[k][gt];
+        gV[gt] = sh->newv[k][gt];
+      }
+      // scores: 8 lanes per cached token, 16 tokens per pass of the 128-thread group
+      float *ps = sh->ps[grp];
+      {
+        const int sub = lane & 7;
+        for (int tb = 0; tb < n_valid; tb += 16) {
+          const int t = tb + (gt >> 3);
+          float sc = 0.f;
+          if (t < n_valid && !sh->abort) {
+            const __half *kr = (t < n_load) ? Ks + (size_t)t * H : sh->newk[k];
 #pragma unroll
-        for (int v = 0; v < 2; ++v) {
-          const uint4 kq = *reinterpret_cast<const uint4 *>(kr + v * 64 + sub * 8);
-          const uint4 qq = *reinterpret_cast<const uint4 *>(sh->qs + v * 64 + sub * 8);
-          const __half2 *kh = reinterpret_cast<const __half2 *>(&kq), *qh = reinterpret_cast<const __half2 *>(&qq);
+            for (int v = 0; v < 2; ++v) {
+              const uint4 kq = *reinterpret_cast<const uint4 *>(kr + v * 64 + sub * 8);
+              const uint4 qq = *reinterpret_cast<const uint4 *>(sh->qs[k] + v * 64 + sub * 8);
+              const __half2 *kh = reinterpret_cast<const __half2 *>(&kq), *qh = reinterpret_cast<const __half2 *>(&qq);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 a = __half22float2(kh[j]), q2 = __half22float2(qh[j]);
-            s += a.x * q2.x + a.y * q2.y;
+              for (int j = 0; j < 4; ++j) {
+                const float2 a = __half22float2(kh[j]), q2 = __half22float2(qh[j]);
+                sc += a.x * q2.x + a.y * q2.y;
+              }
+            }
           }
+          sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+          if (sub == 0 && t < n_valid) ps[t] = __half2float(h_mul(__float2half_rn(sc), p.score_scale));
         }
       }
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
-      if (sub == 0 && t < n_valid) sh->ps[t] = __half2float(h_mul(__float2half_rn(s), p.score_scale));
-    }
-    consumer_sync();
-    if (warp == 0) {  // softmax statistics of the page (fp32, like the reference's cast before SoftmaxV3)
-      float m = -INFINITY;
-      for (int t = lane; t < n_valid; t += 32) m = fmaxf(m, sh->ps[t]);
-      m = warp_max(m);
-      float l = 0.f;
-      for (int t = lane; t < n_valid; t += 32) {
-        const float e = expf(sh->ps[t] - m);
-        sh->ps[t] = e;
-        l += e;
-      }
-      l = warp_sum(l);
-      if (lane == 0) { sh->ml[0] = m; sh->ml[1] = l; }
-    }
-    consumer_sync();
-    {  // P.V: 4 token quarters x 128 channels
-      const int q4 = tid >> 7, j = tid & 127;
-      float o = 0.f;
-      if (!sh->abort)
-        for (int t = q4; t < n_valid; t += 4) {
-          const __half vv = (t < n_load) ? Vs[(size_t)t * H + j] : sh->newv[j];
-          o += sh->ps[t] * __half2float(vv);
+      group_sync(grp);
+      if ((warp & 3) == 0) {  // softmax statistics of the page (fp32, like the reference's cast before SoftmaxV3)
+        float m = -INFINITY;
+        for (int t = lane; t < n_valid; t += 32) m = fmaxf(m, ps[t]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int t = lane; t < n_valid; t += 32) {
+          const float e = expf(ps[t] - m);
+          ps[t] = e;
+          l += e;
         }
-      sh->o4[q4][j] = o;
+        l = warp_sum(l);
+        if (lane == 0) { sh->ml[grp][0] = m; sh->ml[grp][1] = l; }
+      }
+      group_sync(grp);
+      {  // P.V: one thread per channel
+        float o = 0.f;
+        if (!sh->abort)
+          for (int t = 0; t < n_valid; ++t) {
+            const __half vv = (t < n_load) ? Vs[(size_t)t * H + gt] : sh->newv[k][gt];
+            o += ps[t] * __half2float(vv);
+          }
+        const size_t hd = (size_t)b * p.n_head + head;
+        p.ws_o[(hd * p.max_pages + pg) * H + gt] = o;
+        if (gt == 0) p.ws_ml[hd * p.max_pages + pg] = make_float2(sh->ml[grp][0], sh->ml[grp][1]);
+      }
+      group_sync(grp);  // the group is done with the stage and with ps / ml
+      if (n_load > 0 && lane == 0) mbar_arrive(smem_addr(&sh->empty[slot]));
     }
-    consumer_sync();
-    if (n_load > 0 && lane == 0) {  // the K and V stages may be refilled
-      mbar_arrive(smem_addr(&sh->empty[slotK]));
-      mbar_arrive(smem_addr(&sh->empty[slotV]));
-    }
-    const size_t hd = (size_t)b * p.n_head + head;
-    if (tid < H) p.ws_o[(hd * p.max_pages + pg) * H + tid] = (sh->o4[0][tid] + sh->o4[1][tid]) + (sh->o4[2][tid] + sh->o4[3][tid]);
-    if (tid == 0) p.ws_ml[hd * p.max_pages + pg] = make_float2(sh->ml[0], sh->ml[1]);
+    // ---- last page of a (sequence, head) to arrive combines that head in page order
     __threadfence();
     consumer_sync();
-    if (tid == 0) sh->last = (atomicAdd(p.attn_counters + hd, 1) == n_active - 1);
+    if (tid < nu) {
+      const int u = u0 + tid * c.G;
+      const int head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
+      sh->last[tid] = (atomicAdd(p.attn_counters + (size_t)b * p.n_head + head, 1) == n_active - 1);
+    }
     consumer_sync();
-    if (sh->last) {  // last page of this (sequence, head) to arrive: combine in page order
+    for (int k = grp; k >= 0 && k < nu; k += NGRP) {
+      if (!sh->last[k]) continue;
+      const int u = u0 + k * c.G;
+      const int head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
+      const size_t hd = (size_t)b * p.n_head + head;
       __threadfence();
-      if (tid == 0) p.attn_counters[hd] = 0;
-      if (tid < H) {
-        float M = -INFINITY;
-        for (int i = 0; i < n_active; ++i) M = fmaxf(M, __ldcg(&p.ws_ml[hd * p.max_pages + i]).x);
-        float Lsum = 0.f, o = 0.f;
-        for (int i = 0; i < n_active; ++i) {
-          const float2 v = __ldcg(&p.ws_ml[hd * p.max_pages + i]);
-          const float w = expf(v.x - M);
-          Lsum += v.y * w;
-          o += __ldcg(&p.ws_o[(hd * p.max_pages + i) * H + tid]) * w;
-        }
-        p.attn[(size_t)b * p.d + (size_t)head * H + tid] = __float2half_rn(o / Lsum);
+      if (gt == 0) p.attn_counters[hd] = 0;
+      float M = -INFINITY;
+      for (int i = 0; i < n_active; ++i) M = fmaxf(M, __ldcg(&p.ws_ml[hd * p.max_pages + i]).x);
+      float Lsum = 0.f, o = 0.f;
+      for (int i = 0; i < n_active; ++i) {
+        const float2 v = __ldcg(&p.ws_ml[hd * p.max_pages + i]);
+        const float w = expf(v.x - M);
+        Lsum += v.y * w;
+        o += __ldcg(&p.ws_o[(hd * p.max_pages + i) * H + gt]) * w;
       }
+      p.attn[(size_t)b * p.d + (size_t)head * H + gt] = __float2half_rn(o / Lsum);
     }
     consumer_sync();
   }
@@ -459,29 +562,40 @@ __device__ void attention_phase(Ctx &c, const pt_llama_layer &L) {
 struct Producer {
   const Params &p;
   Shared *sh;
-  unsigned char *ring;
   int sm, G;
-  uint32_t gs;
+  int slot;            // ring slot of the next stage
+  uint32_t parity;     // parity to wait for on that slot's `empty` barrier
+  bool first_round;    // slots have not been used yet: nothing to wait for
+  uint32_t ring_s, full_s, empty_s;  // shared-memory addresses
   bool ok;
-  __device__ void push(const void *src, uint32_t bytes) {
-    if (!ok) return;
-    const int slot = gs % p.ns;
-    const uint32_t use = gs / p.ns;
-    if (use > 0 && !mbar_wait(smem_addr(&sh->empty[slot]), (use - 1) & 1, &sh->abort)) {
+  // The loop below competes with the consumer warps for issue slots, so it is kept to a handful of instructions per stage:
+  // no divisions, all addresses incremental.  One stage: `bytes` from src at offset 0 and, for attention stages, `bytes2`
+  // from src2 at V_OFFSET.
+  __device__ __forceinline__ void push(const void *src, uint32_t bytes, const void *src2, uint32_t bytes2) {
+    if (!first_round && !mbar_wait(empty_s + slot * 8, parity, &sh->abort)) {
+      if (ok && p.error_flag) atomicExch(p.error_flag, 6);
       ok = false;
       sh->abort = 1;
-      if (p.error_flag) atomicExch(p.error_flag, 6);
-      return;
     }
-    mbar_expect_tx(smem_addr(&sh->full[slot]), bytes);
-    bulk_g2s(smem_addr(ring + (size_t)slot * STAGE_BYTES), src, bytes, smem_addr(&sh->full[slot]));
-    ++gs;
+    if (ok) {
+      const uint32_t fb = full_s + slot * 8, dst = ring_s + slot * STAGE_BYTES;
+      mbar_expect_tx(fb, bytes + bytes2);
+      bulk_g2s(dst, src, bytes, fb);
+      if (bytes2) bulk_g2s(dst + V_OFFSET, src2, bytes2, fb);
+    }
+    if (++slot == p.ns) {
+      slot = 0;
+      if (first_round) first_round = false;
+      else parity ^= 1u;
+    }
   }
-  __device__ void push_matrix(const unsigned char *w, int n_rt, int nchunks, int tile) {
+  __device__ __forceinline__ void push_matrix(const unsigned char *w, int n_rt, int nchunks, int tile) {
     const int r0 = (int)((long long)sm * n_rt / G), r1 = (int)((long long)(sm + 1) * n_rt / G);
-    const int total = (r1 - r0) * nchunks;
-    const unsigned char *base = w + (size_t)r0 * nchunks * tile;
-    for (int t = 0; t < total && ok; t += NCW) push(base + (size_t)t * tile, (uint32_t)min(NCW, total - t) * tile);
+    int left = (r1 - r0) * nchunks * tile;                 // bytes of this SM's share
+    const unsigned char *src = w + (size_t)r0 * nchunks * tile;
+    const int stage = STAGE_TILES * tile;
+    // stream order: full stages of NCW tiles, then one short stage with the T % NCW warps that have one more tile
+    for (; left > 0 && ok; left -= stage, src += stage) push(src, (uint32_t)min(stage, left), nullptr, 0);
   }
   __device__ void push_attention(const pt_llama_layer &L, int step) {
     const int n_active = step / PAGE + 1;
@@ -494,8 +608,7 @@ struct Producer {
       const int phys = p.page_table[(size_t)b * p.max_pages + pg];
       const __half *gK = (const __half *)L.pool + (((size_t)phys * 2 + 0) * p.n_head + head) * PAGE * H;
       const __half *gV = (const __half *)L.pool + (((size_t)phys * 2 + 1) * p.n_head + head) * PAGE * H;
-      push(gK, (uint32_t)n_load * H * 2);
-      push(gV, (uint32_t)n_load * H * 2);
+      push(gK, (uint32_t)n_load * H * 2, gV, (uint32_t)n_load * H * 2);
     }
   }
 };
@@ -524,7 +637,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   if (warp == NCW) {
     // ---------------- producer: one lane walks the whole step's weight / KV stream of this SM
     if (lane == 0) {
-      Producer pr{p, sh, ring, (int)blockIdx.x, (int)gridDim.x, 0u, true};
+      Producer pr{p, sh, (int)blockIdx.x, (int)gridDim.x, 0, 0u, true, smem_addr(ring), smem_addr(&sh->full[0]), smem_addr(&sh->empty[0]), true};
       for (int l = 0; l < p.n_layer; ++l) {
         const pt_llama_layer &L = p.layers[l];
         pr.push_matrix((const unsigned char *)L.qkv, n_rt_qkv, nc_d, TILE_I4);
@@ -542,7 +655,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   // Two barrier counters are used by alternate launches: word [2] says which one is this launch's (it is zero: the
   // previous launch cleared it when it finished); the last block clears the other one at the very end.
   const unsigned which = __ldcg(p.barrier + 2) & 1u;
-  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u};
+  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, nullptr};
 
   // embedding: every SM gathers the rows itself (no barrier needed); the copy in global memory serves the residual adds
   for (int i = tid; i < p.B * (p.d / 8); i += NCT) {
@@ -552,31 +665,53 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
     const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.emb + (size_t)id * p.d) + u);
     if ((u % c.G) == c.sm) reinterpret_cast<uint4 *>(p.x + (size_t)b * p.d)[u] = v;
   }
+  Gamma g1 = load_gamma((const __half *)p.layers[0].ln1, p.d);
+  const Gamma gnone = load_gamma(nullptr, 0);
   grid_sync(c);
 
+  unsigned long long *tr = p.trace ? p.trace + ((size_t)blockIdx.x * p.n_layer) * 16 : nullptr;
+#define PT_STAMP(k) do { if (tr && tid == 0) tr[l * 16 + (k)] = gtime(); } while (0)
   for (int l = 0; l < p.n_layer; ++l) {
     const pt_llama_layer &L = p.layers[l];
-    stage_x<true>(c, p.x, p.d, (const __half *)L.ln1);
+    PT_STAMP(0);
+    c.tr = tr ? tr + l * 16 : nullptr;
+    stage_x<true>(c, p.x, p.d, (const __half *)L.ln1, g1);
+    c.tr = nullptr;
+    PT_STAMP(1);
     linear_phase<PT_W_INT4, EPI_QKV>(c, n_rt_qkv, nc_d, p.qkv, 3 * p.d, nullptr);
+    PT_STAMP(2);
     grid_sync(c);
+    PT_STAMP(3);
     attention_phase(c, L);
+    PT_STAMP(4);
     grid_sync(c);
-    stage_x<true>(c, p.attn, p.d, nullptr);
+    PT_STAMP(5);
+    stage_x<true>(c, p.attn, p.d, nullptr, gnone);
     linear_phase<PT_W_INT4, EPI_RESID>(c, n_rt_o, nc_d, p.x, p.d, nullptr);
+    PT_STAMP(6);
+    const Gamma g2 = load_gamma((const __half *)L.ln2, p.d);
     grid_sync(c);
-    stage_x<true>(c, p.x, p.d, (const __half *)L.ln2);
+    PT_STAMP(7);
+    stage_x<true>(c, p.x, p.d, (const __half *)L.ln2, g2);
+    PT_STAMP(8);
     linear_phase<PT_W_INT4, EPI_SWIGLU>(c, n_rt_gu, nc_d, p.act, 2 * p.ffn, nullptr);
+    PT_STAMP(9);
     grid_sync(c);
-    stage_x<true>(c, p.act, p.ffn, nullptr);
+    PT_STAMP(10);
+    stage_x<true>(c, p.act, p.ffn, nullptr, gnone);
     linear_phase<PT_W_INT4, EPI_RESID>(c, n_rt_o, nc_f, p.x, p.d, nullptr);
+    PT_STAMP(11);
+    g1 = load_gamma(l + 1 < p.n_layer ? (const __half *)p.layers[l + 1].ln1 : p.norm, p.d);
     grid_sync(c);
+    PT_STAMP(12);
   }
+#undef PT_STAMP
 
   // final norm + LM head + arg-max (lowest index wins ties)
   Best best;
 #pragma unroll
   for (int b = 0; b < BMAX; ++b) { best.v[b] = -INFINITY; best.i[b] = 0x7fffffff; }
-  stage_x<false>(c, p.x, p.d, p.norm);
+  stage_x<false>(c, p.x, p.d, p.norm, g1);
   linear_phase<PT_W_FP16, EPI_HEAD>(c, n_rt_head, nc_head, p.logits, p.vocab, &best);
   for (int b = 0; b < p.B; ++b) {
     float v = best.v[b];
@@ -638,10 +773,52 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   }
 }
 
+// Re-orders the tiles of a packed matrix ([row tile][chunk] order) inside every SM's share into stream order: the tile that
+// consumer warp w processes at its j-th step sits at position j * NCW + w of the share.
+__global__ void stream_permute_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, int n_rt, int nchunks, int tile_u, int G) {
+  for (int sm = blockIdx.y; sm < G; sm += gridDim.y) {
+    const int r0 = (int)((long long)sm * n_rt / G), r1 = (int)((long long)(sm + 1) * n_rt / G);
+    const int T = (r1 - r0) * nchunks;
+    const Split sp(T);
+    const size_t seg = (size_t)r0 * nchunks * tile_u;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < (size_t)T * tile_u; i += (size_t)gridDim.x * blockDim.x) {
+      const int d = (int)(i / tile_u), e = (int)(i - (size_t)d * tile_u);
+      int j, w;
+      if (d < sp.base * NCW) { j = d / NCW; w = d - j * NCW; }
+      else { j = sp.base; w = d - sp.base * NCW; }
+      const int q = sp.start(w) + j;
+      dst[seg + (size_t)d * tile_u + e] = src[seg + (size_t)q * tile_u + e];
+    }
+  }
+}
+
 }  // namespace mk
 }  // namespace pt
 
 using namespace pt;
+
+static int mk_sm_count(int *out) {
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    PT_CUDA(cudaGetDevice(&dev));
+    PT_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  }
+  *out = n_sm;
+  return PT_OK;
+}
+
+extern "C" int pt_llama_stream_permute(int wfmt, const void *packed, void *out, int n_out, int k_in, void *stream) {
+  PT_REQUIRE(packed && out && packed != out, "pt_llama_stream_permute: needs distinct source and destination buffers");
+  PT_REQUIRE(wfmt == PT_W_INT4 || wfmt == PT_W_FP16, "pt_llama_stream_permute: weight format %d not used by the persistent kernel", wfmt);
+  PT_REQUIRE(n_out > 0 && k_in > 0 && k_in % chunk_k(wfmt) == 0, "pt_llama_stream_permute: bad shape [%d, %d]", n_out, k_in);
+  int n_sm = 0;
+  if (int rc = mk_sm_count(&n_sm)) return rc;
+  mk::stream_permute_kernel<<<dim3(32, n_sm), 256, 0, as_stream(stream)>>>((const uint4 *)packed, (uint4 *)out, ceil_div(n_out, 16), k_in / chunk_k(wfmt),
+                                                                            tile_bytes(wfmt) / 16, n_sm);
+  PT_LAUNCH_CHECK("pt_llama_stream_permute");
+  return PT_OK;
+}
 
 extern "C" size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_dim, int max_pages) {
   const size_t heads = (size_t)batch * n_head;
@@ -666,16 +843,15 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   const size_t need = pt_llama_step_workspace_bytes(a->batch, a->n_head, a->head_dim, a->max_pages);
   PT_REQUIRE(a->workspace_bytes >= need, "pt_llama_decode_step: workspace needs %zu bytes, got %zu", need, a->workspace_bytes);
 
-  static int n_sm = 0;
+  int n_sm = 0;
+  if (int rc = mk_sm_count(&n_sm)) return rc;
   static size_t smem_max = 0;
-  if (n_sm == 0) {
-    int dev = 0;
+  if (smem_max == 0) {
+    int dev = 0, v = 0;
     PT_CUDA(cudaGetDevice(&dev));
-    cudaDeviceProp prop;
-    PT_CUDA(cudaGetDeviceProperties(&prop, dev));
-    n_sm = prop.multiProcessorCount;
-    smem_max = prop.sharedMemPerBlockOptin;
-    PT_CUDA(cudaFuncSetAttribute(mk::llama_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+    PT_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    PT_CUDA(cudaFuncSetAttribute(mk::llama_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
+    smem_max = (size_t)v;
   }
   PT_REQUIRE(n_sm <= 256, "pt_llama_decode_step: %d SMs exceed the candidate buffer", n_sm);
 
@@ -689,6 +865,8 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   p.ids = a->ids; p.step = a->step_dev; p.stop_mask = a->stop_mask; p.next_ids = a->next_ids; p.page_table = a->page_table;
   p.x = (__half *)a->x; p.qkv = (__half *)a->qkv; p.attn = (__half *)a->attn; p.act = (__half *)a->act; p.logits = (__half *)a->logits;
   p.error_flag = a->error_flag;
+  p.trace = (unsigned long long *)a->trace;
+  p.debug = a->debug;
   auto al = [](size_t v) { return (v + 255) / 256 * 256; };
   const size_t heads = (size_t)a->batch * a->n_head;
   char *ws = (char *)a->workspace;

@@ -173,6 +173,18 @@ class LlamaDecoder:
         self.persistent = can_persist if persistent is None else (persistent and can_persist)
         if self.persistent:
             L = ops._lib.lib()
+
+            def to_stream(pl):
+                """Packed tiles -> the order in which each SM's consumer warps read them (the per-op kernels cannot use it)."""
+                out = torch.empty_like(pl.packed_w)
+                ops.check(L.pt_llama_stream_permute(pl.wfmt, ops._ptr(pl.packed_w), ops._ptr(out), pl.n_out, pl.k_in, ops._stream()),
+                          "pt_llama_stream_permute")
+                pl.packed_w = out
+
+            for lay in self.layers:
+                for k in ("qkv", "o", "gu", "down"):
+                    to_stream(lay[k])
+            to_stream(self.head)
             arr = (ops._lib.LlamaLayer * c.n_layer)()
             for i, lay in enumerate(self.layers):
                 arr[i].qkv, arr[i].o = lay["qkv"].packed_w.data_ptr(), lay["o"].packed_w.data_ptr()
