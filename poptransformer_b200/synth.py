@@ -13,7 +13,8 @@ def _normal(shape, gen, device, std=0.02):
 
 def llama_state_dict(n_layer, d_model, n_head, ffn, vocab, seed=0, device="cpu", int4_group=0):
     """Llama-2 architecture, weights ~ N(0, 0.02) fp16, RMSNorm weights 1 + N(0, 0.02).
-    int4_group > 0 quantises every transformer linear (not the embedding / LM head)."""
+    int4_group > 0 quantises every transformer linear (not the embedding / LM head) with that scale group along the input
+    features; int4_group = -1 uses one scale per output channel (group = in_features), the reference's checkpoint format."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     sd = {}
@@ -21,7 +22,7 @@ def llama_state_dict(n_layer, d_model, n_head, ffn, vocab, seed=0, device="cpu",
     def lin(key, out_f, in_f):
         w = _normal((out_f, in_f), gen, device)
         if int4_group:
-            sd[key], sd[key + "_scale"] = quantize_int4(w, int4_group)
+            sd[key], sd[key + "_scale"] = quantize_int4(w, in_f if int4_group < 0 else int4_group)
         else:
             sd[key] = w
 

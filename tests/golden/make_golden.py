@@ -1,0 +1,82 @@
+"""Generates the golden vectors that pin the oracle to the reference's own model code.
+
+Runs the UNMODIFIED reference graph builders (poptransformer/models/llama2, layers, ops, utils from the reference
+checkout) through the numpy stand-in for `popart` in oracle/popart_cpu, on seeded synthetic checkpoints, and stores the
+inputs' seeds and the resulting id containers.  Only usable where the reference tree is available (the development
+container); the fixtures it writes (tests/golden/*.npz) travel with the repository.
+
+    python tests/golden/make_golden.py [/path/to/reference]
+"""
+import logging
+import os
+import subprocess
+import sys
+import tempfile
+import types
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+sys.path[:0] = [ROOT, os.path.join(ROOT, "oracle", "popart_cpu"), REF]
+
+CASES = {
+    # name: (dims, precision, int4 group (0 = fp16), batch, max_len, prompt_len, seed)
+    "llama_tiny_fp16": (dict(n_layer=2, d_model=256, n_head=2, ffn=512, vocab=1000), "fp16", 0, 2, 40, 6, 11),
+    "llama_tiny_int4": (dict(n_layer=2, d_model=256, n_head=2, ffn=512, vocab=1000), "int4", -1, 1, 40, 6, 12),
+    "llama_small_int4": (dict(n_layer=3, d_model=512, n_head=4, ffn=1024, vocab=2000), "int4", -1, 2, 72, 10, 13),
+}
+
+
+def run_case(name):
+    """Each case runs in a fresh interpreter: the reference keeps its graph and settings in a process-global registry."""
+    dims, precision, group, batch, max_len, prompt, seed = CASES[name]
+    import popart                                       # the numpy stand-in
+    from poptransformer_b200 import synth
+    # the reference loads '../../custom_ops.so' relative to the working directory at import time (ops/customized.py:17-18)
+    tmp = tempfile.mkdtemp()
+    os.makedirs(os.path.join(tmp, "examples", "llama2"))
+    from oracle import c_ref
+    os.symlink(c_ref.build(), os.path.join(tmp, "custom_ops.so"))
+    os.chdir(os.path.join(tmp, "examples", "llama2"))
+
+    from poptransformer.utils.registry import REGISTRY
+    from poptransformer.utils.tensor_type import TensorType
+    for k, v in dict(num_replicas=1, batch_size=batch, batch_per_step=1, model_type="shard", enable_pipeline=False, precision=precision).items():
+        REGISTRY.register(k, v)
+    REGISTRY.register("tensor_type", TensorType(precision))
+    REGISTRY.register("logger", logging.getLogger("poptransformer"))
+    from poptransformer.models.llama2.model import LLAMA2DecModel
+
+    pad_id = dims["vocab"] - 1
+    sd = synth.llama_state_dict(**dims, seed=seed, device="cpu", int4_group=group)
+    if group:   # the reference's int4 checkpoints carry one scale per output channel, shape [out]
+        sd = {k: (v.reshape(-1) if k.endswith("_scale") else v) for k, v in sd.items()}
+
+    class GoldenLlama(LLAMA2DecModel):
+        def prepare_state_dict(self):
+            self.hf_tokenizer = types.SimpleNamespace(pad_token_id=pad_id, eos_token_id=pad_id - 1)
+            self.hf_config = types.SimpleNamespace(vocab_size=dims["vocab"], hidden_size=dims["d_model"], rms_norm_eps=1e-5,
+                                                   num_attention_heads=dims["n_head"], intermediate_size=dims["ffn"],
+                                                   num_hidden_layers=dims["n_layer"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+            self.state_dict = sd
+            self.register_state_dict()
+
+    model = GoldenLlama(max_length=max_len, max_loop=max_len - 1, layer_per_ipu=[dims["n_layer"]], early_stop=False)
+    model.build_graph()
+    ids = synth.prompt_ids(batch, prompt, max_len, dims["vocab"], pad_id, seed=seed).numpy()
+    env = popart.run_graph(model.graph, {"input_ids": ids})
+    out_ids, out_step = env["Loop:0"], env["Loop:1"]
+    os.chdir(ROOT)
+    np.savez(os.path.join(ROOT, "tests", "golden", name + ".npz"), input_ids=ids, output_ids=np.asarray(out_ids, dtype=np.int32),
+             step=np.asarray(out_step, dtype=np.int32), dims=np.array([dims[k] for k in ("n_layer", "d_model", "n_head", "ffn", "vocab")]),
+             group=group, batch=batch, max_len=max_len, prompt=prompt, seed=seed, pad_id=pad_id, n_nodes=len(model.graph.nodes))
+    print(name, "ok: step", out_step, "ids[0, :12]", np.asarray(out_ids)[0, :12])
+
+
+if __name__ == "__main__":
+    if len(sys.argv) > 2:
+        run_case(sys.argv[2])
+    else:
+        for case in CASES:
+            subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)
