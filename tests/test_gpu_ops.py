@@ -189,8 +189,8 @@ def test_norm_ce(cuda, rows, dim):
         found = False
         for dm in (0, 1, -1):
             for dr in (0, 1, -1):
-                m = (m0.view(np.uint16) + np.uint16(dm)).view(np.float16) if dm else m0
-                r = (r0.view(np.uint16) + np.uint16(dr)).view(np.float16) if dr else r0
+                m = np.array(int(m0.view(np.uint16)) + dm, dtype=np.uint16).view(np.float16)[()] if dm else m0
+                r = np.array(int(r0.view(np.uint16)) + dr, dtype=np.uint16).view(np.float16)[()] if dr else r0
                 t = (xf[row] - np.float32(m)).astype(np.float16)
                 t = (t.astype(np.float32) * np.float32(r)).astype(np.float16)
                 t = (t.astype(np.float32) * g.astype(np.float32)).astype(np.float16)
