@@ -45,27 +45,7 @@ def rope_tables(max_len, head_dim, device):
     return torch.from_numpy(sin).to(device), torch.from_numpy(cos).to(device)
 
 
-def _rows(t, r, n):
-    """'start' strategy: split the output features (rows of the [out, in] matrix)."""
-    per = t.shape[0] // n
-    if per * n != t.shape[0]:
-        raise ops.PtError(f"out_features={t.shape[0]} not divisible by tp={n}")
-    return t[r * per:(r + 1) * per]
-
-
-class _KSlice:
-    """'end' strategy: split the input features.  For INT4 group scales the rank's k-range [k0, k1) is widened
-    to group boundaries [a0, a1); weights outside [k0, k1) are zero nibbles, and the producer of the activation
-    writes at column offset k0 - a0 of a zero-initialised buffer of width a1 - a0."""
-
-    def __init__(self, k_total, r, n, align):
-        per = k_total // n
-        if per * n != k_total:
-            raise ops.PtError(f"in_features={k_total} not divisible by tp={n}")
-        self.k0, self.k1 = r * per, (r + 1) * per
-        self.a0 = (self.k0 // align) * align
-        self.a1 = -(-self.k1 // align) * align
-        self.offset, self.width = self.k0 - self.a0, self.a1 - self.a0
+from .tp import KSlice as _KSlice, rows as _rows, row_parallel_int4, row_parallel_fp16  # noqa: E402
 
 
 class LlamaDecoder:
@@ -99,20 +79,9 @@ class LlamaDecoder:
         def row_parallel(key, k_total):
             w = t(key)
             if w.dtype == torch.int8:
-                sc = t(key + "_scale").reshape(w.shape[0], -1)
-                grp = k_total // sc.shape[1]
-                ks = _KSlice(k_total, r, tp, max(grp, 128) if grp < k_total else 128)
-                if grp == k_total:                      # one scale per output row: any 128-aligned window works
-                    loc_s, grp_loc = sc, ks.width
-                else:
-                    loc_s, grp_loc = sc[:, ks.a0 // grp: ks.a1 // grp], grp
-                loc = w[:, ks.a0 // 2: ks.a1 // 2].clone()
-                loc[:, : ks.offset // 2] = 0            # nibble pairs outside the rank's range contribute exactly 0
-                loc[:, (ks.k1 - ks.a0) // 2:] = 0
-                return ops.PackedLinear(ops.W_INT4, loc.contiguous(), loc_s.contiguous(), group=grp_loc), ks
-            ks = _KSlice(k_total, r, tp, 32)
-            loc = torch.zeros((w.shape[0], ks.width), dtype=torch.float16, device=dev)
-            loc[:, ks.offset: ks.offset + (ks.k1 - ks.k0)] = w[:, ks.k0: ks.k1]
+                loc, loc_s, grp_loc, ks = row_parallel_int4(w, t(key + "_scale").reshape(w.shape[0], -1), k_total, r, tp)
+                return ops.PackedLinear(ops.W_INT4, loc, loc_s, group=grp_loc), ks
+            loc, ks = row_parallel_fp16(w, k_total, r, tp)
             return ops.PackedLinear(ops.W_FP16, loc), ks
 
         self.emb = t("model.embed_tokens.weight").to(torch.float16).contiguous()   # replicated: one row is read per token
