@@ -113,6 +113,21 @@ typedef struct pt_linear_args {
 size_t pt_linear_workspace_bytes(int batch, int n_out, int max_ksplit);
 int pt_linear(const pt_linear_args *args, void *stream);
 
+/* pt_linear without any device allocation on the caller's side (no counterpart in the reference, whose ops get their
+ * temporaries from the Poplar graph compiler).  Some hosts of this library cannot call cudaMalloc at the point where
+ * they run a linear layer: a plugin loaded into a serving process whose memory pool is owned and sized by that process,
+ * or a callback that runs inside a region where allocating is forbidden.  For them the split-k scratch (partial sums +
+ * arrival counters) lives in a 4 MiB array inside the library image, one copy per GPU that loads the library, held until
+ * the process exits.  `args->workspace` and `args->workspace_bytes` are ignored; x, weights and out are still the caller's.
+ *   - Shapes whose scratch need exceeds 4 MiB are rejected with PT_ERR_INVALID (pt_last_error() names the need); use
+ *     pt_linear with a workspace of your own for those.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *     before any stream capture begins.  Later calls only enqueue a small memset of the counters and the kernel.
+ *   - Every call on a device shares the one array: calls that can overlap on the GPU (different streams without an
+ *     ordering between them) race on it.  Serialise them on one stream or order them with events.
+ *   - Nothing is allocated or freed, by this call or on its behalf. */
+int pt_linear_static_scratch(const pt_linear_args *args, void *stream);
+
 /* ---- norms ------------------------------------------------------------------------
  * pt_norm_ce replaces the `NormCE` custom op (customized.py:69-102; custom_ops/NormCE.cpp:534-610):
  * fp16 rows, LayerNorm over `dim`; rows == 1 takes the GetInPlaceNorm arithmetic

@@ -60,6 +60,7 @@ SIGNATURES = {
     "pt_linear_repack": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "pt_linear": (c_int, [ctypes.POINTER(LinearArgs), c_void_p]),
+    "pt_linear_static_scratch": (c_int, [ctypes.POINTER(LinearArgs), c_void_p]),
     "pt_norm_ce": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
     "pt_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "pt_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),

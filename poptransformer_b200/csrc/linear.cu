@@ -533,3 +533,53 @@ extern "C" int pt_linear(const pt_linear_args *a, void *stream) {
     default: return dispatch_nb<PT_W_FP8>(p, smem, st);
   }
 }
+
+// ------------------------------------------------------------------------------------------ no-allocation variant
+// Split-k scratch that lives in the library image: 4 MiB per GPU that loads the library, held until the process exits.
+namespace {
+constexpr size_t kStaticWsBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_linear_static_ws[kStaticWsBytes];
+}  // namespace
+
+// pt_linear for callers that have no way to obtain device scratch memory (see include/pt_b200.h).
+// The name g_linear_static_ws is only a host-side handle here; the device address is fetched once per device with
+// cudaGetSymbolAddress (with that device current) and cached.
+extern "C" int pt_linear_static_scratch(const pt_linear_args *a, void *stream) {
+  PT_REQUIRE(a, "pt_linear_static_scratch: null args");
+  int dev = -1;
+  PT_CUDA(cudaGetDevice(&dev));
+  PT_REQUIRE(dev >= 0 && dev < 64, "pt_linear_static_scratch: device ordinal %d outside 0..63", dev);
+  static void *ws_of_device[64] = {};
+  if (!ws_of_device[dev]) {  // first call on this device: resolve the array's device address
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_linear_static_ws);
+    if (e != cudaSuccess || !ptr) return pt::set_error(PT_ERR_CUDA, "pt_linear_static_scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    ws_of_device[dev] = ptr;
+  }
+  const int ck = chunk_k(a->wfmt == PT_W_INT4 || a->wfmt == PT_W_FP16 || a->wfmt == PT_W_FP8 ? a->wfmt : PT_W_FP16);
+  PT_REQUIRE(a->batch >= 1 && a->n_out > 0 && a->k_in > 0 && a->k_in % ck == 0, "pt_linear_static_scratch: bad shape batch=%d n_out=%d k_in=%d",
+             a->batch, a->n_out, a->k_in);
+  // Fix the k-split here (same rule as pt_linear's default) so that the scratch need is known before the launch.
+  const int n_rt = ceil_div(a->n_out, 16), nchunks = a->k_in / ck;
+  int ksplit = a->ksplit;
+  if (ksplit <= 0) {
+    ksplit = std::max(1, (148 * 24) / n_rt);
+    ksplit = std::max(1, std::min(ksplit, nchunks / 4));
+  }
+  ksplit = std::max(1, std::min(ksplit, nchunks));
+  const size_t need = ksplit > 1 ? pt_linear_workspace_bytes(a->batch, a->n_out, ksplit) : 0;
+  PT_REQUIRE(need <= kStaticWsBytes,
+             "pt_linear_static_scratch: batch=%d n_out=%d k-split=%d needs %zu bytes of scratch, the built-in scratch holds %zu; use pt_linear "
+             "with a caller-provided workspace",
+             a->batch, a->n_out, ksplit, need, (size_t)kStaticWsBytes);
+  pt_linear_args b = *a;
+  b.ksplit = ksplit;
+  b.workspace = ws_of_device[dev];
+  b.workspace_bytes = kStaticWsBytes;
+  if (ksplit > 1) {
+    // The array keeps whatever the previous call left; the arrival counters at its start must be zero.
+    const size_t counters = ((size_t)ceil_div(n_rt, kWarps) * sizeof(int) + 255) / 256 * 256;
+    PT_CUDA(cudaMemsetAsync(ws_of_device[dev], 0, counters, as_stream(stream)));
+  }
+  return pt_linear(&b, stream);
+}
