@@ -38,9 +38,9 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 #ifdef __CUDACC__
 // ---- fp16 arithmetic with the reference's "one rounding per op" semantics -------------
-__device__ __forceinline__ __half h_mul(__half a, __half b) { return __hmul(a, b); }
-__device__ __forceinline__ __half h_add(__half a, __half b) { return __hadd(a, b); }
-__device__ __forceinline__ __half h_sub(__half a, __half b) { return __hsub(a, b); }
+__device__ __forceinline__ __half h_mul(__half a, __half b) { return __hmul_rn(a, b); }
+__device__ __forceinline__ __half h_add(__half a, __half b) { return __hadd_rn(a, b); }
+__device__ __forceinline__ __half h_sub(__half a, __half b) { return __hsub_rn(a, b); }
 
 // swish as the oracle defines it: x * sigmoid(x) in float32, one rounding to fp16.
 __device__ __forceinline__ __half swish_h(__half x) {

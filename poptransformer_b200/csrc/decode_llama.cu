@@ -92,11 +92,15 @@ __device__ __forceinline__ unsigned long long gtime() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 
 struct Shared {           // fixed-size part, placed after the ring / activations
-  float red[NCW][2][32][4];  // per warp: partial sums of the first / last row tile of its tile range
-  float corr[96][8];      // [chunk][batch column], up to 96 chunks of 128 k
+  float red[NCW][2][32][2];  // per warp: partial sums of the first / last row tile of its tile range
+  int4 corr[96][BMAX];    // [chunk][batch]: C-fragment initialiser {-8 sum(t1), -8 sum(t2)} x 2 rows, up to 96 chunks of 128 k
+  float xscale[96][BMAX]; // [chunk][batch]: activation scale of the chunk / 16
+  uint4 zeros[2];         // what lanes without a batch column read as their B operand / C initialiser
   __half qs[MAXU][H], newk[MAXU][H], newv[MAXU][H];
   float ps[NGRP][PAGE];   // one row per 4-warp attention group
   float ml[NGRP][2];
@@ -116,13 +120,16 @@ struct Ctx {
   int sm, G, step;
   unsigned *bar_ctr;
   unsigned bar_target;
-  uint32_t gs;  // global stage counter (same sequence in producer and consumers)
+  uint32_t slot, par;  // ring slot and mbarrier parity of the next stage (same sequence in producer and consumers)
+  __device__ __forceinline__ void advance() {
+    if (++slot == (uint32_t)p.ns) { slot = 0; par ^= 1u; }
+  }
   unsigned long long *tr;  // optional fine-grained stamps of the current layer
 };
 
 // Grid barrier over all blocks (consumer threads only).  Bounded: on time-out the error flag is set and the block
 // stops doing work (every later wait is bounded too), so the kernel always terminates.
-__device__ void grid_sync(Ctx &c) {
+__device__ __forceinline__ void grid_sync(Ctx &c) {
   const int tid = threadIdx.x;
   c.bar_target += c.G;
   consumer_sync();
@@ -167,10 +174,17 @@ __device__ __forceinline__ Gamma load_gamma(const __half *gamma, int K) {
 }
 
 // Stage activations src[B, K] (global, written by other SMs: read through L2) into shared memory for the next linear phase.
-// INT4 phases use the per-chunk swizzle of linear.cu ([chunk][w][tig] 16-byte units) and produce the offset corrections;
-// the fp16 phase (LM head) keeps the natural order.  gamma != nullptr applies RMSNorm first (weights in `gm`).
+// gamma != nullptr applies RMSNorm first (weights in `gm`), with the reference's fp16 roundings.
+//
+// INT4 phases multiply on the integer tensor-core path (u8 x s8 -> s32), so the fp16 activations of every 128-k chunk are
+// turned into 16-bit block fixed point here: T = round(x * 32000 / max|x| of the chunk), split into two signed bytes
+// T = 256 t1 + t2.  t1 and t2 become two columns of the mma's B operand (batch b -> columns 2b and 2b + 1), stored in the
+// order in which a lane needs them: [chunk][column][tig][32 bytes].  The quantisation step is 2^-5 of an fp16 ulp of the
+// chunk's largest element, so the product differs from the exact fp16 x int4 dot product by far less than the final fp16
+// rounding.  The weights stay offset-binary nibbles u = q + 8; sum(q T) = sum(u T) - 8 sum(T) and the second term goes
+// into the accumulator's initial value (corr).  The fp16 phase (LM head) keeps x as fp16 in natural order.
 template <bool INT4>
-__device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma, const Gamma &gm) {
+__device__ __forceinline__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma, const Gamma &gm) {
   const Params &p = c.p;
   const int tid = threadIdx.x;
   const int units = K / 8;
@@ -180,7 +194,6 @@ __device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma, c
 #pragma unroll
     for (int q = 0; q < 3; ++q) v[q] = (tid + q * NCT < units) ? __ldcg(xr + tid + q * NCT) : make_uint4(0, 0, 0, 0);
     __half rb = __half(0);
-    if (c.tr && tid == 0 && b == 0) { c.tr[13] = gtime(); c.tr[14] = (unsigned long long)(v[0].x); c.tr[14] = gtime(); }
     if (gamma) {
       float ss = 0.f;
 #pragma unroll
@@ -194,10 +207,10 @@ __device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma, c
       }
       ss = consumer_sum(c, ss);
       rb = __float2half_rn(1.0f / sqrtf(ss / (float)K + p.eps));
-      if (c.tr && tid == 0 && b == 0) c.tr[15] = gtime();
     }
 #pragma unroll
     for (int q = 0; q < 3; ++q) {
+      if (q * NCT >= units) break;  // uniform: nothing left for any thread
       const int u = tid + q * NCT;
       const bool valid = u < units;
       __half *h = reinterpret_cast<__half *>(&v[q]);
@@ -207,21 +220,42 @@ __device__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma, c
         for (int j = 0; j < 8; ++j) h[j] = h_mul(h_mul(h[j], rb), gh[j]);
       }
       if (INT4) {
-        // units of one 128-k chunk are 16 consecutive u, i.e. 16 consecutive lanes
-        float sa = 0.f, sb = 0.f;
-        if (valid) {
-          sa = (__half2float(h[0]) + __half2float(h[1])) + (__half2float(h[4]) + __half2float(h[5]));
-          sb = (__half2float(h[2]) + __half2float(h[3])) + (__half2float(h[6]) + __half2float(h[7]));
-        }
+        // the 16 units of one 128-k chunk are 16 consecutive u, i.e. one half-warp (invalid units hold zeros)
+        const uint32_t *hw = reinterpret_cast<const uint32_t *>(&v[q]);
+        __half2 mx = __hmax2(__hmax2(u32_as_h2(hw[0] & 0x7FFF7FFFu), u32_as_h2(hw[1] & 0x7FFF7FFFu)),
+                             __hmax2(u32_as_h2(hw[2] & 0x7FFF7FFFu), u32_as_h2(hw[3] & 0x7FFF7FFFu)));
 #pragma unroll
-        for (int o = 1; o < 16; o <<= 1) {
-          sa += __shfl_xor_sync(0xffffffffu, sa, o);
-          sb += __shfl_xor_sync(0xffffffffu, sb, o);
+        for (int o = 1; o < 16; o <<= 1) mx = __hmax2(mx, u32_as_h2(__shfl_xor_sync(0xffffffffu, h2_as_u32(mx), o)));
+        const float amax = fmaxf(__low2float(mx), __high2float(mx));
+        const float inv = amax > 0.f ? 32000.0f / amax : 0.f;
+        // U = T + 128 as 16-bit halves of four registers: t1 = high byte of U, t2 = low byte of U xor 0x80
+        uint32_t U[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(u32_as_h2(hw[j]));
+          const int lo = __float2int_rn(fmaf(f.x, inv, 128.0f)), hi = __float2int_rn(fmaf(f.y, inv, 128.0f));
+          U[j] = __byte_perm((uint32_t)lo, (uint32_t)hi, 0x5410);
         }
+        // bytes in the order of the packed weight word: k offsets (0,4,1,5) sit in the low nibbles of its bytes 0..3 and
+        // (2,6,3,7) in the high nibbles
+        const uint32_t t1a = __byte_perm(U[0], U[2], 0x7351), t1b = __byte_perm(U[1], U[3], 0x7351);
+        const uint32_t t2a = __byte_perm(U[0], U[2], 0x6240) ^ 0x80808080u, t2b = __byte_perm(U[1], U[3], 0x6240) ^ 0x80808080u;
+        int s12 = __dp4a((int)t1a, 0x01010101, __dp4a((int)t1b, 0x01010101, 0)) * 65536 + __dp4a((int)t2a, 0x01010101, __dp4a((int)t2b, 0x01010101, 0));
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) s12 += __shfl_xor_sync(0xffffffffu, s12, o);
         if (valid) {
-          const int chunk = u >> 4, r = u & 15, t4 = r >> 2, w = r & 3;
-          *reinterpret_cast<uint4 *>(c.xs + (size_t)b * p.xs_stride + chunk * 256 + w * 64 + t4 * 16) = v[q];
-          if (r == 0) c.sh->corr[chunk][b] = kOffA * sa + kOffB * sb;
+          // words (0,1) of a lane feed its first mma pair, words (2,3) the second; see linear_phase
+          const int chunk = u >> 4, r = u & 15, tk = r >> 2, w = r & 3;
+          unsigned char *base = c.xs + (size_t)chunk * (p.B * 256) + (size_t)b * 256 + tk * 32 + ((w >> 1) * 4 + (w & 1)) * 4;
+          *reinterpret_cast<uint32_t *>(base) = t1a;            // column 2b (t1): low-nibble operand
+          *reinterpret_cast<uint32_t *>(base + 8) = t1b;        //                  high-nibble operand
+          *reinterpret_cast<uint32_t *>(base + 128) = t2a;      // column 2b + 1 (t2)
+          *reinterpret_cast<uint32_t *>(base + 136) = t2b;
+          if (r == 0) {
+            const int s2 = (int)(short)(s12 & 0xFFFF), s1 = (s12 - s2) >> 16;
+            c.sh->corr[chunk][b] = make_int4(-8 * s1, -8 * s2, -8 * s1, -8 * s2);
+            c.sh->xscale[chunk][b] = amax * (1.0f / (32000.0f * 16.0f));
+          }
         }
       } else if (valid) {
         *reinterpret_cast<uint4 *>(c.xs + (size_t)b * p.xs_stride + u * 16) = v[q];
@@ -251,46 +285,57 @@ struct Split {
   __device__ __forceinline__ int stages() const { return base + (rem ? 1 : 0); }
 };
 
-template <int EPI>
-__device__ __forceinline__ void tile_epilogue(const Params &p, const float (&v)[4], int rt, int lane, __half *out, int N, Best *best) {
-  const int g = lane >> 2, tig = lane & 3;
-  if (tig != 0) return;  // batch columns 0 and 1 live in the tig == 0 lanes
+// Finished sums of one row tile: lane (g, tig) with tig < B holds batch tig, rows g (lo) and g + 8 (hi) of the tile.
+template <bool HEAD>
+__device__ __forceinline__ void tile_epilogue(const Params &p, int epi, float lo, float hi, int rt, int lane, __half *out, int N, Best *best) {
+  const int g = lane >> 2, b = lane & 3;
+  if (b >= p.B) return;
+  if (!HEAD && epi == EPI_SWIGLU) {  // rows g / g + 8 are the gate / up feature rt * 8 + g
+    const int n = rt * 8 + g;
+    if (n < N / 2) out[(size_t)b * (N / 2) + n] = h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo)));
+    return;
+  }
 #pragma unroll
-  for (int jb = 0; jb < 2; ++jb) {
-    const int b = jb;
-    if (b >= p.B) continue;
-    const float lo = v[jb], hi = v[2 + jb];  // rows g and g + 8
-    if (EPI == EPI_SWIGLU) {
-      const int n = rt * 8 + g;
-      if (n < N / 2) out[(size_t)b * (N / 2) + n] = h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo)));
+  for (int hr = 0; hr < 2; ++hr) {
+    const int n = rt * 16 + g + 8 * hr;
+    if (n >= N) continue;
+    __half y = __float2half_rn(hr ? hi : lo);
+    if (HEAD) {
+      const float f = __half2float(y);
+      if (f > best->v[b] || (f == best->v[b] && n < best->i[b])) { best->v[b] = f; best->i[b] = n; }
+      if (out) out[(size_t)b * N + n] = y;
     } else {
-#pragma unroll
-      for (int hr = 0; hr < 2; ++hr) {
-        const int n = rt * 16 + g + 8 * hr;
-        if (n >= N) continue;
-        __half y = __float2half_rn(hr ? hi : lo);
-        if (EPI == EPI_RESID) y = h_add(__ldcg(out + (size_t)b * N + n), y);
-        if (EPI == EPI_HEAD) {
-          const float f = __half2float(y);
-          if (f > best->v[b] || (f == best->v[b] && n < best->i[b])) { best->v[b] = f; best->i[b] = n; }
-          if (out) out[(size_t)b * N + n] = y;
-        } else {
-          out[(size_t)b * N + n] = y;
-        }
-      }
+      if (epi == EPI_RESID) y = h_add(__ldcg(out + (size_t)b * N + n), y);
+      out[(size_t)b * N + n] = y;
     }
   }
 }
+
+__device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma0(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {  // d = a b
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// One tile in registers: the lane's 16 bytes of rows g (a) and g + 8 (b), and the two rows' group scales (INT4).
+struct TileRegs { uint4 a, b; uint32_t s; };
 
 // One linear phase over this SM's row tiles [r0, r1) of a matrix with `nchunks` tiles per row tile.  The SM's tiles arrive
 // in "stream order": stage j holds tile start(w) + j of every warp w that still has one (see pt_llama_stream_permute), so
 // each warp accumulates a contiguous run of chunks in registers and there is no synchronisation inside the phase.  Row
 // tiles that are split between warps are summed after one barrier, in warp order (deterministic).
-template <int WFMT, int EPI>
-__device__ void linear_phase(Ctx &c, int n_rt, int nchunks, __half *out, int N, Best *best) {
+// The loop body is what bounds the kernel once the stream flows, so it is kept to the instructions that the arithmetic
+// needs: two AND per packed word and one integer mma per 512 weights (INT4), operands and accumulator initialisers that
+// arrive from shared memory in fragment order, ring positions advanced without divisions.
+template <int WFMT>
+__device__ __forceinline__ void linear_phase(Ctx &c, int epi, int n_rt, int nchunks, __half *out, int N, Best *best) {
   constexpr int TILE = WTraits<WFMT>::kTileBytes;
-  constexpr int UNITS = WTraits<WFMT>::kUnits;
-  constexpr int CHUNK_X_BYTES = WTraits<WFMT>::kChunkK * 2;
+  constexpr bool I4 = (WFMT == PT_W_INT4);
   const Params &p = c.p;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   const int r0 = (int)((long long)c.sm * n_rt / c.G), r1 = (int)((long long)(c.sm + 1) * n_rt / c.G);
@@ -300,75 +345,95 @@ __device__ void linear_phase(Ctx &c, int n_rt, int nchunks, __half *out, int N, 
   const int first_rt = start / nchunks;
   int rt = first_rt, ch = start - first_rt * nchunks;
   const int ch_first = ch;  // chunk at which this warp enters its first row tile
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc0 = 0.f, acc1 = 0.f;
   const uint32_t ring_s = smem_addr(c.ring) + warp * TILE + lane * 16;
-  const uint32_t xs_s = smem_addr(c.xs) + tig * 16 + g * p.xs_stride;
-  const uint32_t corr_s = smem_addr(&c.sh->corr[0][0]) + 8 * tig;
+  const uint32_t full_s = smem_addr(&c.sh->full[0]), empty_s = smem_addr(&c.sh->empty[0]);
+  const uint32_t zero_s = smem_addr(&c.sh->zeros[0]);
+  // per-lane operand addresses: base + chunk * stride, with stride 0 and the zero block for lanes that carry no batch column
+  uint32_t x_s, x_cs, corr_s, corr_cs, xsc_s;
+  if (I4) {
+    const bool has = g < 2 * p.B;
+    x_s = has ? smem_addr(c.xs) + g * 128 + tig * 32 : zero_s;
+    x_cs = has ? p.B * 256 : 0;
+    corr_s = tig < p.B ? smem_addr(&c.sh->corr[0][tig]) : zero_s;
+    corr_cs = tig < p.B ? (uint32_t)sizeof(int4) * BMAX : 0;
+    xsc_s = smem_addr(&c.sh->xscale[0][tig < p.B ? tig : 0]);
+  } else {
+    const bool has = !(g & 1) && (g >> 1) < p.B;   // batch b sits in column 2b, so that lane tig = b ends up with its sums
+    x_s = has ? smem_addr(c.xs) + (g >> 1) * p.xs_stride + tig * 16 : zero_s;
+    x_cs = has ? 64 : 0;
+    corr_s = corr_cs = xsc_s = 0;
+  }
 
-  auto store_partial = [&](int slot) {
-    *reinterpret_cast<float4 *>(&c.sh->red[warp][slot][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-  };
+  auto store_partial = [&](int slot) { *reinterpret_cast<float2 *>(&c.sh->red[warp][slot][lane][0]) = make_float2(acc0, acc1); };
 
-  // Software pipeline: the tile of stage j + 1 is pulled into registers (and its stage released to the producer) before
-  // the tile of stage j is multiplied, so the registers act as one more ring stage and refills start earlier.
-  uint4 va = make_uint4(0, 0, 0, 0), vb = va, na = va, nb = va;
-  float2 sf = make_float2(1.f, 1.f), nsf = sf;
-  auto fetch = [&](int j, uint4 &a4, uint4 &b4, float2 &s2) {  // stage j of this phase (global stage c.gs) -> registers
-    const int slot = c.gs % p.ns;
-    const bool got = mbar_wait(smem_addr(&c.sh->full[slot]), (c.gs / p.ns) & 1, &c.sh->abort);
+  // stage j of this phase -> registers; the stage is handed back to the producer as soon as the loads are issued
+  auto fetch = [&](int j, TileRegs &t) {
+    const bool got = mbar_wait(full_s + c.slot * 8, c.par, &c.sh->abort);
     if (!got) {
       c.sh->abort = 1;
       if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 4);
     }
     if (j < len && got) {
-      const uint32_t t_s = ring_s + slot * STAGE_BYTES;
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a4.x), "=r"(a4.y), "=r"(a4.z), "=r"(a4.w) : "r"(t_s));
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b4.x), "=r"(b4.y), "=r"(b4.z), "=r"(b4.w) : "r"(t_s + 512));
-      if (WFMT == PT_W_INT4) {
-        uint32_t sraw;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sraw) : "r"(t_s - lane * 16 + 1024 + g * 4));
-        s2 = __half22float2(*reinterpret_cast<__half2 *>(&sraw));
-      }
+      const uint32_t t_s = ring_s + c.slot * STAGE_BYTES;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.a.x), "=r"(t.a.y), "=r"(t.a.z), "=r"(t.a.w) : "r"(t_s));
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.b.x), "=r"(t.b.y), "=r"(t.b.z), "=r"(t.b.w) : "r"(t_s + 512));
+      if (I4) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(t.s) : "r"(t_s - lane * 16 + 1024 + g * 4));
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(smem_addr(&c.sh->empty[slot]));  // this warp's tile is in registers
-    ++c.gs;
+    if (lane == 0) mbar_arrive(empty_s + c.slot * 8);  // this warp's tile is in registers
+    c.advance();
   };
-  if (nstages > 0) fetch(0, va, vb, sf);
-  for (int j = 0; j < nstages; ++j) {
-    if (j + 1 < nstages) fetch(j + 1, na, nb, nsf);
-    if (j < len && !(p.debug & 1)) {
-      float cc[4] = {0.f, 0.f, 0.f, 0.f};
-      const uint32_t x_s = xs_s + ch * CHUNK_X_BYTES;
-#pragma unroll
-      for (int u = 0; u < UNITS; ++u) {
-        uint32_t fa[4], fb[4];
-        expand8<WFMT>(va, u, fa);
-        expand8<WFMT>(vb, u, fb);
-        uint4 xv = make_uint4(0, 0, 0, 0);
-        if (g < p.B) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w) : "r"(x_s + u * 64));
-        mma16816(cc, fa[0], fb[0], fa[1], fb[1], xv.x, xv.y);
-        mma16816(cc, fa[2], fb[2], fa[3], fb[3], xv.z, xv.w);
-      }
-      if (WFMT == PT_W_INT4) {
-        float2 co;
-        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(co.x), "=f"(co.y) : "r"(corr_s + ch * 32));
-        acc[0] += sf.x * (cc[0] - co.x);
-        acc[1] += sf.x * (cc[1] - co.y);
-        acc[2] += sf.y * (cc[2] - co.x);
-        acc[3] += sf.y * (cc[3] - co.y);
-      } else {
-        acc[0] += cc[0]; acc[1] += cc[1]; acc[2] += cc[2]; acc[3] += cc[3];
-      }
-      if (++ch == nchunks) {  // this warp reached the end of row tile rt
-        if (rt == first_rt && ch_first != 0) store_partial(0);                  // entered it midway: another warp holds the beginning
-        else tile_epilogue<EPI>(p, acc, r0 + rt, lane, out, N, best);           // had all of it
-        ch = 0;
-        ++rt;
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-      }
+
+  auto compute = [&](const TileRegs &t) {
+    if (p.debug & 1) return;
+    if (I4) {
+      constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u;
+      uint4 xa, xb;
+      int lo[4], hi[4];
+      float xs;
+      const uint32_t xaddr = x_s + ch * x_cs;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xa.x), "=r"(xa.y), "=r"(xa.z), "=r"(xa.w) : "r"(xaddr));
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xb.x), "=r"(xb.y), "=r"(xb.z), "=r"(xb.w) : "r"(xaddr + 16));
+      asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(lo[0]), "=r"(lo[1]), "=r"(lo[2]), "=r"(lo[3]) : "r"(corr_s + ch * corr_cs));
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xs) : "r"(xsc_s + ch * (uint32_t)(sizeof(float) * BMAX)));
+      imma0(hi, t.a.x & HI, t.b.x & HI, t.a.y & HI, t.b.y & HI, xa.z, xa.w);
+      imma(lo, t.a.x & LO, t.b.x & LO, t.a.y & LO, t.b.y & LO, xa.x, xa.y);
+      imma(hi, t.a.z & HI, t.b.z & HI, t.a.w & HI, t.b.w & HI, xb.z, xb.w);
+      imma(lo, t.a.z & LO, t.b.z & LO, t.a.w & LO, t.b.w & LO, xb.x, xb.y);
+      // value x 16 = 4096 lo(t1) + 16 lo(t2) + 256 hi(t1) + hi(t2); |.| < 2^31 for |t1| <= 125 (see stage_x)
+      const int v0 = ((lo[0] << 8) + lo[1]) * 16 + (hi[0] << 8) + hi[1];
+      const int v1 = ((lo[2] << 8) + lo[3]) * 16 + (hi[2] << 8) + hi[3];
+      const float2 sf = __half22float2(u32_as_h2(t.s));
+      acc0 = fmaf(sf.x * xs, (float)v0, acc0);
+      acc1 = fmaf(sf.y * xs, (float)v1, acc1);
+    } else {
+      uint4 xv;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w) : "r"(x_s + ch * x_cs));
+      float cc[4] = {acc0, 0.f, acc1, 0.f};
+      mma16816(cc, t.a.x, t.b.x, t.a.y, t.b.y, xv.x, xv.y);
+      mma16816(cc, t.a.z, t.b.z, t.a.w, t.b.w, xv.z, xv.w);
+      acc0 = cc[0];
+      acc1 = cc[2];
     }
-    va = na; vb = nb; sf = nsf;
+    if (++ch == nchunks) {  // this warp reached the end of row tile rt
+      if (rt == first_rt && ch_first != 0) store_partial(0);                                   // entered it midway: another warp holds the beginning
+      else tile_epilogue<!I4>(p, epi, acc0, acc1, r0 + rt, lane, out, N, best);              // had all of it
+      ch = 0;
+      ++rt;
+      acc0 = acc1 = 0.f;
+    }
+  };
+
+  // Two tiles in flight per warp: the tile of stage j + 1 is pulled into registers (and its stage released) before the
+  // tile of stage j is multiplied, so the registers act as one more ring stage and refills start earlier.
+  TileRegs ta, tb;
+  if (nstages > 0) fetch(0, ta);
+  for (int j = 0; j < nstages; j += 2) {
+    if (j + 1 < nstages) fetch(j + 1, tb);
+    if (j < len) compute(ta);
+    if (j + 2 < nstages) fetch(j + 2, ta);
+    if (j + 1 < len) compute(tb);
   }
   if (len > 0 && ch != 0) store_partial(rt == first_rt ? 0 : 1);  // the range ended inside a row tile
   consumer_sync();
@@ -377,13 +442,14 @@ __device__ void linear_phase(Ctx &c, int n_rt, int nchunks, __half *out, int N, 
     const int q0 = r * nchunks, q1 = q0 + nchunks - 1;
     const int w_lo = sp.owner(q0), w_hi = sp.owner(q1);
     if (w_lo == w_hi) continue;  // one warp had the whole row tile and already wrote it
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    float v0 = 0.f, v1 = 0.f;
     for (int w = w_lo; w <= w_hi; ++w) {
       const int s_w = (sp.start(w) / nchunks == r) ? 0 : 1;  // r is the first row tile of w's range, or its last
-      const float4 t = *reinterpret_cast<const float4 *>(&c.sh->red[w][s_w][lane][0]);
-      v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+      const float2 t = *reinterpret_cast<const float2 *>(&c.sh->red[w][s_w][lane][0]);
+      v0 += t.x;
+      v1 += t.y;
     }
-    tile_epilogue<EPI>(p, v, r0 + r, lane, out, N, best);
+    tile_epilogue<!I4>(p, epi, v0, v1, r0 + r, lane, out, N, best);
   }
 }
 
@@ -399,7 +465,7 @@ __device__ __forceinline__ void group_sync(int grp) { asm volatile("bar.sync %0,
 // one stage per unit that has cached tokens (K page at offset 0, V page at V_OFFSET).  The consumer warps form NGRP
 // groups of four warps; group q handles this SM's units q, q + NGRP, ... on its own (scores with 8 lanes per token, softmax
 // statistics by warp shuffles, P.V with one thread per channel), so units of an SM run concurrently.
-__device__ void attention_phase(Ctx &c, const pt_llama_layer &L) {
+__device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L) {
   const Params &p = c.p;
   Shared *sh = c.sh;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gt = tid & 127;
@@ -426,19 +492,16 @@ __device__ void attention_phase(Ctx &c, const pt_llama_layer &L) {
       }
     }
     consumer_sync();
-    // stage index of each unit of the pass (units without cached tokens have none)
-    uint32_t gs_unit[MAXU];
-    {
-      uint32_t g0 = c.gs;
-      for (int k = 0; k < nu; ++k) {
-        const int u = u0 + k * c.G;
-        const int pg = u % n_active;
-        const int n_valid = min(PAGE, step + 1 - pg * PAGE);
-        const int n_load = (pg == n_active - 1) ? n_valid - 1 : n_valid;
-        gs_unit[k] = g0;
-        if (n_load > 0) ++g0;
-      }
-      c.gs = g0;
+    // ring slot and parity of each unit of the pass (units without cached tokens have no stage)
+    unsigned char slot_unit[MAXU], par_unit[MAXU];
+    for (int k = 0; k < nu; ++k) {
+      const int u = u0 + k * c.G;
+      const int pg = u % n_active;
+      const int n_valid = min(PAGE, step + 1 - pg * PAGE);
+      const int n_load = (pg == n_active - 1) ? n_valid - 1 : n_valid;
+      slot_unit[k] = (unsigned char)c.slot;
+      par_unit[k] = (unsigned char)c.par;
+      if (n_load > 0) c.advance();
     }
     for (int k = 0; k < nu; ++k) {
       const int u = u0 + k * c.G;
@@ -446,18 +509,19 @@ __device__ void attention_phase(Ctx &c, const pt_llama_layer &L) {
       const int n_valid = min(PAGE, step + 1 - pg * PAGE);
       const bool owner = (pg == n_active - 1);
       const int n_load = owner ? n_valid - 1 : n_valid;
-      const int slot = gs_unit[k] % p.ns;
+      const int slot = slot_unit[k];
+      const uint32_t par = par_unit[k];
       if ((k % NGRP) != grp) {  // not this group's unit: release the stage at once
         if (n_load > 0 && lane == 0) {
           // the arrival only counts once the stage is full, so wait for it first (keeps phases aligned)
-          mbar_wait(smem_addr(&sh->full[slot]), (gs_unit[k] / p.ns) & 1, &sh->abort);
+          mbar_wait(smem_addr(&sh->full[slot]), par, &sh->abort);
           mbar_arrive(smem_addr(&sh->empty[slot]));
         }
         continue;
       }
       const __half *Ks = nullptr, *Vs = nullptr;
       if (n_load > 0) {
-        if (!mbar_wait(smem_addr(&sh->full[slot]), (gs_unit[k] / p.ns) & 1, &sh->abort)) {
+        if (!mbar_wait(smem_addr(&sh->full[slot]), par, &sh->abort)) {
           sh->abort = 1;
           if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 5);
         }
@@ -627,12 +691,14 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
       mbar_init(smem_addr(&sh->empty[s]), NCW);
     }
     sh->abort = 0;
+    sh->zeros[0] = sh->zeros[1] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
   const int n_rt_qkv = 3 * p.d / 16, n_rt_o = p.d / 16, n_rt_gu = 2 * p.ffn / 16, n_rt_head = (p.vocab + 15) / 16;
   const int nc_d = p.d / 128, nc_f = p.ffn / 128, nc_head = p.d / 32;
+  (void)nc_d; (void)nc_f;
 
   if (warp == NCW) {
     // ---------------- producer: one lane walks the whole step's weight / KV stream of this SM
@@ -655,7 +721,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   // Two barrier counters are used by alternate launches: word [2] says which one is this launch's (it is zero: the
   // previous launch cleared it when it finished); the last block clears the other one at the very end.
   const unsigned which = __ldcg(p.barrier + 2) & 1u;
-  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, nullptr};
+  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, 0u, nullptr};
 
   // embedding: every SM gathers the rows itself (no barrier needed); the copy in global memory serves the residual adds
   for (int i = tid; i < p.B * (p.d / 8); i += NCT) {
@@ -665,45 +731,41 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
     const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.emb + (size_t)id * p.d) + u);
     if ((u % c.G) == c.sm) reinterpret_cast<uint4 *>(p.x + (size_t)b * p.d)[u] = v;
   }
-  Gamma g1 = load_gamma((const __half *)p.layers[0].ln1, p.d);
-  const Gamma gnone = load_gamma(nullptr, 0);
+  Gamma gm = load_gamma((const __half *)p.layers[0].ln1, p.d);
   grid_sync(c);
 
+  // The four linear phases of a layer run through one copy of the staging and multiplication code (a loop with a table of
+  // operands), which keeps the kernel small enough for the instruction cache and lets the compiler inline everything.
   unsigned long long *tr = p.trace ? p.trace + ((size_t)blockIdx.x * p.n_layer) * 16 : nullptr;
 #define PT_STAMP(k) do { if (tr && tid == 0) tr[l * 16 + (k)] = gtime(); } while (0)
   for (int l = 0; l < p.n_layer; ++l) {
     const pt_llama_layer &L = p.layers[l];
     PT_STAMP(0);
-    c.tr = tr ? tr + l * 16 : nullptr;
-    stage_x<true>(c, p.x, p.d, (const __half *)L.ln1, g1);
-    c.tr = nullptr;
-    PT_STAMP(1);
-    linear_phase<PT_W_INT4, EPI_QKV>(c, n_rt_qkv, nc_d, p.qkv, 3 * p.d, nullptr);
-    PT_STAMP(2);
-    grid_sync(c);
-    PT_STAMP(3);
-    attention_phase(c, L);
-    PT_STAMP(4);
-    grid_sync(c);
-    PT_STAMP(5);
-    stage_x<true>(c, p.attn, p.d, nullptr, gnone);
-    linear_phase<PT_W_INT4, EPI_RESID>(c, n_rt_o, nc_d, p.x, p.d, nullptr);
-    PT_STAMP(6);
-    const Gamma g2 = load_gamma((const __half *)L.ln2, p.d);
-    grid_sync(c);
-    PT_STAMP(7);
-    stage_x<true>(c, p.x, p.d, (const __half *)L.ln2, g2);
-    PT_STAMP(8);
-    linear_phase<PT_W_INT4, EPI_SWIGLU>(c, n_rt_gu, nc_d, p.act, 2 * p.ffn, nullptr);
-    PT_STAMP(9);
-    grid_sync(c);
-    PT_STAMP(10);
-    stage_x<true>(c, p.act, p.ffn, nullptr, gnone);
-    linear_phase<PT_W_INT4, EPI_RESID>(c, n_rt_o, nc_f, p.x, p.d, nullptr);
-    PT_STAMP(11);
-    g1 = load_gamma(l + 1 < p.n_layer ? (const __half *)p.layers[l + 1].ln1 : p.norm, p.d);
-    grid_sync(c);
-    PT_STAMP(12);
+    for (int ph = 0; ph < 4; ++ph) {
+      const __half *src, *gamma;
+      __half *out;
+      int K, epi, n_rt, N;
+      if (ph == 0) { src = p.x; gamma = (const __half *)L.ln1; K = p.d; epi = EPI_QKV; n_rt = n_rt_qkv; out = p.qkv; N = 3 * p.d; }
+      else if (ph == 1) { src = p.attn; gamma = nullptr; K = p.d; epi = EPI_RESID; n_rt = n_rt_o; out = p.x; N = p.d; }
+      else if (ph == 2) { src = p.x; gamma = (const __half *)L.ln2; K = p.d; epi = EPI_SWIGLU; n_rt = n_rt_gu; out = p.act; N = 2 * p.ffn; }
+      else { src = p.act; gamma = nullptr; K = p.ffn; epi = EPI_RESID; n_rt = n_rt_o; out = p.x; N = p.d; }
+      stage_x<true>(c, src, K, gamma, gm);
+      if (ph == 0) PT_STAMP(1);
+      if (ph == 2) PT_STAMP(8);
+      linear_phase<PT_W_INT4>(c, epi, n_rt, K / 128, out, N, nullptr);
+      PT_STAMP(ph == 0 ? 2 : (ph == 1 ? 6 : (ph == 2 ? 9 : 11)));
+      // RMSNorm weights of the next normalised phase, requested before the barrier so that their latency hides behind it
+      if (ph == 1) gm = load_gamma((const __half *)L.ln2, p.d);
+      if (ph == 3) gm = load_gamma(l + 1 < p.n_layer ? (const __half *)p.layers[l + 1].ln1 : p.norm, p.d);
+      grid_sync(c);
+      PT_STAMP(ph == 0 ? 3 : (ph == 1 ? 7 : (ph == 2 ? 10 : 12)));
+      if (ph == 0) {
+        attention_phase(c, L);
+        PT_STAMP(4);
+        grid_sync(c);
+        PT_STAMP(5);
+      }
+    }
   }
 #undef PT_STAMP
 
@@ -711,8 +773,8 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   Best best;
 #pragma unroll
   for (int b = 0; b < BMAX; ++b) { best.v[b] = -INFINITY; best.i[b] = 0x7fffffff; }
-  stage_x<false>(c, p.x, p.d, p.norm, g1);
-  linear_phase<PT_W_FP16, EPI_HEAD>(c, n_rt_head, nc_head, p.logits, p.vocab, &best);
+  stage_x<false>(c, p.x, p.d, p.norm, gm);
+  linear_phase<PT_W_FP16>(c, EPI_HEAD, n_rt_head, nc_head, p.logits, p.vocab, &best);
   for (int b = 0; b < p.B; ++b) {
     float v = best.v[b];
     int i = best.i[b];
