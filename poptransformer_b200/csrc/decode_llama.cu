@@ -8,12 +8,14 @@
 // Why one kernel: at batch 1 a layer streams ~110 MB in ~17 us, so per-kernel launch, prologue and tail
 // latencies (several microseconds each, five kernels per layer) cost more than the data movement.  Here
 //   * warp 16 is a producer: it walks this SM's share of every weight matrix of the whole step, in order, and
-//     keeps a ring of 16.5 KB shared-memory stages full with 1-D bulk async copies (TMA engine, one mbarrier
+//     keeps a ring of 33 KB shared-memory stages full with 1-D bulk async copies (TMA engine, one mbarrier
 //     per stage).  Weights do not depend on activations, so the producer runs ahead across the grid-wide
 //     barriers and HBM stays busy while the consumers wait for each other;
-//   * warps 0-15 are consumers: consumer w takes tile w of every stage (a stage = 16 consecutive [row tile][chunk]
-//     tiles of the packed layout of linear.cu), does the same nibble -> fp16 -> mma arithmetic as the streaming
-//     linear kernel, and the 16 partial sums of a row tile meet in shared memory in warp order (deterministic);
+//   * warps 0-15 are consumers: consumer w takes tiles w and 16 + w of every stage (a stage = 32 tiles of the packed
+//     layout of linear.cu, re-ordered so that each warp walks a contiguous run of [row tile][chunk] tiles).  INT4 tiles are
+//     multiplied on the integer tensor-core path: the nibbles of a packed word become two u8 operands with one AND each,
+//     the activations are 16-bit block fixed point split into two s8 columns, and the s32 sums are scaled once per
+//     128-k group; sums of a row tile that several warps share meet in shared memory in warp order (deterministic);
 //   * K/V pages travel through the same ring; the attention arithmetic is that of attention.cu;
 //   * phases are separated by a grid barrier (one atomic per block, bounded spin, error flag on time-out).
 // Every SM owns whole row tiles: rows [s * n_rt / G, (s + 1) * n_rt / G).
@@ -32,7 +34,7 @@ constexpr int NCT = NCW * 32;           // consumer threads
 constexpr int THREADS = NCT + 32;       // + the producer warp
 constexpr int NGRP = NCW / 4;           // 4-warp attention groups
 constexpr int TILE_I4 = 1056, TILE_F16 = 1024;
-constexpr int STAGE_TILES = NCW;                  // one tile per consumer warp per stage
+constexpr int STAGE_TILES = 2 * NCW;              // two tiles per consumer warp per stage
 constexpr int STAGE_BYTES = ((STAGE_TILES * TILE_I4 + 127) / 128 * 128) > 33792 ? ((STAGE_TILES * TILE_I4 + 127) / 128 * 128) : 33792;
 constexpr int V_OFFSET = 16896;                   // a K page and a V page (2 x 16 KB) share one attention stage
 constexpr int MAXU = 8;                           // attention units handled per SM per pass
@@ -367,21 +369,24 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int epi, int n_rt, int nchu
 
   auto store_partial = [&](int slot) { *reinterpret_cast<float2 *>(&c.sh->red[warp][slot][lane][0]) = make_float2(acc0, acc1); };
 
-  // stage j of this phase -> registers; the stage is handed back to the producer as soon as the loads are issued
-  auto fetch = [&](int j, TileRegs &t) {
+  // stage s of this phase (tiles 2s and 2s + 1 of this warp's range) -> registers; the stage is handed back to the producer
+  // as soon as the loads are issued, so its refill overlaps the multiplication
+  auto load_tile = [&](uint32_t t_s, TileRegs &t) {
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.a.x), "=r"(t.a.y), "=r"(t.a.z), "=r"(t.a.w) : "r"(t_s));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.b.x), "=r"(t.b.y), "=r"(t.b.z), "=r"(t.b.w) : "r"(t_s + 512));
+    if (I4) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(t.s) : "r"(t_s - lane * 16 + 1024 + g * 4));
+  };
+  auto fetch = [&](int j, TileRegs &t0, TileRegs &t1) {
     const bool got = mbar_wait(full_s + c.slot * 8, c.par, &c.sh->abort);
     if (!got) {
       c.sh->abort = 1;
       if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 4);
     }
-    if (j < len && got) {
-      const uint32_t t_s = ring_s + c.slot * STAGE_BYTES;
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.a.x), "=r"(t.a.y), "=r"(t.a.z), "=r"(t.a.w) : "r"(t_s));
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.b.x), "=r"(t.b.y), "=r"(t.b.z), "=r"(t.b.w) : "r"(t_s + 512));
-      if (I4) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(t.s) : "r"(t_s - lane * 16 + 1024 + g * 4));
-    }
+    const uint32_t t_s = ring_s + c.slot * STAGE_BYTES;
+    if (j < len && got) load_tile(t_s, t0);
+    if (j + 1 < len && got) load_tile(t_s + NCW * TILE, t1);
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty_s + c.slot * 8);  // this warp's tile is in registers
+    if (lane == 0) mbar_arrive(empty_s + c.slot * 8);  // this warp's tiles are in registers
     c.advance();
   };
 
@@ -425,14 +430,10 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int epi, int n_rt, int nchu
     }
   };
 
-  // Two tiles in flight per warp: the tile of stage j + 1 is pulled into registers (and its stage released) before the
-  // tile of stage j is multiplied, so the registers act as one more ring stage and refills start earlier.
   TileRegs ta, tb;
-  if (nstages > 0) fetch(0, ta);
   for (int j = 0; j < nstages; j += 2) {
-    if (j + 1 < nstages) fetch(j + 1, tb);
+    fetch(j, ta, tb);
     if (j < len) compute(ta);
-    if (j + 2 < nstages) fetch(j + 2, ta);
     if (j + 1 < len) compute(tb);
   }
   if (len > 0 && ch != 0) store_partial(rt == first_rt ? 0 : 1);  // the range ended inside a row tile
@@ -676,7 +677,6 @@ struct Producer {
     }
   }
 };
-
 __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char *ring = smem;
@@ -716,7 +716,6 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
     }
     return;
   }
-
   // ---------------- consumers
   // Two barrier counters are used by alternate launches: word [2] says which one is this launch's (it is zero: the
   // previous launch cleared it when it finished); the last block clears the other one at the very end.
