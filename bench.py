@@ -160,8 +160,11 @@ def run_b200(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
 
     batch = args.batch
-    cfg = llama.LlamaConfig(**LLAMA7B, max_len=MAX_LEN, int4_group=GROUP)
-    sd = synth.llama_state_dict(**LLAMA7B, seed=0, device=dev, int4_group=GROUP)
+    dims = dict(LLAMA7B)
+    if args.layers > 0:
+        dims["n_layer"] = args.layers
+    cfg = llama.LlamaConfig(**dims, max_len=MAX_LEN, int4_group=GROUP)
+    sd = synth.llama_state_dict(**dims, seed=0, device=dev, int4_group=GROUP)
     dec = llama.LlamaDecoder(cfg, sd, batch, device=dev, tp_rank=rank, tp_size=world, persistent=False if args.per_op else None,
                              keep_logits=False)
     del sd
@@ -278,7 +281,10 @@ def run_b200(args):
                           "frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / world / peak,
                           "frac_of_8tbs": step_bytes / (ms_step * 1e-3) / 1e9 / world / 8000.0},
     }
-    if world == 1 and not args.no_cpu:
+    if args.layers > 0:
+        line["profiling_only"] = f"first {args.layers} transformer blocks only; not a benchmark result"
+        line["config"]["workload"] += f" (truncated to {args.layers} layers)"
+    if world == 1 and not args.no_cpu and args.layers <= 0:
         line["cpu_baseline"] = cpu_baseline(steps=3, warmup=1)
     print(json.dumps(line))
     if world > 1:
@@ -294,6 +300,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--per-op", action="store_true", help="use the per-op kernels instead of the persistent whole-step kernel")
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only the first N transformer blocks, so that a profiler capture "
+                    "stays small; the line is then marked profiling_only and is not a benchmark result")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

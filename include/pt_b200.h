@@ -213,9 +213,11 @@ int pt_kv_reorder_table(int32_t *page_table, int32_t *table_tmp, int32_t *spare_
  * (poptransformer/models/llama2/model.py:162-197, models/base_model.py:313-355) for batch <= 2: embedding, every
  * transformer block (INT4 linears packed by pt_linear_repack with PT_W_INT4; q|k|v fused, gate|up interleaved), final
  * RMSNorm, fp16 LM head (PT_W_FP16), greedy id and the loop-carry update (ids container, step, stop mask).
- * Same arithmetic as the per-op kernels; one block per SM streams its share of all weights through a shared-memory
- * ring so that HBM stays busy across the phase barriers.  `layers` is a DEVICE array of n_layer entries.
- * The workspace must be zeroed once before the first launch.
+ * One block per SM streams its share of all weights through a shared-memory ring, so that HBM stays busy while the
+ * SMs wait for each other's activations; those travel as tagged words that the consumers poll (no grid barrier between
+ * phases).  INT4 linears run on the integer tensor-core path with the activations of every 128-k chunk in 16-bit block
+ * fixed point (error far below the fp16 rounding of the result).  `layers` is a DEVICE array of n_layer entries.
+ * The workspace and the x / qkv / attn / act scratch must be zeroed once before the first launch.
  * Weights: every matrix (q|k|v, o, gate|up, down, LM head) is first packed with pt_linear_repack and then re-ordered
  * with pt_llama_stream_permute into the order in which each SM's consumer warps read it (a permutation of the
  * packed tiles inside every SM's share; same size). */
@@ -234,12 +236,13 @@ typedef struct pt_llama_step_args {
   const void *rope_sin, *rope_cos;   /* fp16 [max_len, head_dim/2]                                                   */
   int32_t *ids, *step_dev, *stop_mask, *next_ids; /* ids [batch, max_len]; stop_mask optional                          */
   const int32_t *page_table;         /* [batch, max_pages]                                                          */
-  void *x, *qkv, *attn, *act;        /* fp16 scratch: [batch, d_model], [batch, 3 d_model], [batch, d_model], [batch, ffn] */
+  void *x, *qkv, *attn, *act;        /* scratch of 32-bit words, zeroed once: [batch, d_model], [batch, 3 d_model],
+                                        [batch, d_model], [batch, ffn] (fp16 value + 16-bit phase tag per word)        */
   void *logits;                      /* optional fp16 [batch, vocab]                                                */
   void *workspace;                   /* pt_llama_step_workspace_bytes, zeroed once                                  */
   size_t workspace_bytes;
   int32_t *error_flag;               /* set non-zero if a bounded wait gave up                                      */
-  uint64_t *trace;                   /* optional [n_sm, n_layer, 16] global-timer stamps (ns) of each phase boundary */
+  uint64_t *trace;                   /* optional [n_sm, n_layer, 32] global-timer stamps (ns) of each phase boundary */
   int debug;                         /* profiling aid; bit 0: consume the weight tiles without doing the tile math  */
 } pt_llama_step_args;
 

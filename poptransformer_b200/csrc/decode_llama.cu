@@ -51,15 +51,17 @@ struct Params {
   const unsigned char *head;
   int *ids, *step, *stop_mask, *next_ids;
   const int *page_table;
-  __half *x, *qkv, *attn, *act, *logits;
-  float *ws_o;        // [B, n_head, max_pages, H]
-  float2 *ws_ml;      // [B, n_head, max_pages]
-  int *attn_counters; // [B, n_head]
+  uint32_t *xw, *qkvw, *attnw, *actw;  // activations as tagged words (see TaggedWords below)
+  __half *logits;
+  uint2 *ws_o;        // [B, n_head, max_pages, H] partial attention outputs as {fp32 bits, tag}
+  uint2 *ws_ml;       // [B, n_head, max_pages, 2] page max and sum, same format
   float *cand_val;    // [B, grid]
   int *cand_idx;
-  unsigned *barrier;  // [0], [1]: counters used by alternate launches; [2]: which one the next launch uses
+  unsigned *barrier;  // [0], [1]: counters used by alternate launches; [2]: which one the next launch uses; [3]: launch count
+  uint32_t *flag_sm;  // [256] sequence number of the last linear phase (or embedding) that SM s has finished writing
+  uint32_t *flag_head;  // [B, n_head] sequence number of the last attention output written for that head
   int *error_flag;
-  unsigned long long *trace;  // optional: [grid][n_layer][12] global-timer stamps of the phase boundaries
+  unsigned long long *trace;  // optional: [grid][n_layer][32] global-timer stamps of the phase boundaries
 };
 
 // ------------------------------------------------------------------------------------------ small helpers
@@ -77,12 +79,14 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 // slots that the working warps (and the producer) need.  The wait gives up early when the block has already recorded a
 // failure, so that after an error every loop of the kernel still runs its normal trip count (all named barriers stay
 // matched) but finishes quickly.
+__constant__ uint32_t c_wait_hint = 2000u;  // suspend-time hint (ns) of the mbarrier waits
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int *abort_flag) {
+  const uint32_t hint = c_wait_hint;
   for (int it = 0; it < (1 << 18); ++it) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok)
-                 : "r"(bar), "r"(parity), "r"(2000u)
+                 : "r"(bar), "r"(parity), "r"(hint)
                  : "memory");
     if (ok) return true;
     if ((it & 7) == 7 && *abort_flag) return false;
@@ -96,23 +100,107 @@ __device__ __forceinline__ unsigned long long gtime() {
 }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+// ---- Tagged words.  Activations that one SM produces and all SMs consume (x, qkv, attention output, MLP activations)
+// travel through global memory as 32-bit words: fp16 value in the low half, the 16-bit tag of the producing phase in the
+// high half.  A 32-bit store is indivisible, so a consumer that finds the expected tag also has the value: it polls the
+// data itself and no grid-wide barrier (one atomic round trip, one polling round trip, then the load) separates the
+// phases.  Tags grow with every phase and launch (period 32768 phases), every word is rewritten at least once per launch,
+// so a stale word never carries the expected tag.  Re-use of a buffer is safe without barriers because the writer of the
+// next value has (through the chain of phases in between) waited for data that every reader produced after reading.
+constexpr int POLL_LIMIT = 1 << 21;
+__device__ __forceinline__ uint4 ld_words(const uint32_t *p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_word(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// 64-bit variant for fp32 partial results: {value bits, tag}
+__device__ __forceinline__ uint2 ld_tagged(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_tagged(uint2 *p, uint32_t bits, uint32_t tag) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(bits), "r"(tag) : "memory");
+}
+__device__ __forceinline__ bool poll_tagged(const uint2 *p, uint32_t tag, uint32_t &bits, const volatile int *abort_flag) {
+  for (int it = 0; it < (1 << 21); ++it) {
+    const uint2 v = ld_tagged(p);
+    if (v.y == tag) { bits = v.x; return true; }
+    if ((it & 63) == 63 && *abort_flag) break;
+  }
+  bits = 0;
+  return false;
+}
+__device__ __forceinline__ void st_flag(uint32_t *p, uint32_t v) { asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void st_word(uint32_t *p, uint32_t tag, __half v) { *p = (tag << 16) | (uint32_t)__half_as_ushort(v); }
+// Eight consecutive tagged words -> eight fp16 values (as a uint4).  Bounded: on time-out returns false.
+__device__ __forceinline__ bool poll8(const uint32_t *p, uint32_t tag, uint4 &out, const volatile int *abort_flag) {
+  for (int it = 0; it < POLL_LIMIT; ++it) {
+    const uint4 a = ld_words(p), b = ld_words(p + 4);
+    const uint32_t all = a.x & a.y & a.z & a.w & b.x & b.y & b.z & b.w, any = a.x | a.y | a.z | a.w | b.x | b.y | b.z | b.w;
+    if ((all >> 16) == tag && (any >> 16) == tag) {
+      out = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+      return true;
+    }
+    if ((it & 63) == 63 && *abort_flag) break;
+  }
+  out = make_uint4(0, 0, 0, 0);
+  return false;
+}
+__device__ __forceinline__ bool poll1(const uint32_t *p, uint32_t tag, __half &out, const volatile int *abort_flag) {
+  for (int it = 0; it < POLL_LIMIT; ++it) {
+    const uint32_t w = ld_word(p);
+    if ((w >> 16) == tag) { out = __ushort_as_half((unsigned short)(w & 0xFFFFu)); return true; }
+    if ((it & 63) == 63 && *abort_flag) break;
+  }
+  out = __half(0);
+  return false;
+}
+// Warp 0 waits until every one of `count` progress words has reached sequence number `want` (producers may already be one
+// phase further).  This keeps the polling traffic to one warp per SM; the data words still carry tags, so a word whose store
+// lags behind its producer's progress word is caught when it is loaded.
+__device__ __forceinline__ bool wait_flags(const uint32_t *flags, int count, uint32_t want, const volatile int *abort_flag) {
+  const int lane = threadIdx.x & 31;
+  for (int it = 0; it < POLL_LIMIT; ++it) {
+    bool ok = true;
+    for (int i = lane; i < count; i += 32) ok &= (int)(ld_word(flags + i) - want) >= 0;
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if ((it & 63) == 63 && *abort_flag) break;
+  }
+  return false;
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 
-struct Shared {           // fixed-size part, placed after the ring / activations
-  float red[NCW][2][32][2];  // per warp: partial sums of the first / last row tile of its tile range
+// Operands of the running linear phase that only the (rare) row-tile epilogues need.  They live in shared memory rather than
+// in registers, which the multiplication loop needs for itself.
+struct PhaseInfo {
+  uint32_t *outw;   // tagged-word output (phases between layers)
+  __half *logits;   // fp16 output of the LM head (optional)
+  uint32_t tag, out_seq;
+  int epi, N, r0;
+};
+
+struct Shared {           // fixed-size part, placed after the ring / activations (128-byte aligned)
+  alignas(16) float red[NCW][2][32][2];  // per warp: partial sums of the first / last row tile of its tile range
   int4 corr[96][BMAX];    // [chunk][batch]: C-fragment initialiser {-8 sum(t1), -8 sum(t2)} x 2 rows, up to 96 chunks of 128 k
   float xscale[96][BMAX]; // [chunk][batch]: activation scale of the chunk / 16
   uint4 zeros[2];         // what lanes without a batch column read as their B operand / C initialiser
-  __half qs[MAXU][H], newk[MAXU][H], newv[MAXU][H];
+  alignas(16) __half qs[MAXU][H], newk[MAXU][H], newv[MAXU][H];
   float ps[NGRP][PAGE];   // one row per 4-warp attention group
+  float pw[NCW][PAGE];    // softmax weights of the page, one private copy per warp
   float ml[NGRP][2];
-  int last[MAXU];
   float stat[BMAX];
   float wred[32];
   float bestv[32][BMAX];
   int besti[32][BMAX];
   volatile int abort;
   uint64_t full[16], empty[16];
+  PhaseInfo phase;
 };
 
 struct Ctx {
@@ -123,6 +211,9 @@ struct Ctx {
   unsigned *bar_ctr;
   unsigned bar_target;
   uint32_t slot, par;  // ring slot and mbarrier parity of the next stage (same sequence in producer and consumers)
+  uint32_t tag0;       // tag of phase 0 of this launch
+  __device__ __forceinline__ uint32_t tag(int phase) const { return ((tag0 + (uint32_t)phase) & 0x7FFFu) | 0x8000u; }
+  __device__ __forceinline__ uint32_t seq(int phase) const { return tag0 + (uint32_t)phase + 1u; }  // never 0 in the first launches
   __device__ __forceinline__ void advance() {
     if (++slot == (uint32_t)p.ns) { slot = 0; par ^= 1u; }
   }
@@ -165,7 +256,7 @@ __device__ __forceinline__ float consumer_sum(Ctx &c, float v) {  // sum over th
   return t;
 }
 
-// RMSNorm weights of the next phase, requested before the grid barrier so that their (HBM) latency hides behind it.
+// RMSNorm weights of a phase, requested before the wait for its input so that their latency hides behind it.
 struct Gamma { uint4 v[3]; };
 __device__ __forceinline__ Gamma load_gamma(const __half *gamma, int K) {
   Gamma g;
@@ -186,15 +277,29 @@ __device__ __forceinline__ Gamma load_gamma(const __half *gamma, int K) {
 // rounding.  The weights stay offset-binary nibbles u = q + 8; sum(q T) = sum(u T) - 8 sum(T) and the second term goes
 // into the accumulator's initial value (corr).  The fp16 phase (LM head) keeps x as fp16 in natural order.
 template <bool INT4>
-__device__ __forceinline__ void stage_x(Ctx &c, const __half *src, int K, const __half *gamma, const Gamma &gm) {
+__device__ __forceinline__ void stage_x(Ctx &c, const uint32_t *src, uint32_t tag, const uint32_t *flags, int n_flags, uint32_t want, int K,
+                                        const __half *gamma) {
   const Params &p = c.p;
   const int tid = threadIdx.x;
   const int units = K / 8;
+  const Gamma gm = load_gamma(gamma, K);  // requested before the wait, used after it
+  if (tid < 32 && !wait_flags(flags, n_flags, want, &c.sh->abort)) {
+    c.sh->abort = 1;
+    if (p.error_flag) atomicExch(p.error_flag, 10);
+  }
+  consumer_sync();
   for (int b = 0; b < p.B; ++b) {
     uint4 v[3];
-    const uint4 *xr = reinterpret_cast<const uint4 *>(src + (size_t)b * K);
+    bool got = true;
 #pragma unroll
-    for (int q = 0; q < 3; ++q) v[q] = (tid + q * NCT < units) ? __ldcg(xr + tid + q * NCT) : make_uint4(0, 0, 0, 0);
+    for (int q = 0; q < 3; ++q) {
+      v[q] = make_uint4(0, 0, 0, 0);
+      if (tid + q * NCT < units) got &= poll8(src + (size_t)b * K + (size_t)(tid + q * NCT) * 8, tag, v[q], &c.sh->abort);
+    }
+    if (!got) {
+      c.sh->abort = 1;
+      if (p.error_flag) atomicExch(p.error_flag, 7);
+    }
     __half rb = __half(0);
     if (gamma) {
       float ss = 0.f;
@@ -287,14 +392,19 @@ struct Split {
   __device__ __forceinline__ int stages() const { return base + (rem ? 1 : 0); }
 };
 
-// Finished sums of one row tile: lane (g, tig) with tig < B holds batch tig, rows g (lo) and g + 8 (hi) of the tile.
+// Finished sums of row tile `rt` of this SM: lane (g, tig) with tig < B holds batch tig, rows g (lo) and g + 8 (hi) of the tile.
+// Phases between layers write tagged words; the LM head keeps its arg-max and optionally writes fp16 logits.
 template <bool HEAD>
-__device__ __forceinline__ void tile_epilogue(const Params &p, int epi, float lo, float hi, int rt, int lane, __half *out, int N, Best *best) {
+__device__ __forceinline__ void tile_epilogue(const Params &p, const volatile PhaseInfo *pi, float lo, float hi, int rt, int lane, Best *best) {
   const int g = lane >> 2, b = lane & 3;
   if (b >= p.B) return;
+  const int epi = pi->epi, N = pi->N;
+  const uint32_t tag = pi->tag;
+  uint32_t *outw = pi->outw;
+  rt += pi->r0;
   if (!HEAD && epi == EPI_SWIGLU) {  // rows g / g + 8 are the gate / up feature rt * 8 + g
     const int n = rt * 8 + g;
-    if (n < N / 2) out[(size_t)b * (N / 2) + n] = h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo)));
+    if (n < N / 2) st_word(outw + (size_t)b * (N / 2) + n, tag, h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo))));
     return;
   }
 #pragma unroll
@@ -305,10 +415,14 @@ __device__ __forceinline__ void tile_epilogue(const Params &p, int epi, float lo
     if (HEAD) {
       const float f = __half2float(y);
       if (f > best->v[b] || (f == best->v[b] && n < best->i[b])) { best->v[b] = f; best->i[b] = n; }
-      if (out) out[(size_t)b * N + n] = y;
+      __half *logits = pi->logits;
+      if (logits) logits[(size_t)b * N + n] = y;
     } else {
-      if (epi == EPI_RESID) y = h_add(__ldcg(out + (size_t)b * N + n), y);
-      out[(size_t)b * N + n] = y;
+      uint32_t *w = outw + (size_t)b * N + n;
+      // the residual is the value this SM wrote to the same word one or two phases ago (or the embedding, which the first
+      // staging of this launch has already seen complete)
+      if (epi == EPI_RESID) y = h_add(__ushort_as_half((unsigned short)(ld_word(w) & 0xFFFFu)), y);
+      st_word(w, tag, y);
     }
   }
 }
@@ -335,10 +449,11 @@ struct TileRegs { uint4 a, b; uint32_t s; };
 // needs: two AND per packed word and one integer mma per 512 weights (INT4), operands and accumulator initialisers that
 // arrive from shared memory in fragment order, ring positions advanced without divisions.
 template <int WFMT>
-__device__ __forceinline__ void linear_phase(Ctx &c, int epi, int n_rt, int nchunks, __half *out, int N, Best *best) {
+__device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best *best) {
   constexpr int TILE = WTraits<WFMT>::kTileBytes;
   constexpr bool I4 = (WFMT == PT_W_INT4);
   const Params &p = c.p;
+  const volatile PhaseInfo *pi = &c.sh->phase;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   const int r0 = (int)((long long)c.sm * n_rt / c.G), r1 = (int)((long long)(c.sm + 1) * n_rt / c.G);
   const int m = r1 - r0, total = m * nchunks;
@@ -346,66 +461,51 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int epi, int n_rt, int nchu
   const int len = sp.len(warp), start = sp.start(warp), nstages = sp.stages();
   const int first_rt = start / nchunks;
   int rt = first_rt, ch = start - first_rt * nchunks;
-  const int ch_first = ch;  // chunk at which this warp enters its first row tile
+  const bool enters_midway = ch != 0;  // another warp holds the beginning of this warp's first row tile
   float acc0 = 0.f, acc1 = 0.f;
   const uint32_t ring_s = smem_addr(c.ring) + warp * TILE + lane * 16;
   const uint32_t full_s = smem_addr(&c.sh->full[0]), empty_s = smem_addr(&c.sh->empty[0]);
-  const uint32_t zero_s = smem_addr(&c.sh->zeros[0]);
   // per-lane operand addresses: base + chunk * stride, with stride 0 and the zero block for lanes that carry no batch column
   uint32_t x_s, x_cs, corr_s, corr_cs, xsc_s;
-  if (I4) {
-    const bool has = g < 2 * p.B;
-    x_s = has ? smem_addr(c.xs) + g * 128 + tig * 32 : zero_s;
-    x_cs = has ? p.B * 256 : 0;
-    corr_s = tig < p.B ? smem_addr(&c.sh->corr[0][tig]) : zero_s;
-    corr_cs = tig < p.B ? (uint32_t)sizeof(int4) * BMAX : 0;
-    xsc_s = smem_addr(&c.sh->xscale[0][tig < p.B ? tig : 0]);
-  } else {
-    const bool has = !(g & 1) && (g >> 1) < p.B;   // batch b sits in column 2b, so that lane tig = b ends up with its sums
-    x_s = has ? smem_addr(c.xs) + (g >> 1) * p.xs_stride + tig * 16 : zero_s;
-    x_cs = has ? 64 : 0;
-    corr_s = corr_cs = xsc_s = 0;
+  {
+    const uint32_t zero_s = smem_addr(&c.sh->zeros[0]);
+    if (I4) {
+      const bool has = g < 2 * p.B;
+      x_s = has ? smem_addr(c.xs) + g * 128 + tig * 32 : zero_s;
+      x_cs = has ? p.B * 256 : 0;
+      corr_s = tig < p.B ? smem_addr(&c.sh->corr[0][tig]) : zero_s;
+      corr_cs = tig < p.B ? (uint32_t)sizeof(int4) * BMAX : 0;
+      xsc_s = smem_addr(&c.sh->xscale[0][tig < p.B ? tig : 0]);
+    } else {
+      const bool has = !(g & 1) && (g >> 1) < p.B;   // batch b sits in column 2b, so that lane tig = b ends up with its sums
+      x_s = has ? smem_addr(c.xs) + (g >> 1) * p.xs_stride + tig * 16 : zero_s;
+      x_cs = has ? 64 : 0;
+      corr_s = corr_cs = xsc_s = 0;
+    }
   }
 
   auto store_partial = [&](int slot) { *reinterpret_cast<float2 *>(&c.sh->red[warp][slot][lane][0]) = make_float2(acc0, acc1); };
-
-  // stage s of this phase (tiles 2s and 2s + 1 of this warp's range) -> registers; the stage is handed back to the producer
-  // as soon as the loads are issued, so its refill overlaps the multiplication
   auto load_tile = [&](uint32_t t_s, TileRegs &t) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.a.x), "=r"(t.a.y), "=r"(t.a.z), "=r"(t.a.w) : "r"(t_s));
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.b.x), "=r"(t.b.y), "=r"(t.b.z), "=r"(t.b.w) : "r"(t_s + 512));
     if (I4) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(t.s) : "r"(t_s - lane * 16 + 1024 + g * 4));
   };
-  auto fetch = [&](int j, TileRegs &t0, TileRegs &t1) {
-    const bool got = mbar_wait(full_s + c.slot * 8, c.par, &c.sh->abort);
-    if (!got) {
-      c.sh->abort = 1;
-      if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 4);
-    }
-    const uint32_t t_s = ring_s + c.slot * STAGE_BYTES;
-    if (j < len && got) load_tile(t_s, t0);
-    if (j + 1 < len && got) load_tile(t_s + NCW * TILE, t1);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty_s + c.slot * 8);  // this warp's tiles are in registers
-    c.advance();
-  };
-
   auto compute = [&](const TileRegs &t) {
     if (p.debug & 1) return;
     if (I4) {
       constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u;
-      uint4 xa, xb;
+      uint4 xa;
       int lo[4], hi[4];
       float xs;
       const uint32_t xaddr = x_s + ch * x_cs;
       asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xa.x), "=r"(xa.y), "=r"(xa.z), "=r"(xa.w) : "r"(xaddr));
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xb.x), "=r"(xb.y), "=r"(xb.z), "=r"(xb.w) : "r"(xaddr + 16));
       asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(lo[0]), "=r"(lo[1]), "=r"(lo[2]), "=r"(lo[3]) : "r"(corr_s + ch * corr_cs));
       asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xs) : "r"(xsc_s + ch * (uint32_t)(sizeof(float) * BMAX)));
       imma0(hi, t.a.x & HI, t.b.x & HI, t.a.y & HI, t.b.y & HI, xa.z, xa.w);
       imma(lo, t.a.x & LO, t.b.x & LO, t.a.y & LO, t.b.y & LO, xa.x, xa.y);
-      imma(hi, t.a.z & HI, t.b.z & HI, t.a.w & HI, t.b.w & HI, xb.z, xb.w);
-      imma(lo, t.a.z & LO, t.b.z & LO, t.a.w & LO, t.b.w & LO, xb.x, xb.y);
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xa.x), "=r"(xa.y), "=r"(xa.z), "=r"(xa.w) : "r"(xaddr + 16));
+      imma(hi, t.a.z & HI, t.b.z & HI, t.a.w & HI, t.b.w & HI, xa.z, xa.w);
+      imma(lo, t.a.z & LO, t.b.z & LO, t.a.w & LO, t.b.w & LO, xa.x, xa.y);
       // value x 16 = 4096 lo(t1) + 16 lo(t2) + 256 hi(t1) + hi(t2); |.| < 2^31 for |t1| <= 125 (see stage_x)
       const int v0 = ((lo[0] << 8) + lo[1]) * 16 + (hi[0] << 8) + hi[1];
       const int v1 = ((lo[2] << 8) + lo[3]) * 16 + (hi[2] << 8) + hi[3];
@@ -422,19 +522,34 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int epi, int n_rt, int nchu
       acc1 = cc[2];
     }
     if (++ch == nchunks) {  // this warp reached the end of row tile rt
-      if (rt == first_rt && ch_first != 0) store_partial(0);                                   // entered it midway: another warp holds the beginning
-      else tile_epilogue<!I4>(p, epi, acc0, acc1, r0 + rt, lane, out, N, best);              // had all of it
+      if (rt == first_rt && enters_midway) store_partial(0);
+      else tile_epilogue<!I4>(p, pi, acc0, acc1, rt, lane, best);  // had all of it
       ch = 0;
       ++rt;
       acc0 = acc1 = 0.f;
     }
   };
 
-  TileRegs ta, tb;
+  // Stage j / 2 of this phase holds tiles j and j + 1 of this warp's range.  The first tile is multiplied while the second
+  // is on its way to the registers; the stage is handed back to the producer as soon as the second tile's loads are issued.
   for (int j = 0; j < nstages; j += 2) {
-    fetch(j, ta, tb);
-    if (j < len) compute(ta);
-    if (j + 1 < len) compute(tb);
+    const bool got = mbar_wait(full_s + c.slot * 8, c.par, &c.sh->abort);
+    if (!got) {
+      c.sh->abort = 1;
+      if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 4);
+    }
+    const uint32_t t_s = ring_s + c.slot * STAGE_BYTES;
+    TileRegs t;
+    if (j < len && got) {
+      load_tile(t_s, t);
+      compute(t);
+    }
+    const bool second = j + 1 < len && got;
+    if (second) load_tile(t_s + NCW * TILE, t);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_s + c.slot * 8);
+    c.advance();
+    if (second) compute(t);
   }
   if (len > 0 && ch != 0) store_partial(rt == first_rt ? 0 : 1);  // the range ended inside a row tile
   consumer_sync();
@@ -450,13 +565,17 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int epi, int n_rt, int nchu
       v0 += t.x;
       v1 += t.y;
     }
-    tile_epilogue<!I4>(p, epi, v0, v1, r0 + r, lane, out, N, best);
+    tile_epilogue<!I4>(p, pi, v0, v1, r, lane, best);
+  }
+  if (pi->out_seq) {  // tell the other SMs that this SM's rows of the phase are written
+    consumer_sync();
+    if (tid == 0) st_flag(p.flag_sm + c.sm, pi->out_seq);
   }
 }
 
-// RoPE (rotate_half form) on one head vector in global memory -> dst (shared), reference fp16 roundings.
-__device__ __forceinline__ void rope_pair(const __half *x, const __half *sin_r, const __half *cos_r, int i, __half *dst) {
-  const __half a = __ldcg(x + i), b = __ldcg(x + i + H / 2), s = sin_r[i], co = cos_r[i];
+// RoPE (rotate_half form) on elements i and i + H/2 of one head vector -> dst (shared), reference fp16 roundings.
+__device__ __forceinline__ void rope_pair(__half a, __half b, const __half *sin_r, const __half *cos_r, int i, __half *dst) {
+  const __half s = sin_r[i], co = cos_r[i];
   dst[i] = h_add(h_mul(a, co), h_mul(__hneg(b), s));
   dst[i + H / 2] = h_add(h_mul(b, co), h_mul(a, s));
 }
@@ -466,7 +585,7 @@ __device__ __forceinline__ void group_sync(int grp) { asm volatile("bar.sync %0,
 // one stage per unit that has cached tokens (K page at offset 0, V page at V_OFFSET).  The consumer warps form NGRP
 // groups of four warps; group q handles this SM's units q, q + NGRP, ... on its own (scores with 8 lanes per token, softmax
 // statistics by warp shuffles, P.V with one thread per channel), so units of an SM run concurrently.
-__device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L) {
+__device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L, uint32_t qkv_tag, uint32_t attn_tag, uint32_t attn_seq) {
   const Params &p = c.p;
   Shared *sh = c.sh;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gt = tid & 127;
@@ -477,22 +596,43 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L)
   const __half *sin_r = p.sin_t + (size_t)step * (H / 2), *cos_r = p.cos_t + (size_t)step * (H / 2);
   for (int u0 = c.sm; u0 < n_units; u0 += MAXU * c.G) {
     const int nu = min(MAXU, (n_units - u0 + c.G - 1) / c.G);  // units of this pass: u0 + k G
-    // ---- q (and the new token's k, v) of every unit in one go: one L2 round trip for the whole pass
+    // ---- q (and the new token's k, v) of every unit in one go.  The words carry the tag of this layer's QKV phase; all six
+    // loads of a thread are in flight together, so once the producing SMs are done this costs one L2 round trip.
     {
       const int k = tid >> 6, i = tid & 63;
       if (k < nu) {
         const int u = u0 + k * c.G;
         const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
-        const __half *qrow = p.qkv + (size_t)b * row_elems;
-        rope_pair(qrow + (size_t)head * H, sin_r, cos_r, i, sh->qs[k]);
-        if (pg == n_active - 1) {
-          rope_pair(qrow + p.d + (size_t)head * H, sin_r, cos_r, i, sh->newk[k]);
-          sh->newv[k][i] = __ldcg(qrow + 2 * p.d + (size_t)head * H + i);
-          sh->newv[k][i + 64] = __ldcg(qrow + 2 * p.d + (size_t)head * H + i + 64);
+        const bool owner = (pg == n_active - 1);
+        const uint32_t *qw = p.qkvw + (size_t)b * row_elems + (size_t)head * H + i;
+        uint32_t w[6];
+        bool got = false;
+        for (int it = 0; it < POLL_LIMIT && !got; ++it) {
+          w[0] = ld_word(qw);
+          w[1] = ld_word(qw + H / 2);
+          w[2] = owner ? ld_word(qw + p.d) : w[0];
+          w[3] = owner ? ld_word(qw + p.d + H / 2) : w[0];
+          w[4] = owner ? ld_word(qw + 2 * p.d) : w[0];
+          w[5] = owner ? ld_word(qw + 2 * p.d + H / 2) : w[0];
+          const uint32_t all = w[0] & w[1] & w[2] & w[3] & w[4] & w[5], any = w[0] | w[1] | w[2] | w[3] | w[4] | w[5];
+          got = (all >> 16) == qkv_tag && (any >> 16) == qkv_tag;
+          if ((it & 63) == 63 && sh->abort) break;
+        }
+        if (!got) {
+          sh->abort = 1;
+          if (p.error_flag) atomicExch(p.error_flag, 8);
+        }
+        auto val = [&](int j) { return __ushort_as_half((unsigned short)(w[j] & 0xFFFFu)); };
+        rope_pair(val(0), val(1), sin_r, cos_r, i, sh->qs[k]);
+        if (owner) {
+          rope_pair(val(2), val(3), sin_r, cos_r, i, sh->newk[k]);
+          sh->newv[k][i] = val(4);
+          sh->newv[k][i + 64] = val(5);
         }
       }
     }
     consumer_sync();
+    if (c.tr && tid == 0 && u0 == c.sm) c.tr[13] = gtime();
     // ring slot and parity of each unit of the pass (units without cached tokens have no stage)
     unsigned char slot_unit[MAXU], par_unit[MAXU];
     for (int k = 0; k < nu; ++k) {
@@ -526,6 +666,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L)
           sh->abort = 1;
           if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 5);
         }
+        if (c.tr && tid == 0 && k == 0) c.tr[15] = gtime();
         Ks = reinterpret_cast<const __half *>(c.ring + (size_t)slot * STAGE_BYTES);
         Vs = reinterpret_cast<const __half *>(c.ring + (size_t)slot * STAGE_BYTES + V_OFFSET);
       }
@@ -540,7 +681,11 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L)
       float *ps = sh->ps[grp];
       {
         const int sub = lane & 7;
-        for (int tb = 0; tb < n_valid; tb += 16) {
+        uint4 qq[2];
+        qq[0] = *reinterpret_cast<const uint4 *>(sh->qs[k] + sub * 8);
+        qq[1] = *reinterpret_cast<const uint4 *>(sh->qs[k] + 64 + sub * 8);
+#pragma unroll 2
+        for (int tb = 0; tb < PAGE; tb += 16) {
           const int t = tb + (gt >> 3);
           float sc = 0.f;
           if (t < n_valid && !sh->abort) {
@@ -548,8 +693,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L)
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
               const uint4 kq = *reinterpret_cast<const uint4 *>(kr + v * 64 + sub * 8);
-              const uint4 qq = *reinterpret_cast<const uint4 *>(sh->qs[k] + v * 64 + sub * 8);
-              const __half2 *kh = reinterpret_cast<const __half2 *>(&kq), *qh = reinterpret_cast<const __half2 *>(&qq);
+              const __half2 *kh = reinterpret_cast<const __half2 *>(&kq), *qh = reinterpret_cast<const __half2 *>(&qq[v]);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const float2 a = __half22float2(kh[j]), q2 = __half22float2(qh[j]);
@@ -564,63 +708,133 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L)
         }
       }
       group_sync(grp);
-      if ((warp & 3) == 0) {  // softmax statistics of the page (fp32, like the reference's cast before SoftmaxV3)
-        float m = -INFINITY;
-        for (int t = lane; t < n_valid; t += 32) m = fmaxf(m, ps[t]);
-        m = warp_max(m);
-        float l = 0.f;
-        for (int t = lane; t < n_valid; t += 32) {
-          const float e = expf(ps[t] - m);
-          ps[t] = e;
-          l += e;
-        }
-        l = warp_sum(l);
-        if (lane == 0) { sh->ml[grp][0] = m; sh->ml[grp][1] = l; }
+      if (c.tr && tid == 0 && k == 0) c.tr[16] = gtime();
+      // softmax statistics of the page (fp32, like the reference's cast before SoftmaxV3): every warp of the group works them
+      // out for itself (same values), which saves a group barrier and a single-warp section
+      const int tq = warp & 3;
+      float *pw = sh->pw[warp];
+      float m, l;
+      {
+        const float s0 = lane < n_valid ? ps[lane] : -INFINITY, s1 = lane + 32 < n_valid ? ps[lane + 32] : -INFINITY;
+        m = warp_max(fmaxf(s0, s1));
+        const float e0 = lane < n_valid ? expf(s0 - m) : 0.f, e1 = lane + 32 < n_valid ? expf(s1 - m) : 0.f;
+        pw[lane] = e0;
+        pw[lane + 32] = e1;
+        l = warp_sum(e0 + e1);
       }
-      group_sync(grp);
-      {  // P.V: one thread per channel
-        float o = 0.f;
-        if (!sh->abort)
-          for (int t = 0; t < n_valid; ++t) {
-            const __half vv = (t < n_load) ? Vs[(size_t)t * H + gt] : sh->newv[k][gt];
-            o += ps[t] * __half2float(vv);
+      __syncwarp();
+      if (c.tr && tid == 0 && k == 0) c.tr[17] = gtime();
+      // P.V: warp tq of the group takes tokens tq, tq + 4, ...; lane takes channels 4 lane .. 4 lane + 3; the four partial sums
+      // meet in shared memory in warp order
+      float *part = reinterpret_cast<float *>(&sh->red[0][0][0][0]) + (size_t)grp * 4 * H;  // [tq][H]; red is idle during attention
+      {
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!sh->abort) {
+#pragma unroll 4
+          for (int j = 0; j < PAGE / 4; ++j) {
+            const int t = tq + 4 * j;
+            if (t < n_valid) {
+              const uint2 raw = *reinterpret_cast<const uint2 *>((t < n_load ? Vs + (size_t)t * H : sh->newv[k]) + 4 * lane);
+              const float2 v01 = __half22float2(u32_as_h2(raw.x)), v23 = __half22float2(u32_as_h2(raw.y));
+              const float e = pw[t];
+              o[0] += e * v01.x; o[1] += e * v01.y; o[2] += e * v23.x; o[3] += e * v23.y;
+            }
           }
-        const size_t hd = (size_t)b * p.n_head + head;
-        p.ws_o[(hd * p.max_pages + pg) * H + gt] = o;
-        if (gt == 0) p.ws_ml[hd * p.max_pages + pg] = make_float2(sh->ml[grp][0], sh->ml[grp][1]);
+        }
+        *reinterpret_cast<float4 *>(part + tq * H + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
       }
-      group_sync(grp);  // the group is done with the stage and with ps / ml
+      group_sync(grp);  // the group is done with the stage
+      if (c.tr && tid == 0 && k == 0) c.tr[18] = gtime();
       if (n_load > 0 && lane == 0) mbar_arrive(smem_addr(&sh->empty[slot]));
-    }
-    // ---- last page of a (sequence, head) to arrive combines that head in page order
-    __threadfence();
-    consumer_sync();
-    if (tid < nu) {
-      const int u = u0 + tid * c.G;
-      const int head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
-      sh->last[tid] = (atomicAdd(p.attn_counters + (size_t)b * p.n_head + head, 1) == n_active - 1);
-    }
-    consumer_sync();
-    for (int k = grp; k >= 0 && k < nu; k += NGRP) {
-      if (!sh->last[k]) continue;
-      const int u = u0 + k * c.G;
-      const int head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
-      const size_t hd = (size_t)b * p.n_head + head;
-      __threadfence();
-      if (gt == 0) p.attn_counters[hd] = 0;
-      float M = -INFINITY;
-      for (int i = 0; i < n_active; ++i) M = fmaxf(M, __ldcg(&p.ws_ml[hd * p.max_pages + i]).x);
-      float Lsum = 0.f, o = 0.f;
-      for (int i = 0; i < n_active; ++i) {
-        const float2 v = __ldcg(&p.ws_ml[hd * p.max_pages + i]);
-        const float w = expf(v.x - M);
-        Lsum += v.y * w;
-        o += __ldcg(&p.ws_o[(hd * p.max_pages + i) * H + gt]) * w;
+      {  // publish this page's partial result as tagged words; the unit of the head's last page collects them (below)
+        const size_t hd = (size_t)b * p.n_head + head;
+        const float o = ((part[gt] + part[H + gt]) + part[2 * H + gt]) + part[3 * H + gt];
+        st_tagged(&p.ws_o[(hd * p.max_pages + pg) * H + gt], __float_as_uint(o), attn_tag);
+        if (gt == 0) {
+          st_tagged(&p.ws_ml[(hd * p.max_pages + pg) * 2 + 0], __float_as_uint(m), attn_tag);
+          st_tagged(&p.ws_ml[(hd * p.max_pages + pg) * 2 + 1], __float_as_uint(l), attn_tag);
+        }
       }
-      p.attn[(size_t)b * p.d + (size_t)head * H + gt] = __float2half_rn(o / Lsum);
+      group_sync(grp);  // part / ps may be reused by the group's next unit
+      if (c.tr && tid == 0 && k == 0) c.tr[19] = gtime();
     }
+    if (c.tr && tid == 0 && u0 == c.sm) c.tr[14] = gtime();
     consumer_sync();
   }
+  // ---- combine: the SM that had the last page of a (sequence, head) sums that head's pages in page order.  This comes
+  // after all of the SM's own pages, so producing a partial result never waits for a combine (no circular waits between SMs).
+  {
+    int idx = 0;
+    for (int u = c.sm; u < n_units; u += c.G) {
+      const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
+      if (pg != n_active - 1) continue;
+      if ((idx++ % NGRP) != grp) continue;
+      const size_t hd = (size_t)b * p.n_head + head;
+      const int tq = warp & 3;
+      float *wts = sh->ps[grp];  // [0, 32): w_i = exp(m_i - M), [32, 64): l_i w_i of up to 32 pages at a time
+      bool got = true;
+      if (tq == 0) {  // pass 1: M = max over pages
+        float M = -INFINITY;
+        for (int i0 = 0; i0 < n_active; i0 += 32) {
+          float v = -INFINITY;
+          if (i0 + lane < n_active) {
+            uint32_t bits;
+            got &= poll_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 0], attn_tag, bits, &sh->abort);
+            v = __uint_as_float(bits);
+          }
+          M = fmaxf(M, warp_max(v));
+        }
+        if (lane == 0) sh->ml[grp][0] = M;
+      }
+      group_sync(grp);
+      const float M = sh->ml[grp][0];
+      float Lsum = 0.f, o = 0.f;
+      constexpr int CB = 6;  // pages whose partial outputs are fetched together
+      for (int i0 = 0; i0 < n_active; i0 += 32) {
+        if (i0) group_sync(grp);
+        if (tq == 0 && i0 + lane < n_active) {
+          uint32_t mb, lb;
+          got &= poll_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 0], attn_tag, mb, &sh->abort);
+          got &= poll_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 1], attn_tag, lb, &sh->abort);
+          const float w = expf(__uint_as_float(mb) - M);
+          wts[lane] = w;
+          wts[32 + lane] = __uint_as_float(lb) * w;
+        }
+        group_sync(grp);
+        const int n_here = min(32, n_active - i0);
+        for (int j0 = 0; j0 < n_here; j0 += CB) {
+          uint32_t ov[CB];
+          bool all = false;
+          for (int it = 0; it < POLL_LIMIT && !all; ++it) {
+            all = true;
+#pragma unroll
+            for (int j = 0; j < CB; ++j)
+              if (j0 + j < n_here) {
+                const uint2 w2 = ld_tagged(&p.ws_o[(hd * p.max_pages + i0 + j0 + j) * H + gt]);
+                ov[j] = w2.x;
+                all &= (w2.y == attn_tag);
+              }
+            if ((it & 63) == 63 && sh->abort) break;
+          }
+          got &= all;
+#pragma unroll
+          for (int j = 0; j < CB; ++j)
+            if (j0 + j < n_here) {
+              Lsum += wts[32 + j0 + j];
+              o += __uint_as_float(ov[j]) * wts[j0 + j];
+            }
+        }
+      }
+      if (!got) {
+        sh->abort = 1;
+        if (p.error_flag) atomicExch(p.error_flag, 9);
+      }
+      st_word(p.attnw + (size_t)b * p.d + (size_t)head * H + gt, attn_tag, __float2half_rn(o / Lsum));
+      group_sync(grp);  // ps / ml may be reused by the group's next combine; the head's words are all issued
+      if (gt == 0) st_flag(p.flag_head + hd, attn_seq);
+    }
+  }
+  consumer_sync();
 }
 
 // ------------------------------------------------------------------------------------------ producer
@@ -720,51 +934,62 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   // Two barrier counters are used by alternate launches: word [2] says which one is this launch's (it is zero: the
   // previous launch cleared it when it finished); the last block clears the other one at the very end.
   const unsigned which = __ldcg(p.barrier + 2) & 1u;
-  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, 0u, nullptr};
+  // Word [3] counts launches; it numbers the tags of this launch (block 0 advances it after the final barrier).
+  const int n_phases = 5 * p.n_layer + 1;  // phase 0: embedding; layer l: 1 + 5 l + {0 qkv, 1 attention, 2 o, 3 gate|up, 4 down}
+  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, 0u, __ldcg(p.barrier + 3) * (uint32_t)n_phases, nullptr};
 
-  // embedding: every SM gathers the rows itself (no barrier needed); the copy in global memory serves the residual adds
+  // embedding: the SMs share the gather; the copy in global memory feeds the first staging and the residual adds
   for (int i = tid; i < p.B * (p.d / 8); i += NCT) {
     const int b = i / (p.d / 8), u = i - b * (p.d / 8);
+    if ((u % c.G) != c.sm) continue;
     int id = p.ids[(size_t)b * p.max_len + step];
     id = min(max(id, 0), p.vocab - 1);
     const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.emb + (size_t)id * p.d) + u);
-    if ((u % c.G) == c.sm) reinterpret_cast<uint4 *>(p.x + (size_t)b * p.d)[u] = v;
+    const uint32_t hw[4] = {v.x, v.y, v.z, v.w}, t = c.tag(0) << 16;
+    uint32_t *dst = p.xw + (size_t)b * p.d + (size_t)u * 8;
+    reinterpret_cast<uint4 *>(dst)[0] = make_uint4(t | (hw[0] & 0xFFFFu), t | (hw[0] >> 16), t | (hw[1] & 0xFFFFu), t | (hw[1] >> 16));
+    reinterpret_cast<uint4 *>(dst)[1] = make_uint4(t | (hw[2] & 0xFFFFu), t | (hw[2] >> 16), t | (hw[3] & 0xFFFFu), t | (hw[3] >> 16));
   }
-  Gamma gm = load_gamma((const __half *)p.layers[0].ln1, p.d);
-  grid_sync(c);
+  consumer_sync();
+  if (tid == 0) st_flag(p.flag_sm + c.sm, c.seq(0));
 
   // The four linear phases of a layer run through one copy of the staging and multiplication code (a loop with a table of
   // operands), which keeps the kernel small enough for the instruction cache and lets the compiler inline everything.
-  unsigned long long *tr = p.trace ? p.trace + ((size_t)blockIdx.x * p.n_layer) * 16 : nullptr;
-#define PT_STAMP(k) do { if (tr && tid == 0) tr[l * 16 + (k)] = gtime(); } while (0)
+  unsigned long long *tr = p.trace ? p.trace + ((size_t)blockIdx.x * p.n_layer) * 32 : nullptr;
+#define PT_STAMP(k) do { if (tr && tid == 0) tr[l * 32 + (k)] = gtime(); } while (0)
   for (int l = 0; l < p.n_layer; ++l) {
     const pt_llama_layer &L = p.layers[l];
+    const int ph0 = 1 + 5 * l;
     PT_STAMP(0);
     for (int ph = 0; ph < 4; ++ph) {
-      const __half *src, *gamma;
-      __half *out;
-      int K, epi, n_rt, N;
-      if (ph == 0) { src = p.x; gamma = (const __half *)L.ln1; K = p.d; epi = EPI_QKV; n_rt = n_rt_qkv; out = p.qkv; N = 3 * p.d; }
-      else if (ph == 1) { src = p.attn; gamma = nullptr; K = p.d; epi = EPI_RESID; n_rt = n_rt_o; out = p.x; N = p.d; }
-      else if (ph == 2) { src = p.x; gamma = (const __half *)L.ln2; K = p.d; epi = EPI_SWIGLU; n_rt = n_rt_gu; out = p.act; N = 2 * p.ffn; }
-      else { src = p.act; gamma = nullptr; K = p.ffn; epi = EPI_RESID; n_rt = n_rt_o; out = p.x; N = p.d; }
-      stage_x<true>(c, src, K, gamma, gm);
-      if (ph == 0) PT_STAMP(1);
-      if (ph == 2) PT_STAMP(8);
-      linear_phase<PT_W_INT4>(c, epi, n_rt, K / 128, out, N, nullptr);
+      const uint32_t *src;
+      const __half *gamma;
+      uint32_t *out;
+      int K, epi, n_rt, N, src_phase, out_phase;
+      if (ph == 0) { src = p.xw; src_phase = ph0 - 1; gamma = (const __half *)L.ln1; K = p.d; epi = EPI_QKV; n_rt = n_rt_qkv; out = p.qkvw; N = 3 * p.d; out_phase = ph0; }
+      else if (ph == 1) { src = p.attnw; src_phase = ph0 + 1; gamma = nullptr; K = p.d; epi = EPI_RESID; n_rt = n_rt_o; out = p.xw; N = p.d; out_phase = ph0 + 2; }
+      else if (ph == 2) { src = p.xw; src_phase = ph0 + 2; gamma = (const __half *)L.ln2; K = p.d; epi = EPI_SWIGLU; n_rt = n_rt_gu; out = p.actw; N = 2 * p.ffn; out_phase = ph0 + 3; }
+      else { src = p.actw; src_phase = ph0 + 3; gamma = nullptr; K = p.ffn; epi = EPI_RESID; n_rt = n_rt_o; out = p.xw; N = p.d; out_phase = ph0 + 4; }
+      const bool from_attn = (ph == 1);
+      if (tid == 0) {
+        PhaseInfo *w = &sh->phase;
+        w->outw = out; w->logits = nullptr; w->tag = c.tag(out_phase); w->out_seq = c.seq(out_phase);
+        w->epi = epi; w->N = N; w->r0 = (int)((long long)c.sm * n_rt / c.G);
+      }
+      c.tr = tr ? tr + l * 32 : nullptr;
+      stage_x<true>(c, src, c.tag(src_phase), from_attn ? p.flag_head : p.flag_sm, from_attn ? p.B * p.n_head : c.G, c.seq(src_phase), K, gamma);
+      PT_STAMP(ph == 0 ? 1 : (ph == 1 ? 5 : (ph == 2 ? 8 : 10)));
+      linear_phase<PT_W_INT4>(c, n_rt, K / 128, nullptr);
       PT_STAMP(ph == 0 ? 2 : (ph == 1 ? 6 : (ph == 2 ? 9 : 11)));
-      // RMSNorm weights of the next normalised phase, requested before the barrier so that their latency hides behind it
-      if (ph == 1) gm = load_gamma((const __half *)L.ln2, p.d);
-      if (ph == 3) gm = load_gamma(l + 1 < p.n_layer ? (const __half *)p.layers[l + 1].ln1 : p.norm, p.d);
-      grid_sync(c);
-      PT_STAMP(ph == 0 ? 3 : (ph == 1 ? 7 : (ph == 2 ? 10 : 12)));
+      if (ph == 1) PT_STAMP(7);
       if (ph == 0) {
-        attention_phase(c, L);
+        PT_STAMP(3);
+        attention_phase(c, L, c.tag(ph0), c.tag(ph0 + 1), c.seq(ph0 + 1));
+        c.tr = nullptr;
         PT_STAMP(4);
-        grid_sync(c);
-        PT_STAMP(5);
       }
     }
+    PT_STAMP(12);
   }
 #undef PT_STAMP
 
@@ -772,8 +997,13 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   Best best;
 #pragma unroll
   for (int b = 0; b < BMAX; ++b) { best.v[b] = -INFINITY; best.i[b] = 0x7fffffff; }
-  stage_x<false>(c, p.x, p.d, p.norm, gm);
-  linear_phase<PT_W_FP16>(c, EPI_HEAD, n_rt_head, nc_head, p.logits, p.vocab, &best);
+  if (tid == 0) {
+    PhaseInfo *w = &sh->phase;
+    w->outw = nullptr; w->logits = p.logits; w->tag = 0u; w->out_seq = 0u;
+    w->epi = EPI_HEAD; w->N = p.vocab; w->r0 = (int)((long long)c.sm * n_rt_head / c.G);
+  }
+  stage_x<false>(c, p.xw, c.tag(5 * p.n_layer), p.flag_sm, c.G, c.seq(5 * p.n_layer), p.d, p.norm);
+  linear_phase<PT_W_FP16>(c, n_rt_head, nc_head, &best);
   for (int b = 0; b < p.B; ++b) {
     float v = best.v[b];
     int i = best.i[b];
@@ -831,6 +1061,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   if (blockIdx.x == 0 && tid == 0) {  // every block has passed the last barrier of this launch
     p.barrier[which ^ 1u] = 0;
     p.barrier[2] = which ^ 1u;
+    p.barrier[3] = __ldcg(p.barrier + 3) + 1u;
   }
 }
 
@@ -884,9 +1115,8 @@ extern "C" int pt_llama_stream_permute(int wfmt, const void *packed, void *out, 
 extern "C" size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_dim, int max_pages) {
   const size_t heads = (size_t)batch * n_head;
   auto al = [](size_t v) { return (v + 255) / 256 * 256; };
-  // barrier counters | attention counters | (max, sum) | partial outputs | arg-max candidates (value, index) for up to 256 SMs
-  return 256 + al(heads * sizeof(int)) + al(heads * max_pages * sizeof(float2)) + al(heads * max_pages * head_dim * sizeof(float)) +
-         2 * al((size_t)batch * 256 * sizeof(float));
+  // barrier words | per-SM progress words | per-head progress words | page (max, sum) | partial outputs (both as 8-byte tagged words) | arg-max candidates (value, index) for up to 256 SMs
+  return 256 + 1024 + al(heads * sizeof(uint32_t)) + al(heads * max_pages * 2 * sizeof(uint2)) + al(heads * max_pages * head_dim * sizeof(uint2)) + 2 * al((size_t)batch * 256 * sizeof(float));
 }
 
 extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
@@ -924,7 +1154,7 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   p.layers = a->layers; p.norm = (const __half *)a->norm; p.emb = (const __half *)a->emb;
   p.sin_t = (const __half *)a->rope_sin; p.cos_t = (const __half *)a->rope_cos; p.head = (const unsigned char *)a->head;
   p.ids = a->ids; p.step = a->step_dev; p.stop_mask = a->stop_mask; p.next_ids = a->next_ids; p.page_table = a->page_table;
-  p.x = (__half *)a->x; p.qkv = (__half *)a->qkv; p.attn = (__half *)a->attn; p.act = (__half *)a->act; p.logits = (__half *)a->logits;
+  p.xw = (uint32_t *)a->x; p.qkvw = (uint32_t *)a->qkv; p.attnw = (uint32_t *)a->attn; p.actw = (uint32_t *)a->act; p.logits = (__half *)a->logits;
   p.error_flag = a->error_flag;
   p.trace = (unsigned long long *)a->trace;
   p.debug = a->debug;
@@ -932,9 +1162,10 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   const size_t heads = (size_t)a->batch * a->n_head;
   char *ws = (char *)a->workspace;
   p.barrier = (unsigned *)ws; ws += 256;
-  p.attn_counters = (int *)ws; ws += al(heads * sizeof(int));
-  p.ws_ml = (float2 *)ws; ws += al(heads * a->max_pages * sizeof(float2));
-  p.ws_o = (float *)ws; ws += al(heads * a->max_pages * a->head_dim * sizeof(float));
+  p.flag_sm = (uint32_t *)ws; ws += 1024;
+  p.flag_head = (uint32_t *)ws; ws += al(heads * sizeof(uint32_t));
+  p.ws_ml = (uint2 *)ws; ws += al(heads * a->max_pages * 2 * sizeof(uint2));
+  p.ws_o = (uint2 *)ws; ws += al(heads * a->max_pages * a->head_dim * sizeof(uint2));
   p.cand_val = (float *)ws; ws += al((size_t)a->batch * 256 * sizeof(float));
   p.cand_idx = (int *)ws;
 
@@ -945,6 +1176,14 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   p.ns = (int)std::min<size_t>(16, (smem_max - fixed) / mk::STAGE_BYTES);
   const size_t smem = (size_t)p.ns * mk::STAGE_BYTES + fixed;
 
+  {
+    static uint32_t hint_set = 2000u;
+    const uint32_t want = ((uint32_t)a->debug >> 16) ? ((uint32_t)a->debug >> 16) : 2000u;
+    if (want != hint_set) {
+      PT_CUDA(cudaMemcpyToSymbolAsync(mk::c_wait_hint, &want, sizeof(want), 0, cudaMemcpyHostToDevice, as_stream(stream)));
+      hint_set = want;
+    }
+  }
   void *kargs[] = {(void *)&p};
   cudaError_t e = cudaLaunchCooperativeKernel((const void *)mk::llama_step_kernel, dim3(n_sm), dim3(mk::THREADS), kargs, smem, as_stream(stream));
   if (e != cudaSuccess) return pt::set_error(PT_ERR_CUDA, "pt_llama_decode_step: %s", cudaGetErrorString(e));

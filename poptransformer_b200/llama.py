@@ -170,7 +170,9 @@ class LlamaDecoder:
             a.rope_sin, a.rope_cos = self.sin.data_ptr(), self.cos.data_ptr()
             a.ids, a.step_dev, a.stop_mask, a.next_ids = self.ids.data_ptr(), self.step_t.data_ptr(), self.stop_mask.data_ptr(), self.next_ids.data_ptr()
             a.page_table = self.caches[0].page_table.data_ptr()
-            a.x, a.qkv, a.attn, a.act = self.x.data_ptr(), self.qkv.data_ptr(), self.attn.data_ptr(), self.act.data_ptr()
+            # the kernel's own activation scratch: 32-bit words (fp16 value + phase tag), zeroed once
+            self.mk_act = [torch.zeros((B, n), dtype=torch.int32, device=dev) for n in (d, 3 * d, d, f)]
+            a.x, a.qkv, a.attn, a.act = (t.data_ptr() for t in self.mk_act)
             a.logits = self.logits.data_ptr() if keep_logits else None
             a.workspace, a.workspace_bytes = self.mk_ws.data_ptr(), self.mk_ws.numel()
             a.error_flag = self.error_flag.data_ptr()
