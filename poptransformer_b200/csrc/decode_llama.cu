@@ -41,6 +41,7 @@ constexpr int MAXU = 8;                           // attention units handled per
 constexpr int BMAX = 2;
 constexpr int H = 128, PAGE = 64;
 constexpr int SPIN_LIMIT = 1 << 22;
+static_assert(NCT == 8 * PAGE, "the attention scores use eight lanes per token of a page");
 
 struct Params {
   int B, d, n_head, ffn, vocab, n_layer, max_len, max_pages, ns, xs_stride, pad_id, eos_id, debug;
@@ -278,28 +279,50 @@ __device__ __forceinline__ Gamma load_gamma(const __half *gamma, int K) {
 // into the accumulator's initial value (corr).  The fp16 phase (LM head) keeps x as fp16 in natural order.
 template <bool INT4>
 __device__ __forceinline__ void stage_x(Ctx &c, const uint32_t *src, uint32_t tag, const uint32_t *flags, int n_flags, uint32_t want, int K,
-                                        const __half *gamma) {
+                                        const __half *gamma, int trace_slot = 0) {
   const Params &p = c.p;
   const int tid = threadIdx.x;
   const int units = K / 8;
   const Gamma gm = load_gamma(gamma, K);  // requested before the wait, used after it
+  unsigned long long *ts = (c.tr && trace_slot && tid == 0) ? c.tr + trace_slot : nullptr;
+  if (ts) ts[0] = gtime();
+  // First attempt at this thread's words of batch row 0 right away: an SM that arrives after all producers are done then
+  // has its data one round trip earlier.  Words that are not there yet are fetched again after the wait.
+  uint4 v0[3];
+  unsigned have = 0;
+#pragma unroll
+  for (int q = 0; q < 3; ++q) {
+    v0[q] = make_uint4(0, 0, 0, 0);
+    if (tid + q * NCT < units) {
+      const uint32_t *w = src + (size_t)(tid + q * NCT) * 8;
+      const uint4 a = ld_words(w), b4 = ld_words(w + 4);
+      const uint32_t all = a.x & a.y & a.z & a.w & b4.x & b4.y & b4.z & b4.w, any = a.x | a.y | a.z | a.w | b4.x | b4.y | b4.z | b4.w;
+      if ((all >> 16) == tag && (any >> 16) == tag) {
+        v0[q] = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b4.x, b4.y, 0x5410), __byte_perm(b4.z, b4.w, 0x5410));
+        have |= 1u << q;
+      }
+    }
+  }
   if (tid < 32 && !wait_flags(flags, n_flags, want, &c.sh->abort)) {
     c.sh->abort = 1;
     if (p.error_flag) atomicExch(p.error_flag, 10);
   }
   consumer_sync();
+  if (ts) ts[1] = gtime();
   for (int b = 0; b < p.B; ++b) {
     uint4 v[3];
     bool got = true;
 #pragma unroll
     for (int q = 0; q < 3; ++q) {
       v[q] = make_uint4(0, 0, 0, 0);
-      if (tid + q * NCT < units) got &= poll8(src + (size_t)b * K + (size_t)(tid + q * NCT) * 8, tag, v[q], &c.sh->abort);
+      if (b == 0 && (have >> q & 1)) v[q] = v0[q];
+      else if (tid + q * NCT < units) got &= poll8(src + (size_t)b * K + (size_t)(tid + q * NCT) * 8, tag, v[q], &c.sh->abort);
     }
     if (!got) {
       c.sh->abort = 1;
       if (p.error_flag) atomicExch(p.error_flag, 7);
     }
+    if (ts && b == 0) ts[2] = gtime();
     __half rb = __half(0);
     if (gamma) {
       float ss = 0.f;
@@ -633,85 +656,63 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
     }
     consumer_sync();
     if (c.tr && tid == 0 && u0 == c.sm) c.tr[13] = gtime();
-    // ring slot and parity of each unit of the pass (units without cached tokens have no stage)
-    unsigned char slot_unit[MAXU], par_unit[MAXU];
-    for (int k = 0; k < nu; ++k) {
-      const int u = u0 + k * c.G;
-      const int pg = u % n_active;
-      const int n_valid = min(PAGE, step + 1 - pg * PAGE);
-      const int n_load = (pg == n_active - 1) ? n_valid - 1 : n_valid;
-      slot_unit[k] = (unsigned char)c.slot;
-      par_unit[k] = (unsigned char)c.par;
-      if (n_load > 0) c.advance();
-    }
+    // The units of the pass one after the other, each with all consumer warps (an SM has two or three units at the sizes
+    // this kernel is for, and a unit is a chain of short steps, so width beats concurrency).
     for (int k = 0; k < nu; ++k) {
       const int u = u0 + k * c.G;
       const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
       const int n_valid = min(PAGE, step + 1 - pg * PAGE);
       const bool owner = (pg == n_active - 1);
-      const int n_load = owner ? n_valid - 1 : n_valid;
-      const int slot = slot_unit[k];
-      const uint32_t par = par_unit[k];
-      if ((k % NGRP) != grp) {  // not this group's unit: release the stage at once
-        if (n_load > 0 && lane == 0) {
-          // the arrival only counts once the stage is full, so wait for it first (keeps phases aligned)
-          mbar_wait(smem_addr(&sh->full[slot]), par, &sh->abort);
-          mbar_arrive(smem_addr(&sh->empty[slot]));
-        }
-        continue;
-      }
+      const int n_load = owner ? n_valid - 1 : n_valid;  // tokens that come from the pool (units without any have no stage)
+      const uint32_t slot = c.slot;
       const __half *Ks = nullptr, *Vs = nullptr;
       if (n_load > 0) {
-        if (!mbar_wait(smem_addr(&sh->full[slot]), par, &sh->abort)) {
+        if (!mbar_wait(smem_addr(&sh->full[slot]), c.par, &sh->abort)) {
           sh->abort = 1;
           if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 5);
         }
         if (c.tr && tid == 0 && k == 0) c.tr[15] = gtime();
         Ks = reinterpret_cast<const __half *>(c.ring + (size_t)slot * STAGE_BYTES);
         Vs = reinterpret_cast<const __half *>(c.ring + (size_t)slot * STAGE_BYTES + V_OFFSET);
+        c.advance();
       }
-      if (owner && !sh->abort) {  // append the new token to the pool
+      if (owner && tid < H && !sh->abort) {  // append the new token to the pool
         const int phys = p.page_table[(size_t)b * p.max_pages + pg];
         __half *gK = (__half *)L.pool + (((size_t)phys * 2 + 0) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
         __half *gV = (__half *)L.pool + (((size_t)phys * 2 + 1) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
-        gK[gt] = sh->newk[k][gt];
-        gV[gt] = sh->newv[k][gt];
+        gK[tid] = sh->newk[k][tid];
+        gV[tid] = sh->newv[k][tid];
       }
-      // scores: 8 lanes per cached token, 16 tokens per pass of the 128-thread group
-      float *ps = sh->ps[grp];
+      // scores: 8 lanes per cached token, all 64 tokens of the page at once
+      float *ps = sh->ps[0];
       {
-        const int sub = lane & 7;
-        uint4 qq[2];
-        qq[0] = *reinterpret_cast<const uint4 *>(sh->qs[k] + sub * 8);
-        qq[1] = *reinterpret_cast<const uint4 *>(sh->qs[k] + 64 + sub * 8);
-#pragma unroll 2
-        for (int tb = 0; tb < PAGE; tb += 16) {
-          const int t = tb + (gt >> 3);
-          float sc = 0.f;
-          if (t < n_valid && !sh->abort) {
-            const __half *kr = (t < n_load) ? Ks + (size_t)t * H : sh->newk[k];
+        const int sub = lane & 7, t = tid >> 3;
+        float sc0 = 0.f, sc1 = 0.f;
+        if (t < n_valid && !sh->abort) {
+          const __half *kr = (t < n_load) ? Ks + (size_t)t * H : sh->newk[k];
 #pragma unroll
-            for (int v = 0; v < 2; ++v) {
-              const uint4 kq = *reinterpret_cast<const uint4 *>(kr + v * 64 + sub * 8);
-              const __half2 *kh = reinterpret_cast<const __half2 *>(&kq), *qh = reinterpret_cast<const __half2 *>(&qq[v]);
+          for (int v = 0; v < 2; ++v) {
+            const uint4 kq = *reinterpret_cast<const uint4 *>(kr + v * 64 + sub * 8);
+            const uint4 qq = *reinterpret_cast<const uint4 *>(sh->qs[k] + v * 64 + sub * 8);
+            const __half2 *kh = reinterpret_cast<const __half2 *>(&kq), *qh = reinterpret_cast<const __half2 *>(&qq);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 a = __half22float2(kh[j]), q2 = __half22float2(qh[j]);
-                sc += a.x * q2.x + a.y * q2.y;
-              }
+            for (int j = 0; j < 4; ++j) {
+              const float2 a = __half22float2(kh[j]), q2 = __half22float2(qh[j]);
+              sc0 = fmaf(a.x, q2.x, sc0);
+              sc1 = fmaf(a.y, q2.y, sc1);
             }
           }
-          sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-          sc += __shfl_xor_sync(0xffffffffu, sc, 2);
-          sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-          if (sub == 0 && t < n_valid) ps[t] = __half2float(h_mul(__float2half_rn(sc), p.score_scale));
         }
+        float sc = sc0 + sc1;
+        sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+        if (sub == 0 && t < n_valid) ps[t] = __half2float(h_mul(__float2half_rn(sc), p.score_scale));
       }
-      group_sync(grp);
+      consumer_sync();
       if (c.tr && tid == 0 && k == 0) c.tr[16] = gtime();
-      // softmax statistics of the page (fp32, like the reference's cast before SoftmaxV3): every warp of the group works them
-      // out for itself (same values), which saves a group barrier and a single-warp section
-      const int tq = warp & 3;
+      // softmax statistics of the page (fp32, like the reference's cast before SoftmaxV3): every warp works them out for
+      // itself (same values), which saves a barrier and a single-warp section
       float *pw = sh->pw[warp];
       float m, l;
       {
@@ -724,15 +725,15 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
       }
       __syncwarp();
       if (c.tr && tid == 0 && k == 0) c.tr[17] = gtime();
-      // P.V: warp tq of the group takes tokens tq, tq + 4, ...; lane takes channels 4 lane .. 4 lane + 3; the four partial sums
-      // meet in shared memory in warp order
-      float *part = reinterpret_cast<float *>(&sh->red[0][0][0][0]) + (size_t)grp * 4 * H;  // [tq][H]; red is idle during attention
+      // P.V: warp w takes tokens w, w + 16, ...; lane takes channels 4 lane .. 4 lane + 3; the 16 partial sums meet in shared
+      // memory in warp order
+      float *part = reinterpret_cast<float *>(&sh->red[0][0][0][0]);  // [NCW][H]; red is idle during attention
       {
         float o[4] = {0.f, 0.f, 0.f, 0.f};
         if (!sh->abort) {
-#pragma unroll 4
-          for (int j = 0; j < PAGE / 4; ++j) {
-            const int t = tq + 4 * j;
+#pragma unroll
+          for (int j = 0; j < PAGE / NCW; ++j) {
+            const int t = warp + NCW * j;
             if (t < n_valid) {
               const uint2 raw = *reinterpret_cast<const uint2 *>((t < n_load ? Vs + (size_t)t * H : sh->newv[k]) + 4 * lane);
               const float2 v01 = __half22float2(u32_as_h2(raw.x)), v23 = __half22float2(u32_as_h2(raw.y));
@@ -741,21 +742,23 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
             }
           }
         }
-        *reinterpret_cast<float4 *>(part + tq * H + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4 *>(part + warp * H + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
       }
-      group_sync(grp);  // the group is done with the stage
+      consumer_sync();  // everyone is done with the stage
       if (c.tr && tid == 0 && k == 0) c.tr[18] = gtime();
       if (n_load > 0 && lane == 0) mbar_arrive(smem_addr(&sh->empty[slot]));
-      {  // publish this page's partial result as tagged words; the unit of the head's last page collects them (below)
+      if (tid < H) {  // publish this page's partial result as tagged words; the unit of the head's last page collects them (below)
         const size_t hd = (size_t)b * p.n_head + head;
-        const float o = ((part[gt] + part[H + gt]) + part[2 * H + gt]) + part[3 * H + gt];
-        st_tagged(&p.ws_o[(hd * p.max_pages + pg) * H + gt], __float_as_uint(o), attn_tag);
-        if (gt == 0) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < NCW; ++w) o += part[w * H + tid];
+        st_tagged(&p.ws_o[(hd * p.max_pages + pg) * H + tid], __float_as_uint(o), attn_tag);
+        if (tid == 0) {
           st_tagged(&p.ws_ml[(hd * p.max_pages + pg) * 2 + 0], __float_as_uint(m), attn_tag);
           st_tagged(&p.ws_ml[(hd * p.max_pages + pg) * 2 + 1], __float_as_uint(l), attn_tag);
         }
       }
-      group_sync(grp);  // part / ps may be reused by the group's next unit
+      consumer_sync();  // part / ps are reused by the next unit
       if (c.tr && tid == 0 && k == 0) c.tr[19] = gtime();
     }
     if (c.tr && tid == 0 && u0 == c.sm) c.tr[14] = gtime();
@@ -977,7 +980,8 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
         w->epi = epi; w->N = N; w->r0 = (int)((long long)c.sm * n_rt / c.G);
       }
       c.tr = tr ? tr + l * 32 : nullptr;
-      stage_x<true>(c, src, c.tag(src_phase), from_attn ? p.flag_head : p.flag_sm, from_attn ? p.B * p.n_head : c.G, c.seq(src_phase), K, gamma);
+      stage_x<true>(c, src, c.tag(src_phase), from_attn ? p.flag_head : p.flag_sm, from_attn ? p.B * p.n_head : c.G, c.seq(src_phase), K, gamma,
+                    ph == 0 ? 20 : (ph == 3 ? 24 : (ph == 2 ? 28 : 0)));
       PT_STAMP(ph == 0 ? 1 : (ph == 1 ? 5 : (ph == 2 ? 8 : 10)));
       linear_phase<PT_W_INT4>(c, n_rt, K / 128, nullptr);
       PT_STAMP(ph == 0 ? 2 : (ph == 1 ? 6 : (ph == 2 ? 9 : 11)));
