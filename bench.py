@@ -61,6 +61,10 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
         self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
         sm, smax, reasons = [], [], set()
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
@@ -260,9 +264,20 @@ def run_b200(args):
                 "kernel": "linear_kernel<INT4>", "peak_source": peak_src, "launch_us": lin_ms * 1e3, "bytes_per_launch": lin_bytes / n_lin}
     roof["frac"] = roof["achieved"] / peak
 
-    if rank != 0:
+    def shutdown():
+        # The captured CUDA graph holds NCCL kernels: release it before the communicator goes away, and do not let a slow
+        # communicator tear-down keep the process (and the launcher that waits for it) alive.
         if world > 1:
+            dec.graph = None
+            torch.cuda.synchronize()
+            dist.barrier()
+            sys.stdout.flush()
+            threading.Timer(20.0, lambda: os._exit(0)).start()
             dist.destroy_process_group()
+            os._exit(0)
+
+    if rank != 0:
+        shutdown()
         return
     ms_step = ms / K
     line = {
@@ -287,8 +302,7 @@ def run_b200(args):
     if world == 1 and not args.no_cpu and args.layers <= 0:
         line["cpu_baseline"] = cpu_baseline(steps=3, warmup=1)
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown()
 
 
 def main():
