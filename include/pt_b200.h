@@ -244,9 +244,21 @@ typedef struct pt_llama_step_args {
   int32_t *error_flag;               /* set non-zero if a bounded wait gave up                                      */
   uint64_t *trace;                   /* optional [n_sm, n_layer, 32] global-timer stamps (ns) of each phase boundary */
   int debug;                         /* profiling aid; bit 0: consume the weight tiles without doing the tile math  */
+  /* Tensor parallelism inside the kernel (tp_size > 1; one process and one launch per GPU, all ranks launch every step).
+   * The reference's TP layers (layers/linear.py 'start' / 'end' strategies, layers/lm_head.py:75-116) map to: d_model = the
+   * full hidden size, n_head = this rank's heads, ffn = width of this rank's k window of down_proj (a multiple of 128
+   * holding its ffn_valid activations at ffn_offset; weights outside are zero), vocab = this rank's LM-head rows, first id
+   * vocab_offset.  The all-reduce after o_proj / down_proj is fused into the kernel: every rank stores its fp16 partial
+   * sums into its slot of every rank's exchange buffer (plain peer stores, tagged words), and the next staging step on
+   * every rank adds the slots in rank order.  tp_buffers[r] is rank r's exchange buffer as mapped in this process
+   * (pt_llama_tp_buffer_bytes each, zeroed once); x must then hold two copies ([2, batch, d_model] words). */
+  int tp_size, tp_rank, ffn_offset, ffn_valid, vocab_offset;
+  int emb_rows;                      /* tp_size > 1: rows of the embedding table (the full vocabulary; the table is replicated) */
+  void *tp_buffers[8];
 } pt_llama_step_args;
 
 size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);
+size_t pt_llama_tp_buffer_bytes(int batch, int d_model, int tp_size);
 int pt_llama_decode_step(const pt_llama_step_args *args, void *stream);
 
 /* ---- top-k / LM-head ids / beam search --------------------------------------------------

@@ -47,7 +47,8 @@ class LlamaStepArgs(ctypes.Structure):
                                      "max_pages", "pad_id", "eos_id")] + [("norm_eps", c_float), ("score_scale", c_float)] + \
                [(n, c_void_p) for n in ("layers", "norm", "head", "emb", "rope_sin", "rope_cos", "ids", "step_dev", "stop_mask", "next_ids",
                                         "page_table", "x", "qkv", "attn", "act", "logits", "workspace")] + \
-               [("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("trace", c_void_p), ("debug", c_int)]
+               [("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("trace", c_void_p), ("debug", c_int)] + \
+               [(n, c_int) for n in ("tp_size", "tp_rank", "ffn_offset", "ffn_valid", "vocab_offset", "emb_rows")] + [("tp_buffers", c_void_p * 8)]
 
 
 # name -> (restype, argtypes); mirrors include/pt_b200.h one to one
@@ -73,6 +74,7 @@ SIGNATURES = {
     "pt_kv_reorder_table": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "pt_llama_stream_permute": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "pt_llama_step_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "pt_llama_tp_buffer_bytes": (c_size_t, [c_int, c_int, c_int]),
     "pt_llama_decode_step": (c_int, [ctypes.POINTER(LlamaStepArgs), c_void_p]),
     "pt_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_lm_head_local_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -45,6 +45,13 @@ static_assert(NCT == 8 * PAGE, "the attention scores use eight lanes per token o
 
 struct Params {
   int B, d, n_head, ffn, vocab, n_layer, max_len, max_pages, ns, xs_stride, pad_id, eos_id, debug;
+  // Tensor parallelism: d is the full hidden size; n_head, ffn and vocab are this rank's shares.  dq = n_head * H is the
+  // width of the rank's q / k / v / attention vectors (the k range of its o_proj slice); the rank's MLP activations are
+  // ffn_valid values at offset ffn_off inside a window of ffn columns (a multiple of 128; the weights outside are zero).
+  int tp, rank, dq, ffn_off, ffn_valid, vocab_off, emb_rows;  // emb_rows: rows of the (replicated) embedding table
+  uint32_t *peer_part[8];   // every rank's partial-sum buffer [2 (o_proj, down_proj)][tp][B][d], tagged words
+  uint32_t *peer_flag[8];   // every rank's progress words [tp][256]
+  uint2 *peer_cand[8];      // every rank's arg-max candidates [tp][BMAX][2] {value bits | index, sequence number}
   float eps;
   __half score_scale;
   const pt_llama_layer *layers;
@@ -52,7 +59,7 @@ struct Params {
   const unsigned char *head;
   int *ids, *step, *stop_mask, *next_ids;
   const int *page_table;
-  uint32_t *xw, *qkvw, *attnw, *actw;  // activations as tagged words (see TaggedWords below)
+  uint32_t *xw, *qkvw, *attnw, *actw;  // activations as tagged words; xw holds two copies [2][B][d] when tp > 1
   __half *logits;
   uint2 *ws_o;        // [B, n_head, max_pages, H] partial attention outputs as {fp32 bits, tag}
   uint2 *ws_ml;       // [B, n_head, max_pages, 2] page max and sum, same format
@@ -137,6 +144,16 @@ __device__ __forceinline__ bool poll_tagged(const uint2 *p, uint32_t tag, uint32
   bits = 0;
   return false;
 }
+// Stores to another GPU's memory (or to this GPU's copy of a buffer that peers also write): system scope.
+__device__ __forceinline__ void st_sys(uint32_t *p, uint32_t v) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void st_sys2(uint2 *p, uint32_t a, uint32_t b) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_sys2(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_flag(uint32_t *p, uint32_t v) { asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ void st_word(uint32_t *p, uint32_t tag, __half v) { *p = (tag << 16) | (uint32_t)__half_as_ushort(v); }
 // Eight consecutive tagged words -> eight fp16 values (as a uint4).  Bounded: on time-out returns false.
@@ -162,14 +179,15 @@ __device__ __forceinline__ bool poll1(const uint32_t *p, uint32_t tag, __half &o
   out = __half(0);
   return false;
 }
-// Warp 0 waits until every one of `count` progress words has reached sequence number `want` (producers may already be one
-// phase further).  This keeps the polling traffic to one warp per SM; the data words still carry tags, so a word whose store
-// lags behind its producer's progress word is caught when it is loaded.
-__device__ __forceinline__ bool wait_flags(const uint32_t *flags, int count, uint32_t want, const volatile int *abort_flag) {
+// Warp 0 waits until every one of rows x cols progress words (row stride 256) has reached sequence number `want` (producers
+// may already be one phase further).  This keeps the polling traffic to one warp per SM; the data words still carry tags, so
+// a word whose store lags behind its producer's progress word is caught when it is loaded.
+__device__ __forceinline__ bool wait_flags(const uint32_t *flags, int rows, int cols, uint32_t want, const volatile int *abort_flag) {
   const int lane = threadIdx.x & 31;
   for (int it = 0; it < POLL_LIMIT; ++it) {
     bool ok = true;
-    for (int i = lane; i < count; i += 32) ok &= (int)(ld_word(flags + i) - want) >= 0;
+    for (int r = 0; r < rows; ++r)
+      for (int i = lane; i < cols; i += 32) ok &= (int)(ld_word(flags + r * 256 + i) - want) >= 0;
     if (__all_sync(0xffffffffu, ok)) return true;
     if ((it & 63) == 63 && *abort_flag) break;
   }
@@ -184,6 +202,9 @@ struct PhaseInfo {
   __half *logits;   // fp16 output of the LM head (optional)
   uint32_t tag, out_seq;
   int epi, N, r0;
+  int out_ld, out_off;  // MLP activations: row stride and offset of the first feature inside the k window of down_proj
+  int push;         // 1: the rows are partial sums of a row-parallel linear, pushed into slot `push_slot` of every rank's buffer
+  size_t push_slot; // word offset of this rank's slot for this linear in a rank's partial-sum buffer
 };
 
 struct Shared {           // fixed-size part, placed after the ring / activations (128-byte aligned)
@@ -277,46 +298,112 @@ __device__ __forceinline__ Gamma load_gamma(const __half *gamma, int K) {
 // chunk's largest element, so the product differs from the exact fp16 x int4 dot product by far less than the final fp16
 // rounding.  The weights stay offset-binary nibbles u = q + 8; sum(q T) = sum(u T) - 8 sum(T) and the second term goes
 // into the accumulator's initial value (corr).  The fp16 phase (LM head) keeps x as fp16 in natural order.
-template <bool INT4>
-__device__ __forceinline__ void stage_x(Ctx &c, const uint32_t *src, uint32_t tag, const uint32_t *flags, int n_flags, uint32_t want, int K,
-                                        const __half *gamma, int trace_slot = 0) {
+// Tensor parallelism: v (eight fp16 values of x) += fp16(sum over ranks, in rank order, of the ranks' fp16 partial sums), so that
+// every rank computes the same words.
+__device__ __forceinline__ bool add_partial_sums(const uint32_t *parts, int n_parts, uint32_t part_tag, int B, int b, int K, int u, uint4 &v,
+                                              const volatile int *abort_flag) {
+  bool got = true;
+  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int r0 = 0; r0 < n_parts; r0 += 2) {  // two ranks' words in flight together
+    uint4 pa[2], pb[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (r0 + i < n_parts) {
+        const uint32_t *w = parts + ((size_t)(r0 + i) * B + b) * K + (size_t)u * 8;
+        pa[i] = ld_words(w);
+        pb[i] = ld_words(w + 4);
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (r0 + i < n_parts) {
+        const uint32_t all = pa[i].x & pa[i].y & pa[i].z & pa[i].w & pb[i].x & pb[i].y & pb[i].z & pb[i].w;
+        const uint32_t any = pa[i].x | pa[i].y | pa[i].z | pa[i].w | pb[i].x | pb[i].y | pb[i].z | pb[i].w;
+        uint4 pv = make_uint4(__byte_perm(pa[i].x, pa[i].y, 0x5410), __byte_perm(pa[i].z, pa[i].w, 0x5410), __byte_perm(pb[i].x, pb[i].y, 0x5410),
+                              __byte_perm(pb[i].z, pb[i].w, 0x5410));
+        if ((all >> 16) != part_tag || (any >> 16) != part_tag)  // not there yet: wait for this rank's words
+          got &= poll8(parts + ((size_t)(r0 + i) * B + b) * K + (size_t)u * 8, part_tag, pv, abort_flag);
+        const __half2 *ph = reinterpret_cast<const __half2 *>(&pv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t2 = __half22float2(ph[j]);
+          f[2 * j] += t2.x;
+          f[2 * j + 1] += t2.y;
+        }
+      }
+  }
+  __half *h = reinterpret_cast<__half *>(&v);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) h[j] = h_add(h[j], __float2half_rn(f[j]));
+  return got;
+}
+
+// Where a staging step takes its input from.
+struct StageSrc {
+  const uint32_t *x;        // tagged words [B][K]
+  uint32_t x_tag;
+  const uint32_t *flags;    // progress words to wait for first: rows x cols (row stride 256), sequence number `want`
+  int flag_rows, flag_cols;
+  uint32_t want;
+  // tensor parallelism: the input is x + the sum over ranks of the partial sums of a row-parallel linear
+  const uint32_t *parts;    // [n_parts][B][K] tagged words (nullptr: no partial sums)
+  int n_parts;
+  uint32_t part_tag;
+  uint32_t *x_out;          // where the sum is stored (units u with u % G == sm), tagged x_out_tag; nullptr: nowhere
+  uint32_t x_out_tag;
+  int lo_unit, hi_unit;     // 8-element units outside [lo_unit, hi_unit) are zero and are not loaded (window of a k slice)
+};
+
+template <bool INT4, bool TP>
+__device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, const __half *gamma, int trace_slot = 0) {
   const Params &p = c.p;
   const int tid = threadIdx.x;
   const int units = K / 8;
-  const Gamma gm = load_gamma(gamma, K);  // requested before the wait, used after it
+  const uint32_t tag = src.x_tag;
+  Gamma gm;
+  if (!TP) gm = load_gamma(gamma, K);  // requested before the wait, used after it
   unsigned long long *ts = (c.tr && trace_slot && tid == 0) ? c.tr + trace_slot : nullptr;
   if (ts) ts[0] = gtime();
   // First attempt at this thread's words of batch row 0 right away: an SM that arrives after all producers are done then
   // has its data one round trip earlier.  Words that are not there yet are fetched again after the wait.
-  uint4 v0[3];
+  uint4 v[3];
   unsigned have = 0;
 #pragma unroll
   for (int q = 0; q < 3; ++q) {
-    v0[q] = make_uint4(0, 0, 0, 0);
-    if (tid + q * NCT < units) {
-      const uint32_t *w = src + (size_t)(tid + q * NCT) * 8;
+    v[q] = make_uint4(0, 0, 0, 0);
+    const int u = tid + q * NCT;
+    if (u < units && u >= src.lo_unit && u < src.hi_unit) {
+      const uint32_t *w = src.x + (size_t)u * 8;
       const uint4 a = ld_words(w), b4 = ld_words(w + 4);
       const uint32_t all = a.x & a.y & a.z & a.w & b4.x & b4.y & b4.z & b4.w, any = a.x | a.y | a.z | a.w | b4.x | b4.y | b4.z | b4.w;
       if ((all >> 16) == tag && (any >> 16) == tag) {
-        v0[q] = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b4.x, b4.y, 0x5410), __byte_perm(b4.z, b4.w, 0x5410));
+        v[q] = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410), __byte_perm(b4.x, b4.y, 0x5410), __byte_perm(b4.z, b4.w, 0x5410));
         have |= 1u << q;
       }
     }
   }
-  if (tid < 32 && !wait_flags(flags, n_flags, want, &c.sh->abort)) {
+  if (tid < 32 && !wait_flags(src.flags, src.flag_rows, src.flag_cols, src.want, &c.sh->abort)) {
     c.sh->abort = 1;
     if (p.error_flag) atomicExch(p.error_flag, 10);
   }
   consumer_sync();
   if (ts) ts[1] = gtime();
   for (int b = 0; b < p.B; ++b) {
-    uint4 v[3];
     bool got = true;
 #pragma unroll
     for (int q = 0; q < 3; ++q) {
-      v[q] = make_uint4(0, 0, 0, 0);
-      if (b == 0 && (have >> q & 1)) v[q] = v0[q];
-      else if (tid + q * NCT < units) got &= poll8(src + (size_t)b * K + (size_t)(tid + q * NCT) * 8, tag, v[q], &c.sh->abort);
+      const int u = tid + q * NCT;
+      if (u >= units || u < src.lo_unit || u >= src.hi_unit) { v[q] = make_uint4(0, 0, 0, 0); continue; }
+      if (!(b == 0 && (have >> q & 1))) got &= poll8(src.x + (size_t)b * K + (size_t)u * 8, tag, v[q], &c.sh->abort);
+      if (TP && src.n_parts > 0) {
+        got &= add_partial_sums(src.parts, src.n_parts, src.part_tag, p.B, b, K, u, v[q], &c.sh->abort);
+        if (src.x_out && (u % c.G) == c.sm) {
+          const uint32_t *hw = reinterpret_cast<const uint32_t *>(&v[q]);
+          const uint32_t t = src.x_out_tag << 16;
+          uint32_t *dst = src.x_out + (size_t)b * K + (size_t)u * 8;
+          reinterpret_cast<uint4 *>(dst)[0] = make_uint4(t | (hw[0] & 0xFFFFu), t | (hw[0] >> 16), t | (hw[1] & 0xFFFFu), t | (hw[1] >> 16));
+          reinterpret_cast<uint4 *>(dst)[1] = make_uint4(t | (hw[2] & 0xFFFFu), t | (hw[2] >> 16), t | (hw[3] & 0xFFFFu), t | (hw[3] >> 16));
+        }
+      }
     }
     if (!got) {
       c.sh->abort = 1;
@@ -324,6 +411,7 @@ __device__ __forceinline__ void stage_x(Ctx &c, const uint32_t *src, uint32_t ta
     }
     if (ts && b == 0) ts[2] = gtime();
     __half rb = __half(0);
+    if (TP) gm = load_gamma(gamma, K);  // tp > 1: requested only now (registers), its latency hides behind the reduction below
     if (gamma) {
       float ss = 0.f;
 #pragma unroll
@@ -417,7 +505,7 @@ struct Split {
 
 // Finished sums of row tile `rt` of this SM: lane (g, tig) with tig < B holds batch tig, rows g (lo) and g + 8 (hi) of the tile.
 // Phases between layers write tagged words; the LM head keeps its arg-max and optionally writes fp16 logits.
-template <bool HEAD>
+template <bool HEAD, bool TP>
 __device__ __forceinline__ void tile_epilogue(const Params &p, const volatile PhaseInfo *pi, float lo, float hi, int rt, int lane, Best *best) {
   const int g = lane >> 2, b = lane & 3;
   if (b >= p.B) return;
@@ -427,7 +515,7 @@ __device__ __forceinline__ void tile_epilogue(const Params &p, const volatile Ph
   rt += pi->r0;
   if (!HEAD && epi == EPI_SWIGLU) {  // rows g / g + 8 are the gate / up feature rt * 8 + g
     const int n = rt * 8 + g;
-    if (n < N / 2) st_word(outw + (size_t)b * (N / 2) + n, tag, h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo))));
+    if (n < N / 2) st_word(outw + (size_t)b * pi->out_ld + pi->out_off + n, tag, h_mul(__float2half_rn(hi), swish_h(__float2half_rn(lo))));
     return;
   }
 #pragma unroll
@@ -436,10 +524,18 @@ __device__ __forceinline__ void tile_epilogue(const Params &p, const volatile Ph
     if (n >= N) continue;
     __half y = __float2half_rn(hr ? hi : lo);
     if (HEAD) {
-      const float f = __half2float(y);
-      if (f > best->v[b] || (f == best->v[b] && n < best->i[b])) { best->v[b] = f; best->i[b] = n; }
+      float f = __half2float(y);
+      if (TP && f == 0.f) f = -10000.0f;  // the tensor-parallel LM head reads exact zeros as -10000 (layers/lm_head.py:86-88)
+      const int id = TP ? n + p.vocab_off : n;
+      if (f > best->v[b] || (f == best->v[b] && id < best->i[b])) { best->v[b] = f; best->i[b] = id; }
       __half *logits = pi->logits;
       if (logits) logits[(size_t)b * N + n] = y;
+    } else if (TP && pi->push) {
+      // partial sum of a row-parallel linear: one copy into this rank's slot on every rank (the sum and the residual add
+      // happen in the next staging step, on every rank alike)
+      const uint32_t word = (tag << 16) | (uint32_t)__half_as_ushort(y);
+      const size_t at = pi->push_slot + (size_t)b * N + n;
+      for (int r = 0; r < p.tp; ++r) st_sys(p.peer_part[r] + at, word);
     } else {
       uint32_t *w = outw + (size_t)b * N + n;
       // the residual is the value this SM wrote to the same word one or two phases ago (or the embedding, which the first
@@ -471,7 +567,7 @@ struct TileRegs { uint4 a, b; uint32_t s; };
 // The loop body is what bounds the kernel once the stream flows, so it is kept to the instructions that the arithmetic
 // needs: two AND per packed word and one integer mma per 512 weights (INT4), operands and accumulator initialisers that
 // arrive from shared memory in fragment order, ring positions advanced without divisions.
-template <int WFMT>
+template <int WFMT, bool TP>
 __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best *best) {
   constexpr int TILE = WTraits<WFMT>::kTileBytes;
   constexpr bool I4 = (WFMT == PT_W_INT4);
@@ -546,7 +642,7 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best
     }
     if (++ch == nchunks) {  // this warp reached the end of row tile rt
       if (rt == first_rt && enters_midway) store_partial(0);
-      else tile_epilogue<!I4>(p, pi, acc0, acc1, rt, lane, best);  // had all of it
+      else tile_epilogue<!I4, TP>(p, pi, acc0, acc1, rt, lane, best);  // had all of it
       ch = 0;
       ++rt;
       acc0 = acc1 = 0.f;
@@ -588,11 +684,15 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best
       v0 += t.x;
       v1 += t.y;
     }
-    tile_epilogue<!I4>(p, pi, v0, v1, r, lane, best);
+    tile_epilogue<!I4, TP>(p, pi, v0, v1, r, lane, best);
   }
-  if (pi->out_seq) {  // tell the other SMs that this SM's rows of the phase are written
+  if (pi->out_seq) {  // tell the other SMs (of every rank, for pushed partial sums) that this SM's rows of the phase are written
     consumer_sync();
-    if (tid == 0) st_flag(p.flag_sm + c.sm, pi->out_seq);
+    if (TP && pi->push) {
+      if (tid < p.tp) st_sys(p.peer_flag[tid] + p.rank * 256 + c.sm, pi->out_seq);
+    } else if (tid == 0) {
+      st_flag(p.flag_sm + c.sm, pi->out_seq);
+    }
   }
 }
 
@@ -615,7 +715,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
   const int grp = (warp >> 2) < NGRP ? (warp >> 2) : -1;  // warps beyond the last full group only release stages
   const int step = c.step, n_active = step / PAGE + 1;
   const int n_units = p.B * p.n_head * n_active;
-  const int row_elems = 3 * p.d;
+  const int row_elems = 3 * p.dq;
   const __half *sin_r = p.sin_t + (size_t)step * (H / 2), *cos_r = p.cos_t + (size_t)step * (H / 2);
   for (int u0 = c.sm; u0 < n_units; u0 += MAXU * c.G) {
     const int nu = min(MAXU, (n_units - u0 + c.G - 1) / c.G);  // units of this pass: u0 + k G
@@ -633,10 +733,10 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
         for (int it = 0; it < POLL_LIMIT && !got; ++it) {
           w[0] = ld_word(qw);
           w[1] = ld_word(qw + H / 2);
-          w[2] = owner ? ld_word(qw + p.d) : w[0];
-          w[3] = owner ? ld_word(qw + p.d + H / 2) : w[0];
-          w[4] = owner ? ld_word(qw + 2 * p.d) : w[0];
-          w[5] = owner ? ld_word(qw + 2 * p.d + H / 2) : w[0];
+          w[2] = owner ? ld_word(qw + p.dq) : w[0];
+          w[3] = owner ? ld_word(qw + p.dq + H / 2) : w[0];
+          w[4] = owner ? ld_word(qw + 2 * p.dq) : w[0];
+          w[5] = owner ? ld_word(qw + 2 * p.dq + H / 2) : w[0];
           const uint32_t all = w[0] & w[1] & w[2] & w[3] & w[4] & w[5], any = w[0] | w[1] | w[2] | w[3] | w[4] | w[5];
           got = (all >> 16) == qkv_tag && (any >> 16) == qkv_tag;
           if ((it & 63) == 63 && sh->abort) break;
@@ -832,7 +932,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
         sh->abort = 1;
         if (p.error_flag) atomicExch(p.error_flag, 9);
       }
-      st_word(p.attnw + (size_t)b * p.d + (size_t)head * H + gt, attn_tag, __float2half_rn(o / Lsum));
+      st_word(p.attnw + (size_t)b * p.dq + (size_t)head * H + gt, attn_tag, __float2half_rn(o / Lsum));
       group_sync(grp);  // ps / ml may be reused by the group's next combine; the head's words are all issued
       if (gt == 0) st_flag(p.flag_head + hd, attn_seq);
     }
@@ -894,6 +994,7 @@ struct Producer {
     }
   }
 };
+template <bool TP>
 __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char *ring = smem;
@@ -913,9 +1014,8 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   }
   __syncthreads();
 
-  const int n_rt_qkv = 3 * p.d / 16, n_rt_o = p.d / 16, n_rt_gu = 2 * p.ffn / 16, n_rt_head = (p.vocab + 15) / 16;
-  const int nc_d = p.d / 128, nc_f = p.ffn / 128, nc_head = p.d / 32;
-  (void)nc_d; (void)nc_f;
+  const int n_rt_qkv = 3 * p.dq / 16, n_rt_o = p.d / 16, n_rt_gu = 2 * p.ffn_valid / 16, n_rt_head = (p.vocab + 15) / 16;
+  const int nc_d = p.d / 128, nc_q = p.dq / 128, nc_f = p.ffn / 128, nc_head = p.d / 32;
 
   if (warp == NCW) {
     // ---------------- producer: one lane walks the whole step's weight / KV stream of this SM
@@ -925,7 +1025,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
         const pt_llama_layer &L = p.layers[l];
         pr.push_matrix((const unsigned char *)L.qkv, n_rt_qkv, nc_d, TILE_I4);
         pr.push_attention(L, step);
-        pr.push_matrix((const unsigned char *)L.o, n_rt_o, nc_d, TILE_I4);
+        pr.push_matrix((const unsigned char *)L.o, n_rt_o, nc_q, TILE_I4);
         pr.push_matrix((const unsigned char *)L.gu, n_rt_gu, nc_d, TILE_I4);
         pr.push_matrix((const unsigned char *)L.down, n_rt_o, nc_f, TILE_I4);
       }
@@ -946,7 +1046,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
     const int b = i / (p.d / 8), u = i - b * (p.d / 8);
     if ((u % c.G) != c.sm) continue;
     int id = p.ids[(size_t)b * p.max_len + step];
-    id = min(max(id, 0), p.vocab - 1);
+    id = min(max(id, 0), p.emb_rows - 1);
     const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.emb + (size_t)id * p.d) + u);
     const uint32_t hw[4] = {v.x, v.y, v.z, v.w}, t = c.tag(0) << 16;
     uint32_t *dst = p.xw + (size_t)b * p.d + (size_t)u * 8;
@@ -960,30 +1060,66 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   // operands), which keeps the kernel small enough for the instruction cache and lets the compiler inline everything.
   unsigned long long *tr = p.trace ? p.trace + ((size_t)blockIdx.x * p.n_layer) * 32 : nullptr;
 #define PT_STAMP(k) do { if (tr && tid == 0) tr[l * 32 + (k)] = gtime(); } while (0)
+  int xcur = 0;  // which copy of x is current (tp > 1)
   for (int l = 0; l < p.n_layer; ++l) {
     const pt_llama_layer &L = p.layers[l];
     const int ph0 = 1 + 5 * l;
     PT_STAMP(0);
     for (int ph = 0; ph < 4; ++ph) {
-      const uint32_t *src;
+      // x lives in xw[cur] (two copies alternate when tp > 1, where every staging that follows a row-parallel linear forms
+      // x + sum of the ranks' partial sums and stores it into the other copy)
+      const bool tpar = TP;
+      const size_t xsz = (size_t)p.B * p.d, psz = (size_t)p.tp * p.B * p.d;
+      StageSrc src{};
       const __half *gamma;
       uint32_t *out;
-      int K, epi, n_rt, N, src_phase, out_phase;
-      if (ph == 0) { src = p.xw; src_phase = ph0 - 1; gamma = (const __half *)L.ln1; K = p.d; epi = EPI_QKV; n_rt = n_rt_qkv; out = p.qkvw; N = 3 * p.d; out_phase = ph0; }
-      else if (ph == 1) { src = p.attnw; src_phase = ph0 + 1; gamma = nullptr; K = p.d; epi = EPI_RESID; n_rt = n_rt_o; out = p.xw; N = p.d; out_phase = ph0 + 2; }
-      else if (ph == 2) { src = p.xw; src_phase = ph0 + 2; gamma = (const __half *)L.ln2; K = p.d; epi = EPI_SWIGLU; n_rt = n_rt_gu; out = p.actw; N = 2 * p.ffn; out_phase = ph0 + 3; }
-      else { src = p.actw; src_phase = ph0 + 3; gamma = nullptr; K = p.ffn; epi = EPI_RESID; n_rt = n_rt_o; out = p.xw; N = p.d; out_phase = ph0 + 4; }
-      const bool from_attn = (ph == 1);
+      int K, epi, n_rt, N, out_phase, push = 0, out_ld = 0, out_off = 0;
+      src.flags = p.flag_sm; src.flag_rows = 1; src.flag_cols = c.G;
+      src.lo_unit = 0; src.hi_unit = 1 << 30;
+      if (ph == 0) {
+        // input: the embedding (layer 0), or x + the down_proj partial sums of the previous layer
+        gamma = (const __half *)L.ln1; K = p.d; epi = EPI_QKV; n_rt = n_rt_qkv; out = p.qkvw; N = 3 * p.dq; out_phase = ph0;
+        if (tpar && l > 0) {
+          src.x = p.xw + xcur * xsz; src.x_tag = c.tag(ph0 - 2);   // written by the staging before gate|up of the previous layer
+          src.parts = p.peer_part[p.rank] + psz; src.n_parts = p.tp; src.part_tag = c.tag(ph0 - 1);
+          src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.want = c.seq(ph0 - 1);
+          src.x_out = p.xw + (xcur ^ 1) * xsz; src.x_out_tag = c.tag(ph0);
+        } else {
+          src.x = p.xw + xcur * xsz; src.x_tag = c.tag(ph0 - 1); src.want = c.seq(ph0 - 1);
+        }
+      } else if (ph == 1) {
+        src.x = p.attnw; src.x_tag = c.tag(ph0 + 1); src.flags = p.flag_head; src.flag_cols = p.B * p.n_head; src.want = c.seq(ph0 + 1);
+        gamma = nullptr; K = p.dq; epi = EPI_RESID; n_rt = n_rt_o; out = p.xw + xcur * xsz; N = p.d; out_phase = ph0 + 2;
+        push = tpar;
+      } else if (ph == 2) {
+        gamma = (const __half *)L.ln2; K = p.d; epi = EPI_SWIGLU; n_rt = n_rt_gu; out = p.actw; N = 2 * p.ffn_valid; out_phase = ph0 + 3;
+        out_ld = p.ffn; out_off = p.ffn_off;
+        if (tpar) {
+          src.x = p.xw + xcur * xsz; src.x_tag = (l == 0) ? c.tag(0) : c.tag(ph0);  // the embedding, or this layer's phase-0 staging
+          src.parts = p.peer_part[p.rank]; src.n_parts = p.tp; src.part_tag = c.tag(ph0 + 2);
+          src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.want = c.seq(ph0 + 2);
+          src.x_out = p.xw + (xcur ^ 1) * xsz; src.x_out_tag = c.tag(ph0 + 3);
+        } else {
+          src.x = p.xw; src.x_tag = c.tag(ph0 + 2); src.want = c.seq(ph0 + 2);
+        }
+      } else {
+        src.x = p.actw; src.x_tag = c.tag(ph0 + 3); src.want = c.seq(ph0 + 3);
+        src.lo_unit = p.ffn_off / 8; src.hi_unit = (p.ffn_off + p.ffn_valid) / 8;
+        gamma = nullptr; K = p.ffn; epi = EPI_RESID; n_rt = n_rt_o; out = p.xw + xcur * xsz; N = p.d; out_phase = ph0 + 4;
+        push = tpar;
+      }
       if (tid == 0) {
         PhaseInfo *w = &sh->phase;
         w->outw = out; w->logits = nullptr; w->tag = c.tag(out_phase); w->out_seq = c.seq(out_phase);
         w->epi = epi; w->N = N; w->r0 = (int)((long long)c.sm * n_rt / c.G);
+        w->out_ld = out_ld; w->out_off = out_off;
+        w->push = push; w->push_slot = (size_t)(ph == 3 ? 1 : 0) * psz + (size_t)p.rank * xsz;
       }
       c.tr = tr ? tr + l * 32 : nullptr;
-      stage_x<true>(c, src, c.tag(src_phase), from_attn ? p.flag_head : p.flag_sm, from_attn ? p.B * p.n_head : c.G, c.seq(src_phase), K, gamma,
-                    ph == 0 ? 20 : (ph == 3 ? 24 : (ph == 2 ? 28 : 0)));
+      stage_x<true, TP>(c, src, K, gamma, ph == 0 ? 20 : (ph == 3 ? 24 : (ph == 2 ? 28 : 0)));
+      if (src.x_out) xcur ^= 1;
       PT_STAMP(ph == 0 ? 1 : (ph == 1 ? 5 : (ph == 2 ? 8 : 10)));
-      linear_phase<PT_W_INT4>(c, n_rt, K / 128, nullptr);
+      linear_phase<PT_W_INT4, TP>(c, n_rt, K / 128, nullptr);
       PT_STAMP(ph == 0 ? 2 : (ph == 1 ? 6 : (ph == 2 ? 9 : 11)));
       if (ph == 1) PT_STAMP(7);
       if (ph == 0) {
@@ -1005,9 +1141,24 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
     PhaseInfo *w = &sh->phase;
     w->outw = nullptr; w->logits = p.logits; w->tag = 0u; w->out_seq = 0u;
     w->epi = EPI_HEAD; w->N = p.vocab; w->r0 = (int)((long long)c.sm * n_rt_head / c.G);
+    w->out_ld = 0; w->out_off = 0; w->push = 0; w->push_slot = 0;
   }
-  stage_x<false>(c, p.xw, c.tag(5 * p.n_layer), p.flag_sm, c.G, c.seq(5 * p.n_layer), p.d, p.norm);
-  linear_phase<PT_W_FP16>(c, n_rt_head, nc_head, &best);
+  {
+    const int last = 5 * p.n_layer;  // the last down_proj phase
+    StageSrc src{};
+    src.x = p.xw + (size_t)xcur * p.B * p.d;
+    src.lo_unit = 0; src.hi_unit = 1 << 30;
+    if (TP) {
+      src.x_tag = c.tag(last - 1);   // staging before gate|up of the last layer
+      src.parts = p.peer_part[p.rank] + (size_t)p.tp * p.B * p.d; src.n_parts = p.tp; src.part_tag = c.tag(last);
+      src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.flag_cols = c.G; src.want = c.seq(last);
+    } else {
+      src.x_tag = c.tag(last);
+      src.flags = p.flag_sm; src.flag_rows = 1; src.flag_cols = c.G; src.want = c.seq(last);
+    }
+    stage_x<false, TP>(c, src, p.d, p.norm);
+  }
+  linear_phase<PT_W_FP16, TP>(c, n_rt_head, nc_head, &best);
   for (int b = 0; b < p.B; ++b) {
     float v = best.v[b];
     int i = best.i[b];
@@ -1047,6 +1198,39 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
         const float ov = __shfl_xor_sync(0xffffffffu, v, o);
         const int oi = __shfl_xor_sync(0xffffffffu, i, o);
         if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+      }
+      if (TP) {
+        // vocabulary-parallel head (layers/lm_head.py:75-116): every rank sends its best (value, id) to every rank, and each
+        // takes the first maximum in rank order, so all ranks append the same id
+        const uint32_t sq = c.seq(5 * p.n_layer + 1);
+        if (lane < p.tp) {
+          uint2 *dst = p.peer_cand[lane] + ((size_t)p.rank * BMAX + b) * 2;
+          st_sys2(dst, __float_as_uint(v), sq);
+          st_sys2(dst + 1, (uint32_t)i, sq);
+        }
+        float rv = -INFINITY;
+        int ri = 0x7fffffff;
+        if (lane < p.tp) {
+          const uint2 *srcc = p.peer_cand[p.rank] + ((size_t)lane * BMAX + b) * 2;
+          bool got = false;
+          for (int it = 0; it < POLL_LIMIT && !got; ++it) {
+            const uint2 a0 = ld_sys2(srcc), a1 = ld_sys2(srcc + 1);
+            if (a0.y == sq && a1.y == sq) { rv = __uint_as_float(a0.x); ri = (int)a1.x; got = true; }
+            if ((it & 63) == 63 && sh->abort) break;
+          }
+          if (!got) {
+            sh->abort = 1;
+            if (p.error_flag) atomicExch(p.error_flag, 11);
+          }
+        }
+        v = rv;
+        i = ri;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+          if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+        }
       }
       if (lane == 0) {
         p.next_ids[b] = i;
@@ -1123,13 +1307,24 @@ extern "C" size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_
   return 256 + 1024 + al(heads * sizeof(uint32_t)) + al(heads * max_pages * 2 * sizeof(uint2)) + al(heads * max_pages * head_dim * sizeof(uint2)) + 2 * al((size_t)batch * 256 * sizeof(float));
 }
 
+extern "C" size_t pt_llama_tp_buffer_bytes(int batch, int d_model, int tp_size) {
+  return (size_t)2 * tp_size * batch * d_model * sizeof(uint32_t) + (size_t)tp_size * 256 * sizeof(uint32_t) + (size_t)tp_size * mk::BMAX * 2 * sizeof(uint2);
+}
+
 extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   PT_REQUIRE(a, "pt_llama_decode_step: null args");
   PT_REQUIRE(a->batch >= 1 && a->batch <= mk::BMAX, "pt_llama_decode_step: batch=%d outside 1..%d (larger batches use the per-op kernels)", a->batch,
              mk::BMAX);
   PT_REQUIRE(a->head_dim == mk::H && a->page_size == mk::PAGE, "pt_llama_decode_step: needs head_dim=%d and page_size=%d", mk::H, mk::PAGE);
-  PT_REQUIRE(a->d_model % 128 == 0 && a->ffn % 128 == 0 && a->d_model == a->n_head * a->head_dim && a->d_model <= 96 * 128 && a->ffn <= 96 * 128,
-             "pt_llama_decode_step: d_model=%d ffn=%d must be multiples of 128 (at most 12288) with d_model = n_head * head_dim", a->d_model, a->ffn);
+  const int tp = a->tp_size > 1 ? a->tp_size : 1;
+  PT_REQUIRE(tp <= 8 && a->tp_rank >= 0 && a->tp_rank < tp, "pt_llama_decode_step: tp_size=%d tp_rank=%d (at most 8 ranks)", a->tp_size, a->tp_rank);
+  PT_REQUIRE(a->d_model % 128 == 0 && a->ffn % 128 == 0 && a->d_model == a->n_head * a->head_dim * tp && a->d_model <= 96 * 128 && a->ffn <= 96 * 128,
+             "pt_llama_decode_step: d_model=%d ffn=%d must be multiples of 128 (at most 12288) with d_model = tp * n_head * head_dim", a->d_model, a->ffn);
+  const int ffn_off = tp > 1 ? a->ffn_offset : 0, ffn_valid = tp > 1 ? a->ffn_valid : a->ffn;
+  PT_REQUIRE(ffn_off >= 0 && ffn_valid > 0 && ffn_off % 8 == 0 && ffn_valid % 8 == 0 && ffn_off + ffn_valid <= a->ffn,
+             "pt_llama_decode_step: MLP slice [%d, %d) must be a multiple-of-8 range inside the window of %d columns", ffn_off, ffn_off + ffn_valid, a->ffn);
+  if (tp > 1)
+    for (int r = 0; r < tp; ++r) PT_REQUIRE(a->tp_buffers[r], "pt_llama_decode_step: tp_buffers[%d] is null", r);
   PT_REQUIRE((2 * a->ffn) % 16 == 0 && a->vocab > 0 && a->n_layer > 0 && a->max_len > 0 && a->max_pages * mk::PAGE >= a->max_len,
              "pt_llama_decode_step: bad shape");
   PT_REQUIRE(a->layers && a->norm && a->head && a->emb && a->ids && a->step_dev && a->page_table && a->rope_sin && a->rope_cos && a->x && a->qkv &&
@@ -1145,13 +1340,26 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
     int dev = 0, v = 0;
     PT_CUDA(cudaGetDevice(&dev));
     PT_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    PT_CUDA(cudaFuncSetAttribute(mk::llama_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
+    PT_CUDA(cudaFuncSetAttribute(mk::llama_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
+    PT_CUDA(cudaFuncSetAttribute(mk::llama_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
     smem_max = (size_t)v;
   }
   PT_REQUIRE(n_sm <= 256, "pt_llama_decode_step: %d SMs exceed the candidate buffer", n_sm);
 
   mk::Params p{};
   p.B = a->batch; p.d = a->d_model; p.n_head = a->n_head; p.ffn = a->ffn; p.vocab = a->vocab; p.n_layer = a->n_layer;
+  p.tp = tp; p.rank = tp > 1 ? a->tp_rank : 0; p.dq = a->n_head * a->head_dim; p.ffn_off = ffn_off; p.ffn_valid = ffn_valid;
+  p.vocab_off = tp > 1 ? a->vocab_offset : 0;
+  p.emb_rows = tp > 1 ? a->emb_rows : a->vocab;
+  PT_REQUIRE(p.emb_rows > 0, "pt_llama_decode_step: emb_rows=%d", p.emb_rows);
+  for (int r = 0; r < tp && tp > 1; ++r) {
+    // exchange buffer of rank r: partial sums [2][tp][B][d] | progress words [tp][256] | arg-max candidates [tp][BMAX][2]
+    char *base = (char *)a->tp_buffers[r];
+    const size_t part_bytes = (size_t)2 * tp * a->batch * a->d_model * sizeof(uint32_t);
+    p.peer_part[r] = (uint32_t *)base;
+    p.peer_flag[r] = (uint32_t *)(base + part_bytes);
+    p.peer_cand[r] = (uint2 *)(base + part_bytes + (size_t)tp * 256 * sizeof(uint32_t));
+  }
   p.max_len = a->max_len; p.max_pages = a->max_pages; p.pad_id = a->pad_id; p.eos_id = a->eos_id;
   p.eps = a->norm_eps;
   p.score_scale = __float2half_rn(a->score_scale);
@@ -1189,7 +1397,8 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
     }
   }
   void *kargs[] = {(void *)&p};
-  cudaError_t e = cudaLaunchCooperativeKernel((const void *)mk::llama_step_kernel, dim3(n_sm), dim3(mk::THREADS), kargs, smem, as_stream(stream));
+  const void *kernel = tp > 1 ? (const void *)mk::llama_step_kernel<true> : (const void *)mk::llama_step_kernel<false>;
+  cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(n_sm), dim3(mk::THREADS), kargs, smem, as_stream(stream));
   if (e != cudaSuccess) return pt::set_error(PT_ERR_CUDA, "pt_llama_decode_step: %s", cudaGetErrorString(e));
   PT_LAUNCH_CHECK("pt_llama_decode_step");
   return PT_OK;

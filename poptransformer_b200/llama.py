@@ -136,9 +136,13 @@ class LlamaDecoder:
         self.attn_ws = ops.attn_workspace(B, self.h_loc, c.head_dim, self.caches[0].max_pages, dev)
         self.lin_ws = ops.linear_workspace(B, max(3 * self.d_loc, 2 * self.f_loc, d, self.logits.shape[1]), 16, dev)
         self.graph = None
-        # The persistent whole-step kernel covers the single-GPU, INT4, batch <= 2 case; everything else takes the per-op kernels.
-        can_persist = (tp == 1 and batch <= 2 and c.head_dim == 128 and page_size == 64 and self.layers[0]["qkv"].wfmt == ops.W_INT4
+        # The persistent whole-step kernel covers INT4, batch <= 2, on one GPU or tensor-parallel over up to 8 (the all-reduces are
+        # then fused into the kernel as peer stores); everything else takes the per-op kernels and NCCL.
+        can_persist = (batch <= 2 and c.head_dim == 128 and page_size == 64 and self.layers[0]["qkv"].wfmt == ops.W_INT4
                        and d % 128 == 0 and f % 128 == 0)
+        if tp > 1:
+            can_persist = (can_persist and tp <= 8 and self.d_loc % 128 == 0 and self.f_loc % 8 == 0 and self.o_ks.offset == 0
+                           and self.o_ks.width == self.d_loc and self.down_ks.offset % 8 == 0)
         self.persistent = can_persist if persistent is None else (persistent and can_persist)
         if self.persistent:
             L = ops._lib.lib()
@@ -161,9 +165,10 @@ class LlamaDecoder:
                 arr[i].ln1, arr[i].ln2 = lay["ln1"].data_ptr(), lay["ln2"].data_ptr()
                 arr[i].pool = self.caches[i].pool.data_ptr()
             self.mk_layers = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(dev)
-            self.mk_ws = torch.zeros(L.pt_llama_step_workspace_bytes(B, c.n_head, c.head_dim, self.caches[0].max_pages), dtype=torch.uint8, device=dev)
+            self.mk_ws = torch.zeros(L.pt_llama_step_workspace_bytes(B, self.h_loc, c.head_dim, self.caches[0].max_pages), dtype=torch.uint8, device=dev)
             a = ops._lib.LlamaStepArgs()
-            a.batch, a.d_model, a.n_head, a.head_dim, a.ffn, a.vocab, a.n_layer = B, d, c.n_head, c.head_dim, f, c.vocab, c.n_layer
+            a.batch, a.d_model, a.n_head, a.head_dim, a.n_layer = B, d, self.h_loc, c.head_dim, c.n_layer
+            a.ffn, a.vocab = self.down_ks.width, (self.vocab_loc if tp > 1 else c.vocab)
             a.max_len, a.page_size, a.max_pages, a.pad_id, a.eos_id = c.max_len, page_size, self.caches[0].max_pages, self.pad_id, self.eos_id
             a.norm_eps, a.score_scale = c.eps, self.score_scale
             a.layers, a.norm, a.head, a.emb = self.mk_layers.data_ptr(), self.norm.data_ptr(), self.head.packed_w.data_ptr(), self.emb.data_ptr()
@@ -171,8 +176,24 @@ class LlamaDecoder:
             a.ids, a.step_dev, a.stop_mask, a.next_ids = self.ids.data_ptr(), self.step_t.data_ptr(), self.stop_mask.data_ptr(), self.next_ids.data_ptr()
             a.page_table = self.caches[0].page_table.data_ptr()
             # the kernel's own activation scratch: 32-bit words (fp16 value + phase tag), zeroed once
-            self.mk_act = [torch.zeros((B, n), dtype=torch.int32, device=dev) for n in (d, 3 * d, d, f)]
+            self.mk_act = [torch.zeros((B, n), dtype=torch.int32, device=dev)
+                           for n in ((2 if tp > 1 else 1) * d, 3 * self.d_loc, self.d_loc, self.down_ks.width)]
             a.x, a.qkv, a.attn, a.act = (t.data_ptr() for t in self.mk_act)
+            if tp > 1:
+                # exchange buffer for the fused all-reduces: symmetric memory, every rank maps every rank's buffer; plain peer
+                # loads / stores only (no multicast object is requested)
+                import torch.distributed._symmetric_memory as symm_mem
+                nbytes = L.pt_llama_tp_buffer_bytes(B, d, tp)
+                grp = group if group is not None else torch.distributed.group.WORLD
+                self.tp_buf = symm_mem.empty((nbytes + 3) // 4, dtype=torch.int32, device=dev)
+                self.tp_buf.zero_()
+                self.tp_hdl = symm_mem.rendezvous(self.tp_buf, grp)
+                a.tp_size, a.tp_rank = tp, r
+                a.ffn_offset, a.ffn_valid, a.vocab_offset, a.emb_rows = self.down_ks.offset, self.f_loc, r * self.vocab_loc, c.vocab
+                for i in range(tp):
+                    a.tp_buffers[i] = int(self.tp_hdl.buffer_ptrs[i])
+                torch.cuda.synchronize()
+                torch.distributed.barrier(group=grp)
             a.logits = self.logits.data_ptr() if keep_logits else None
             a.workspace, a.workspace_bytes = self.mk_ws.data_ptr(), self.mk_ws.numel()
             a.error_flag = self.error_flag.data_ptr()
