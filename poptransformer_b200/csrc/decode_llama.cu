@@ -999,7 +999,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char *ring = smem;
   unsigned char *xs = smem + (size_t)p.ns * STAGE_BYTES;
-  Shared *sh = reinterpret_cast<Shared *>(xs + (((size_t)BMAX * p.xs_stride + 127) / 128) * 128);
+  Shared *sh = reinterpret_cast<Shared *>(xs + (((size_t)p.B * p.xs_stride + 127) / 128) * 128);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int step = *p.step;
 
@@ -1383,7 +1383,7 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
 
   const int kmax = std::max(a->d_model, a->ffn);
   p.xs_stride = (kmax * 2) | 64;
-  const size_t fixed = (((size_t)mk::BMAX * p.xs_stride + 127) / 128) * 128 + sizeof(mk::Shared) + 128;
+  const size_t fixed = (((size_t)p.B * p.xs_stride + 127) / 128) * 128 + sizeof(mk::Shared) + 128;
   PT_REQUIRE(smem_max > fixed + 3 * (size_t)mk::STAGE_BYTES, "pt_llama_decode_step: shared memory too small");
   p.ns = (int)std::min<size_t>(16, (smem_max - fixed) / mk::STAGE_BYTES);
   const size_t smem = (size_t)p.ns * mk::STAGE_BYTES + fixed;

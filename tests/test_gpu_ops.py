@@ -390,3 +390,51 @@ def test_embedding_and_step_containers(cuda):
         ops.step_containers(ids_t, step_t, dev(nxt, cuda), pad)
         ids, step, _ = O.step_containers(ids, step, nxt, pad)
         assert np.array_equal(ids_t.cpu().numpy(), ids) and step_t.item() == step
+
+
+# ------------------------------------------------------------------ beam reorder of the paged cache, TP head ops
+def test_kv_reorder_pages_and_table(cuda):
+    """Row r continues from row parent[r]: full pages are shared through the page table, the page being filled is copied
+    into the row's spare page.  Checked through the reference-layout export, twice in a row (spare pages swap roles)."""
+    from poptransformer_b200 import _lib, ops
+    L = _lib.lib()
+    rows, n_kv, hd, page, max_len, step = 4, 2, 128, 64, 200, 150
+    kc = ops.PagedKVCache(rows, n_kv, hd, max_len, page, cuda, extra_pages=rows)
+    g = torch.Generator(device=cuda).manual_seed(3)
+    kc.pool.copy_(torch.randn(kc.pool.shape, generator=g, device=cuda).to(torch.float16))
+    spare = (torch.arange(rows, dtype=torch.int32, device=cuda) + rows * kc.max_pages).contiguous()
+    tmp = torch.empty_like(kc.page_table)
+    step_t = torch.tensor([step], dtype=torch.int32, device=cuda)
+    dense = kc.export(step_t, max_len).cpu().numpy()
+    for parent in ([2, 2, 0, 1], [3, 0, 0, 2]):
+        par = torch.tensor(parent, dtype=torch.int32, device=cuda)
+        ops.check(L.pt_kv_reorder_pages(ops._ptr(kc.pool), ops._ptr(kc.page_table), ops._ptr(spare), ops._ptr(par), ops._ptr(step_t), rows, n_kv, hd,
+                                        page, kc.max_pages, ops._stream()), "pt_kv_reorder_pages")
+        ops.check(L.pt_kv_reorder_table(ops._ptr(kc.page_table), ops._ptr(tmp), ops._ptr(spare), ops._ptr(par), ops._ptr(step_t), rows, page,
+                                        kc.max_pages, ops._stream()), "pt_kv_reorder_table")
+        got = kc.export(step_t, max_len).cpu().numpy()
+        dense = O.kv_reorder_dense(dense, parent)
+        assert np.array_equal(got.view(np.uint16), dense.view(np.uint16))
+        # every row owns its current page exclusively (appending to one row must not touch another)
+        cur = kc.page_table[:, step // page].cpu().numpy()
+        assert len(set(cur.tolist())) == rows and not set(cur.tolist()) & set(spare.cpu().numpy().tolist())
+
+
+def test_lm_head_tp_ops(cuda):
+    from poptransformer_b200 import _lib, ops
+    L = _lib.lib()
+    r = rng(21)
+    tp, rows, vocab = 4, 3, 1001
+    per = -(-vocab // tp)
+    full = r.standard_normal((rows, per * tp)).astype(np.float16)
+    full[:, vocab:] = 0                       # zero-padded shard rows
+    full[1, 5] = 0                            # an exact zero inside the vocabulary is read as -10000 too
+    shards = [full[:, k * per:(k + 1) * per].copy() for k in range(tp)]
+    vals = torch.empty((tp, rows), dtype=torch.float16, device=cuda)
+    ids = torch.empty((tp, rows), dtype=torch.int32, device=cuda)
+    for k in range(tp):
+        ops.check(L.pt_lm_head_local_topk(ops._ptr(dev(shards[k], cuda)), rows, per, k * per, ops._ptr(vals[k]), ops._ptr(ids[k]), ops._stream()),
+                  "pt_lm_head_local_topk")
+    nxt = torch.empty(rows, dtype=torch.int32, device=cuda)
+    ops.check(L.pt_lm_head_tp_pick(ops._ptr(vals), ops._ptr(ids), tp, rows, ops._ptr(nxt), ops._stream()), "pt_lm_head_tp_pick")
+    assert np.array_equal(nxt.cpu().numpy(), O.lm_head_tp_merge(shards, vocab))
