@@ -41,6 +41,34 @@ def llama_state_dict(n_layer, d_model, n_head, ffn, vocab, seed=0, device="cpu",
     return sd
 
 
+def gpt2_state_dict(n_layer, d_model, n_head, vocab, n_positions, seed=0, device="cpu"):
+    """GPT-2 architecture with the reference's key names after its checkpoint pre-processing (gpt2/model.py:154-166): linear
+    weights [out, in], the query third of c_attn (weight and bias) multiplied by 1/sqrt(head_size).  fp16, N(0, 0.02);
+    LayerNorm weights 1 + N(0, 0.02), biases N(0, 0.02)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    sd = {"transformer.wte.weight": _normal((vocab, d_model), gen, device), "transformer.wpe.weight": _normal((n_positions, d_model), gen, device)}
+    scale = float(1.0 / (d_model // n_head) ** 0.5)
+
+    def ln(key):
+        sd[key + ".weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+        sd[key + ".bias"] = _normal((d_model,), gen, device)
+
+    for i in range(n_layer):
+        p = f"transformer.h.{i}."
+        ln(p + "ln_1")
+        w, b = _normal((3 * d_model, d_model), gen, device).float(), _normal((3 * d_model,), gen, device).float()
+        w[:d_model] *= scale
+        b[:d_model] *= scale
+        sd[p + "attn.c_attn.weight"], sd[p + "attn.c_attn.bias"] = w.to(torch.float16), b.to(torch.float16)
+        sd[p + "attn.c_proj.weight"], sd[p + "attn.c_proj.bias"] = _normal((d_model, d_model), gen, device), _normal((d_model,), gen, device)
+        ln(p + "ln_2")
+        sd[p + "mlp.c_fc.weight"], sd[p + "mlp.c_fc.bias"] = _normal((4 * d_model, d_model), gen, device), _normal((4 * d_model,), gen, device)
+        sd[p + "mlp.c_proj.weight"], sd[p + "mlp.c_proj.bias"] = _normal((d_model, 4 * d_model), gen, device), _normal((d_model,), gen, device)
+    ln("transformer.ln_f")
+    return sd
+
+
 def prompt_ids(batch, prompt_len, max_len, vocab, pad_id, seed=0):
     """Uniform-random prompt ids excluding pad_id, right-padded to max_len with pad_id (int32, CPU)."""
     gen = torch.Generator().manual_seed(seed)

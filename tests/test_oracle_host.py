@@ -139,3 +139,42 @@ def test_c_restatement_matches_numpy_oracle():
         ka, kb = a.kv[0][0].cache[0], b.kcache(0)        # layer-0 K cache: same values up to fp16 rounding flips of the matmul sums
         assert (ka.view(np.uint16) == kb.view(np.uint16)).mean() > 0.97
         np.testing.assert_allclose(ka.astype(np.float32), kb.astype(np.float32), rtol=4e-3, atol=1e-3)
+
+
+def test_gpt2_oracle_matches_plain_fp32_transformer():
+    """The step-by-step fp16 restatement of the reference's GPT-2 decode graph (shift-right KV cache, additive mask, NormCE,
+    pre-scaled query, tied head) against a plain float32 causal transformer over the whole sequence."""
+    import math
+    from oracle import gpt2_np
+    from poptransformer_b200 import synth
+    dims = dict(n_layer=2, d_model=128, n_head=2, vocab=300, n_positions=32)
+    T = 12
+    sd = {k: v.numpy() for k, v in synth.gpt2_state_dict(**dims, seed=4).items()}
+    orc = gpt2_np.GPT2Oracle(gpt2_np.GPT2Config(**dims, max_len=T), sd, 1)
+    ids = synth.prompt_ids(1, T, T, dims["vocab"], dims["vocab"] - 1, seed=5).numpy()
+    got = np.stack([orc.logits(ids[:, t], t)[0][0].astype(np.float32) for t in range(T)])
+
+    f = lambda k: sd[k].astype(np.float32)
+    d, nh = dims["d_model"], dims["n_head"]
+    hs = d // nh
+
+    def ln(x, p):
+        mu, var = x.mean(-1, keepdims=True), x.var(-1, keepdims=True)
+        return (x - mu) / np.sqrt(var + 1e-5) * f(p + ".weight") + f(p + ".bias")
+
+    x = f("transformer.wte.weight")[ids[0]] + f("transformer.wpe.weight")[:T]
+    causal = np.triu(np.full((T, T), -np.inf, np.float32), 1)
+    for i in range(dims["n_layer"]):
+        p = f"transformer.h.{i}."
+        qkv = ln(x, p + "ln_1") @ f(p + "attn.c_attn.weight").T + f(p + "attn.c_attn.bias")
+        q, k, v = (qkv[:, j * d:(j + 1) * d].reshape(T, nh, hs).transpose(1, 0, 2) for j in range(3))
+        s = q @ k.transpose(0, 2, 1) + causal                       # the 1/sqrt(hs) is already in the query weights
+        pr = np.exp(s - s.max(-1, keepdims=True))
+        pr /= pr.sum(-1, keepdims=True)
+        a = (pr @ v).transpose(1, 0, 2).reshape(T, d)
+        x = x + a @ f(p + "attn.c_proj.weight").T + f(p + "attn.c_proj.bias")
+        h = ln(x, p + "ln_2") @ f(p + "mlp.c_fc.weight").T + f(p + "mlp.c_fc.bias")
+        h = 0.5 * h * (1 + np.vectorize(math.erf)(h / math.sqrt(2.0)))
+        x = x + h @ f(p + "mlp.c_proj.weight").T + f(p + "mlp.c_proj.bias")
+    exp = ln(x, "transformer.ln_f") @ f("transformer.wte.weight").T
+    np.testing.assert_allclose(got, exp, rtol=3e-2, atol=3e-2)
