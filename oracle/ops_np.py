@@ -278,6 +278,33 @@ def llama_rope_apply(x, sin_row, cos_row):
     return add_f16(mul_f16(x, cos), mul_f16(rot, sin))
 
 
+def chatglm2_rope_tables(max_len, head_dim):
+    """fixed_pos_embedding (chatglm2/attention.py:77-96) with dim = rotary_dim // 2 = head_dim // 2: inv_freq float32 for
+    i = 0, 2, ... < dim; angle = float32(position) * inv_freq in float32, cast to fp16; sin / cos of the fp16 angle, fp16.
+    The concat(freqs, freqs) of the reference makes both halves equal: one row holds the dim // 2 distinct values."""
+    dim = head_dim // 2
+    inv_freq = np.array([1.0 / (10000 ** (i / dim)) for i in range(0, dim, 2)]).astype(F32)
+    ang = (np.arange(max_len, dtype=F32)[:, None] * inv_freq[None, :]).astype(F32).astype(F16)
+    return np.sin(f32(ang)).astype(F16), np.cos(f32(ang)).astype(F16)
+
+
+def chatglm2_rope_apply(x, sin_row, cos_row):
+    """rotary_embedding / apply_rotary_pos_emb / rotate_half (chatglm2/attention.py:98-151): only the first half of each head
+    is rotated; there, consecutive pairs (x[2i], x[2i+1]) are de-interleaved, y = fp16(fp16(y * cos) + fp16(rot(y) * sin))
+    with rot = concat(-odd, even), and interleaved again.  x [..., H]; sin / cos rows [H/4]."""
+    x = np.asarray(x, dtype=F16)
+    h = x.shape[-1]
+    x1, x2 = x[..., : h // 2], x[..., h // 2:]
+    y = np.concatenate([x1[..., 0::2], x1[..., 1::2]], axis=-1)                       # [even | odd]
+    sin = np.concatenate([sin_row, sin_row]).astype(F16)
+    cos = np.concatenate([cos_row, cos_row]).astype(F16)
+    rot = np.concatenate([(-f32(y[..., h // 4:])).astype(F16), y[..., : h // 4]], axis=-1)
+    y = add_f16(mul_f16(y, cos), mul_f16(rot, sin))
+    out1 = np.empty_like(x1)
+    out1[..., 0::2], out1[..., 1::2] = y[..., : h // 4], y[..., h // 4:]
+    return np.concatenate([out1, x2], axis=-1)
+
+
 # --------------------------------------------------------------------------- attention core
 def decode_mask(batch, max_len, step):
     """Additive mask in the shift-cache frame (poptransformer/models/base_model.py:258-262,

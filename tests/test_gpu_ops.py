@@ -270,7 +270,8 @@ def test_kv_cache_pipeline(cuda):
 
 # ------------------------------------------------------------------ fused RoPE + paged append + attention
 @pytest.mark.parametrize("B,N,G,H,L,page,mode", [(1, 4, 4, 128, 40, 16, "llama"), (2, 8, 8, 128, 150, 64, "llama"),
-                                                (2, 4, 4, 64, 70, 32, "gpt2"), (2, 8, 2, 128, 70, 64, "none_gqa")])
+                                                (2, 4, 4, 64, 70, 32, "gpt2"), (2, 8, 2, 128, 70, 64, "none_gqa"),
+                                                (2, 8, 2, 128, 70, 64, "chatglm2")])
 def test_kv_append_attn(cuda, B, N, G, H, L, page, mode):
     from poptransformer_b200 import ops
     from poptransformer_b200.llama import rope_tables
@@ -278,6 +279,7 @@ def test_kv_append_attn(cuda, B, N, G, H, L, page, mode):
     sin_o, cos_o = O.llama_rope_tables(L, H)
     sin_t, cos_t = rope_tables(L, H, cuda)
     assert np.array_equal(sin_t.cpu().numpy().view(np.uint16), sin_o.view(np.uint16))
+    sin_c, cos_c = O.chatglm2_rope_tables(L, H)
     cache = ops.PagedKVCache(B, G, H, L, page, cuda)
     # scramble the page table to prove the indirection is honoured
     perm = torch.randperm(B * cache.max_pages, generator=torch.Generator().manual_seed(0)).to(torch.int32)
@@ -295,17 +297,21 @@ def test_kv_append_attn(cuda, B, N, G, H, L, page, mode):
         if mode == "llama":
             q = O.llama_rope_apply(q, sin_o[step], cos_o[step])
             k = O.llama_rope_apply(k, sin_o[step], cos_o[step])
+        if mode == "chatglm2":       # multi-query groups, interleaved pairs on the first half of each head, fp16 softmax
+            q = O.chatglm2_rope_apply(q, sin_c[step], cos_c[step])
+            k = O.chatglm2_rope_apply(k, sin_c[step], cos_c[step])
         past = O.kv_cache(st_o, step, np.stack([k, v]), L, 3, 1)          # [2,B,G,L,H]
         step_t.fill_(step)
         kw = dict(rope_mode=ops.ROPE_LLAMA, softmax_mode=ops.SOFTMAX_F32, score_scale=scale, rope_sin=sin_t, rope_cos=cos_t) if mode == "llama" \
-            else dict(rope_mode=ops.ROPE_NONE, softmax_mode=ops.SOFTMAX_F16 if mode == "gpt2" else ops.SOFTMAX_F32,
+            else dict(rope_mode=ops.ROPE_CHATGLM2, softmax_mode=ops.SOFTMAX_F16, score_scale=scale, rope_sin=dev(sin_c, cuda),
+                      rope_cos=dev(cos_c, cuda)) if mode == "chatglm2" else dict(rope_mode=ops.ROPE_NONE, softmax_mode=ops.SOFTMAX_F16 if mode == "gpt2" else ops.SOFTMAX_F32,
                       score_scale=1.0 if mode == "gpt2" else scale)
         got = ops.kv_append_attn(dev(qkv, cuda), step_t, cache, N, workspace=ws, error_flag=err, **kw).cpu().numpy()
         if step % 7 == 0 or step == L - 1:
             rep = N // G
             K = np.repeat(past[0], rep, axis=1)
             V = np.repeat(past[1], rep, axis=1)
-            exp = O.attention_decode(q, K, V, O.decode_mask(B, L, step), H, "float16" if mode == "gpt2" else "float32",
+            exp = O.attention_decode(q, K, V, O.decode_mask(B, L, step), H, "float16" if mode in ("gpt2", "chatglm2") else "float32",
                                      pre_scaled=(mode == "gpt2")).reshape(B, N * H)
             np.testing.assert_allclose(got.astype(np.float32), exp.astype(np.float32), rtol=2e-2, atol=2e-3, err_msg=f"step {step}")
             # cache contents, exported to the reference layout, are bit-exact

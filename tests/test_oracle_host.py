@@ -178,3 +178,18 @@ def test_gpt2_oracle_matches_plain_fp32_transformer():
         x = x + h @ f(p + "mlp.c_proj.weight").T + f(p + "mlp.c_proj.bias")
     exp = ln(x, "transformer.ln_f") @ f("transformer.wte.weight").T
     np.testing.assert_allclose(got, exp, rtol=3e-2, atol=3e-2)
+
+
+def test_chatglm2_rope_is_a_rotation_of_interleaved_pairs():
+    """chatglm2/attention.py:98-151 restated: pair i of the first half of a head turns by angle pos * 10000^(-2i/(H/2))."""
+    r = np.random.default_rng(31)
+    H, L = 128, 50
+    sin_t, cos_t = O.chatglm2_rope_tables(L, H)
+    x = r.standard_normal((3, 2, 1, H)).astype(np.float16)
+    for pos in (0, 1, 17, 49):
+        y = O.chatglm2_rope_apply(x, sin_t[pos], cos_t[pos]).astype(np.float32)
+        ang = pos * np.array([1.0 / (10000 ** (i / (H // 2))) for i in range(0, H // 2, 2)])
+        xe, xo = x[..., 0:H // 2:2].astype(np.float64), x[..., 1:H // 2:2].astype(np.float64)
+        np.testing.assert_allclose(y[..., 0:H // 2:2], xe * np.cos(ang) - xo * np.sin(ang), atol=2e-2)
+        np.testing.assert_allclose(y[..., 1:H // 2:2], xo * np.cos(ang) + xe * np.sin(ang), atol=2e-2)
+        assert np.array_equal(y[..., H // 2:], x[..., H // 2:].astype(np.float32))
