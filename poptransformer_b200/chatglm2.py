@@ -1,0 +1,135 @@
+"""ChatGLM2 decode loop on the per-op kernels: host-side mirror of the reference's ChatGLM2DecodeModel
+(poptransformer/models/chatglm2/model.py:95-117, :199-254) for one token per loop iteration.
+
+Per block: RMSNorm -> query | key_value (+bias) -> interleaved RoPE on the first half of each head, multi-query KV append and
+attention with the fp16 softmax (chatglm2/attention.py:98-302) -> dense (+residual) -> RMSNorm -> SwiGLU MLP (chatglm2/mlp.py:51-59)
+-> dense_4h_to_h (+residual); final RMSNorm and the output layer.  The RMSNorms and (for FP8) the activation casts run as
+prologues of the linears.  Weights: fp16, or E4M3 bytes with a float `<key>_scale` per tensor."""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import ops
+
+
+class ChatGLM2Config:
+    def __init__(self, n_layer, d_model, n_head, n_group, ffn, vocab, max_len, eps=1e-5, precision="fp16", act_scales=None):
+        self.n_layer, self.d_model, self.n_head, self.n_group, self.ffn, self.vocab, self.max_len, self.eps = (
+            n_layer, d_model, n_head, n_group, ffn, vocab, max_len, eps)
+        self.precision = precision
+        self.head_dim = d_model // n_head
+        self.act_scales = act_scales or {"norm": 8.0 / 448.0, "attn": 2.0 / 448.0, "mlp": 1.0 / 448.0}
+
+
+def chatglm2_rope_tables(max_len, head_dim, device):
+    """sin / cos [max_len, head_dim / 4] with the reference's recipe (chatglm2/attention.py:77-96): float32 inverse frequencies
+    for dim = head_dim / 2, float32 angle, cast to fp16, sin / cos of the fp16 angle rounded to fp16."""
+    dim = head_dim // 2
+    inv_freq = np.array([1.0 / (10000 ** (i / dim)) for i in range(0, dim, 2)]).astype(np.float32)
+    ang = (np.arange(max_len, dtype=np.float32)[:, None] * inv_freq[None, :]).astype(np.float32).astype(np.float16)
+    sin, cos = np.sin(ang.astype(np.float32)).astype(np.float16), np.cos(ang.astype(np.float32)).astype(np.float16)
+    return torch.from_numpy(sin).to(device), torch.from_numpy(cos).to(device)
+
+
+class ChatGLM2Decoder:
+    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1):
+        c = cfg
+        if c.head_dim not in (64, 128) or c.n_head % c.n_group:
+            raise ops.PtError(f"head size {c.head_dim} / groups {c.n_group} not supported")
+        self.cfg, self.batch, self.device = cfg, batch, device
+        self.pad_id = c.vocab - 1 if pad_id is None else pad_id
+        self.eos_id = eos_id
+        dev, fp8 = device, c.precision == "fp8"
+        t = lambda k: state_dict[k].to(dev)
+
+        def packed(keys, interleave=False):
+            ws = [t(k) for k in keys]
+            if fp8:
+                scales = {float(state_dict[k + "_scale"]) for k in keys}
+                if len(scales) != 1:
+                    raise ops.PtError("fused FP8 linears need one common weight scale")
+                return ops.PackedLinear(ops.W_FP8, torch.cat(ws, 0).contiguous(), w_scale=scales.pop(), interleave_gate_up=interleave)
+            return ops.PackedLinear(ops.W_FP16, torch.cat(ws, 0).to(torch.float16).contiguous(), interleave_gate_up=interleave)
+
+        self.emb = t("transformer.embedding.word_embeddings.weight").to(torch.float16).contiguous()
+        self.layers = []
+        for i in range(c.n_layer):
+            p = f"transformer.encoder.layers.{i}."
+            self.layers.append({
+                "ln1": t(p + "input_layernorm.weight").contiguous(), "ln2": t(p + "post_attention_layernorm.weight").contiguous(),
+                "qkv": packed([p + "self_attention.query.weight", p + "self_attention.key_value.weight"]),
+                "b_qkv": torch.cat([t(p + "self_attention.query.bias"), t(p + "self_attention.key_value.bias")]).to(torch.float16).contiguous(),
+                "dense": packed([p + "self_attention.dense.weight"]),
+                "gu": packed([p + "mlp.dense_h_to_4h_1.weight", p + "mlp.dense_h_to_4h_2.weight"], interleave=True),
+                "down": packed([p + "mlp.dense_4h_to_h.weight"]),
+            })
+        self.norm = t("transformer.encoder.final_layernorm.weight").contiguous()
+        self.head = packed(["transformer.output_layer.weight"])
+        self.sin, self.cos = chatglm2_rope_tables(c.max_len, c.head_dim, dev)
+        self.score_scale = float(np.float16(1.0 / np.sqrt(c.head_dim)))
+        B, d = batch, c.d_model
+        f16 = dict(dtype=torch.float16, device=dev)
+        self.ids = torch.full((B, c.max_len), self.pad_id, dtype=torch.int32, device=dev)
+        self.step_t = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.stop_mask = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.x = torch.empty((B, d), **f16)
+        self.qkv = torch.empty((B, (c.n_head + 2 * c.n_group) * c.head_dim), **f16)
+        self.attn = torch.empty((B, d), **f16)
+        self.act = torch.empty((B, c.ffn), **f16)
+        self.logits = torch.empty((B, c.vocab), **f16)
+        self.next_val = torch.empty((B, 1), **f16)
+        self.next_ids = torch.empty((B, 1), dtype=torch.int32, device=dev)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        page_table = None
+        self.caches = []
+        for _ in range(c.n_layer):
+            kc = ops.PagedKVCache(B, c.n_group, c.head_dim, c.max_len, page_size, dev, page_table)
+            page_table = kc.page_table
+            self.caches.append(kc)
+        self.attn_ws = ops.attn_workspace(B, c.n_head, c.head_dim, self.caches[0].max_pages, dev)
+        self.lin_ws = ops.linear_workspace(B, max(2 * c.ffn, c.vocab, self.qkv.shape[1]), 16, dev)
+        self.graph = None
+        torch.cuda.synchronize()
+
+    def _linear(self, x, pl, out, site, gamma=None, epilogue=ops.EPI_STORE, bias=None, residual=None):
+        fp8 = pl.wfmt == ops.W_FP8
+        pro = (ops.PRO_RMSNORM_CAST_FP8 if fp8 else ops.PRO_RMSNORM) if gamma is not None else (ops.PRO_CAST_FP8 if fp8 else ops.PRO_NONE)
+        a = ops.linear_args(x, pl, out, prologue=pro, epilogue=epilogue, gamma=gamma, eps=self.cfg.eps,
+                            act_scale=self.cfg.act_scales[site] if fp8 else 0.0, bias=bias, residual=residual, workspace=self.lin_ws,
+                            error_flag=self.error_flag)
+        ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
+
+    def enqueue_step(self):
+        c, L_ = self.cfg, ops._lib.lib()
+        ops.embedding(self.emb, self.ids, self.step_t, out=self.x)
+        for li, L in enumerate(self.layers):
+            self._linear(self.x, L["qkv"], self.qkv, "norm", gamma=L["ln1"], epilogue=ops.EPI_BIAS, bias=L["b_qkv"])
+            a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, c.n_head, ops.ROPE_CHATGLM2, ops.SOFTMAX_F16, self.score_scale,
+                              self.sin, self.cos, self.attn_ws, self.error_flag)
+            ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
+            self._linear(self.attn, L["dense"], self.x, "attn", epilogue=ops.EPI_RESIDUAL, residual=self.x)
+            self._linear(self.x, L["gu"], self.act, "norm", gamma=L["ln2"], epilogue=ops.EPI_SWIGLU)
+            self._linear(self.act, L["down"], self.x, "mlp", epilogue=ops.EPI_RESIDUAL, residual=self.x)
+        self._linear(self.x, self.head, self.logits, "norm", gamma=self.norm)
+        ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids), ops._stream()),
+                  "topk")
+        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
+
+    def reset(self, input_ids):
+        self.ids.copy_(torch.as_tensor(input_ids, dtype=torch.int32).to(self.device))
+        self.step_t.zero_()
+        self.stop_mask.zero_()
+
+    def step(self):
+        self.enqueue_step()
+
+    def run(self, input_ids, max_loop=None):
+        """Session.run analogue (poptransformer/sessions.py:47-49): returns the anchors {'Loop:0': ids, 'Loop:1': step}."""
+        self.reset(input_ids)
+        for _ in range(self.cfg.max_len if max_loop is None else max_loop):
+            self.step()
+        torch.cuda.synchronize()
+        if int(self.error_flag.item()) != 0:
+            raise ops.PtError("a bounded device-side wait gave up")
+        return {"Loop:0": self.ids.cpu().numpy(), "Loop:1": self.step_t.cpu().numpy()}

@@ -4,7 +4,7 @@ that the reference layers look up (e.g. llama2/model.py:114-132 via layers/linea
 INT4 linears are stored as int8 `<key>` + fp16 `<key>_scale` like the reference's int4 checkpoints."""
 import torch
 
-from .quant import quantize_int4
+from .quant import quantize_fp8, quantize_int4
 
 
 def _normal(shape, gen, device, std=0.02):
@@ -66,6 +66,42 @@ def gpt2_state_dict(n_layer, d_model, n_head, vocab, n_positions, seed=0, device
         sd[p + "mlp.c_fc.weight"], sd[p + "mlp.c_fc.bias"] = _normal((4 * d_model, d_model), gen, device), _normal((4 * d_model,), gen, device)
         sd[p + "mlp.c_proj.weight"], sd[p + "mlp.c_proj.bias"] = _normal((d_model, 4 * d_model), gen, device), _normal((d_model,), gen, device)
     ln("transformer.ln_f")
+    return sd
+
+
+def chatglm2_state_dict(n_layer, d_model, n_head, n_group, ffn, vocab, seed=0, device="cpu", precision="fp16"):
+    """ChatGLM2 architecture with the reference's key names after its checkpoint pre-processing (chatglm2/model.py:256-289:
+    query / key_value and the two halves of dense_h_to_4h split).  precision "fp8" stores every transformer linear and the output
+    layer as E4M3 bytes plus a float `<key>_scale`; linears that the decoder fuses (query | key_value, the two MLP halves) are
+    quantised with one common scale."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    hs = d_model // n_head
+    sd = {"transformer.embedding.word_embeddings.weight": _normal((vocab, d_model), gen, device)}
+
+    def lin(group):
+        ws = {k: _normal(shape, gen, device) for k, shape in group}
+        if precision == "fp8":
+            amax = max(float(w.float().abs().max()) for w in ws.values())
+            scale = amax / 448.0
+            for k, w in ws.items():
+                sd[k] = torch.clamp(w.float() / scale, -448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+                sd[k + "_scale"] = scale
+        else:
+            sd.update(ws)
+
+    for i in range(n_layer):
+        p = f"transformer.encoder.layers.{i}."
+        sd[p + "input_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+        sd[p + "post_attention_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+        lin([(p + "self_attention.query.weight", (d_model, d_model)), (p + "self_attention.key_value.weight", (2 * n_group * hs, d_model))])
+        sd[p + "self_attention.query.bias"] = _normal((d_model,), gen, device)
+        sd[p + "self_attention.key_value.bias"] = _normal((2 * n_group * hs,), gen, device)
+        lin([(p + "self_attention.dense.weight", (d_model, d_model))])
+        lin([(p + "mlp.dense_h_to_4h_1.weight", (ffn, d_model)), (p + "mlp.dense_h_to_4h_2.weight", (ffn, d_model))])
+        lin([(p + "mlp.dense_4h_to_h.weight", (d_model, ffn))])
+    sd["transformer.encoder.final_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+    lin([("transformer.output_layer.weight", (vocab, d_model))])
     return sd
 
 

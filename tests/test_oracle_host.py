@@ -193,3 +193,51 @@ def test_chatglm2_rope_is_a_rotation_of_interleaved_pairs():
         np.testing.assert_allclose(y[..., 0:H // 2:2], xe * np.cos(ang) - xo * np.sin(ang), atol=2e-2)
         np.testing.assert_allclose(y[..., 1:H // 2:2], xo * np.cos(ang) + xe * np.sin(ang), atol=2e-2)
         assert np.array_equal(y[..., H // 2:], x[..., H // 2:].astype(np.float32))
+
+
+def test_chatglm2_oracle_matches_plain_fp32_transformer():
+    """The step-by-step fp16 restatement of the reference's ChatGLM2 decode graph (multi-query groups, interleaved RoPE on half of
+    each head, RMSNorm, SwiGLU) against a plain float32 causal transformer over the whole sequence."""
+    from oracle import chatglm2_np
+    from poptransformer_b200 import synth
+    dims = dict(n_layer=2, d_model=256, n_head=4, n_group=2, ffn=384, vocab=300)
+    T = 10
+    sd = {k: (v.numpy() if hasattr(v, "numpy") else v) for k, v in synth.chatglm2_state_dict(**dims, seed=6).items()}
+    orc = chatglm2_np.ChatGLM2Oracle(chatglm2_np.ChatGLM2Config(**dims, max_len=T), sd, 1)
+    ids = synth.prompt_ids(1, T, T, dims["vocab"], dims["vocab"] - 1, seed=7).numpy()
+    got = np.stack([orc.logits(ids[:, t], t)[0][0].astype(np.float32) for t in range(T)])
+
+    f = lambda k: sd[k].astype(np.float32)
+    d, N, G = dims["d_model"], dims["n_head"], dims["n_group"]
+    hs = d // N
+    rms = lambda x, k: x / np.sqrt((x * x).mean(-1, keepdims=True) + 1e-5) * f(k)
+    ang = np.arange(T)[:, None] * np.array([1.0 / (10000 ** (i / (hs // 2))) for i in range(0, hs // 2, 2)])[None, :]   # [T, hs/4]
+
+    def rope(x):                                   # x [T, heads, hs]
+        y = x.copy()
+        xe, xo = x[..., 0:hs // 2:2], x[..., 1:hs // 2:2]
+        c, s = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+        y[..., 0:hs // 2:2], y[..., 1:hs // 2:2] = xe * c - xo * s, xo * c + xe * s
+        return y
+
+    x = f("transformer.embedding.word_embeddings.weight")[ids[0]]
+    causal = np.triu(np.full((T, T), -np.inf, np.float32), 1)
+    for i in range(dims["n_layer"]):
+        p = f"transformer.encoder.layers.{i}."
+        h = rms(x, p + "input_layernorm.weight")
+        q = (h @ f(p + "self_attention.query.weight").T + f(p + "self_attention.query.bias")).reshape(T, N, hs)
+        kv = h @ f(p + "self_attention.key_value.weight").T + f(p + "self_attention.key_value.bias")
+        k, v = kv[:, : G * hs].reshape(T, G, hs), kv[:, G * hs:].reshape(T, G, hs)
+        q, k = rope(q), rope(k)
+        k, v = np.repeat(k, N // G, axis=1), np.repeat(v, N // G, axis=1)
+        s = np.einsum("tnh,unh->ntu", q, k) / np.sqrt(hs) + causal
+        pr = np.exp(s - s.max(-1, keepdims=True))
+        pr /= pr.sum(-1, keepdims=True)
+        a = np.einsum("ntu,unh->tnh", pr, v).reshape(T, d)
+        x = x + a @ f(p + "self_attention.dense.weight").T
+        h = rms(x, p + "post_attention_layernorm.weight")
+        g = h @ f(p + "mlp.dense_h_to_4h_1.weight").T
+        u = h @ f(p + "mlp.dense_h_to_4h_2.weight").T
+        x = x + (u * g / (1 + np.exp(-g))) @ f(p + "mlp.dense_4h_to_h.weight").T
+    exp = rms(x, "transformer.encoder.final_layernorm.weight") @ f("transformer.output_layer.weight").T
+    np.testing.assert_allclose(got, exp, rtol=3e-2, atol=3e-2)
