@@ -295,6 +295,14 @@ int pt_fp8_matmul(const void *a, const void *b, float scale_a, float scale_b, in
  * num/den/max fp32 [b, c] updated in place; out fp16 [b, c] = fp16(wkv). */
 int pt_wkv(const void *k, const void *v, const float *time_first, const float *time_decay, float *num,
            float *den, float *max_state, int b, int c, void *out, void *stream);
+/* Token-shift gates of RWKV (`gate`, rwkv/attention.py:59-64 and ffn.py:40-45): out_x = h * mix_x + (1 - mix_x) * state for up to
+ * three fp16 mixing vectors [dim] (out_b / out_c optional), fp16 rounding after every op; then state <- hidden.
+ * hidden, state, out_x fp16 [rows, dim]. */
+int pt_rwkv_mix(const void *hidden, void *state, const void *mix_a, const void *mix_b, const void *mix_c, void *out_a,
+                void *out_b, void *out_c, int rows, int dim, void *stream);
+/* Element-wise steps of RWKV on fp16 [n]: mode 0 out = sigmoid(a) * b (receptance gate, attention.py:76,103, ffn.py:57-58);
+ * mode 1 out = relu(a)^2 (ffn.py:53-54); mode 2 out = a / 2 (rescale_every, rwkv/model.py:115-116). */
+int pt_rwkv_act(int mode, const void *a, const void *b, void *out, int64_t n, void *stream);
 
 /* ---- loop-carry and small ops ----------------------------------------------------------
  * Embedding gather (layers/embedding.py:34-36): out[b] = table[ids[b*ids_stride + *step_dev]]. */

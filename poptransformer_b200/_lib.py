@@ -84,6 +84,8 @@ SIGNATURES = {
                                c_void_p, c_size_t, c_void_p]),
     "pt_cast_fp8": (c_int, [c_void_p, c_float, c_int64, c_void_p, c_void_p]),
     "pt_fp8_matmul": (c_int, [c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "pt_rwkv_mix": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "pt_rwkv_act": (c_int, [c_int, c_void_p, c_void_p, c_void_p, ctypes.c_int64, c_void_p]),
     "pt_wkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "pt_embedding": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_step_containers": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),

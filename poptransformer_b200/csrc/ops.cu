@@ -365,6 +365,40 @@ __global__ void wkv_kernel(const __half *__restrict__ k, const __half *__restric
   }
 }
 
+// RWKV token-shift gates (poptransformer/models/rwkv/attention.py:59-64, ffn.py:40-45): out_x = fp16(fp16(h * w_x) + fp16(fp16(1 - w_x) * s)) for up to
+// three mixing vectors, then the state takes the current hidden vector.
+__global__ void rwkv_mix_kernel(const __half *__restrict__ hidden, __half *__restrict__ state, const __half *__restrict__ wa,
+                                const __half *__restrict__ wb, const __half *__restrict__ wc, __half *__restrict__ oa, __half *__restrict__ ob,
+                                __half *__restrict__ oc, int rows, int dim) {
+  const size_t total = (size_t)rows * dim;
+  const __half one = __float2half_rn(1.0f);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int ch = i % dim;
+    const __half h = hidden[i], s = state[i];
+    oa[i] = h_add(h_mul(h, wa[ch]), h_mul(h_sub(one, wa[ch]), s));
+    if (ob) ob[i] = h_add(h_mul(h, wb[ch]), h_mul(h_sub(one, wb[ch]), s));
+    if (oc) oc[i] = h_add(h_mul(h, wc[ch]), h_mul(h_sub(one, wc[ch]), s));
+    state[i] = h;
+  }
+}
+// RWKV element-wise steps: 0: out = fp16(sigmoid(a)) * b   (receptance gate, attention.py:76,103; ffn.py:57-58)
+//                          1: out = relu(a)^2              (ffn.py:53-54)
+//                          2: out = a / 2                  (rescale_every, rwkv/model.py:115-116)
+__global__ void rwkv_act_kernel(int mode, const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ out, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const __half x = a[i];
+    if (mode == 0) {
+      const __half sg = __float2half_rn(1.0f / (1.0f + expf(-__half2float(x))));
+      out[i] = h_mul(sg, b[i]);
+    } else if (mode == 1) {
+      const __half r = __hgt(x, __float2half_rn(0.f)) ? x : __float2half_rn(0.f);
+      out[i] = h_mul(r, r);
+    } else {
+      out[i] = h_mul(x, __float2half_rn(0.5f));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ loop carry
 __global__ void embedding_kernel(const uint4 *__restrict__ table, const int *__restrict__ ids, int ids_stride, const int *step_dev,
                                  int dim8, int vocab, uint4 *__restrict__ out) {
@@ -564,6 +598,24 @@ extern "C" int pt_wkv(const void *k, const void *v, const float *time_first, con
   wkv_kernel<<<grid_for((size_t)b * c), 256, 0, as_stream(stream)>>>((const __half *)k, (const __half *)v, time_first, time_decay, num, den,
                                                                      max_state, b, c, (__half *)out);
   PT_LAUNCH_CHECK("pt_wkv");
+  return PT_OK;
+}
+
+extern "C" int pt_rwkv_mix(const void *hidden, void *state, const void *mix_a, const void *mix_b, const void *mix_c, void *out_a, void *out_b,
+                           void *out_c, int rows, int dim, void *stream) {
+  PT_REQUIRE(hidden && state && mix_a && out_a && (!out_b || mix_b) && (!out_c || mix_c), "pt_rwkv_mix: null pointer argument");
+  PT_REQUIRE(rows > 0 && dim > 0, "pt_rwkv_mix: bad shape [%d, %d]", rows, dim);
+  rwkv_mix_kernel<<<grid_for((size_t)rows * dim), 256, 0, as_stream(stream)>>>((const __half *)hidden, (__half *)state, (const __half *)mix_a,
+                                                                              (const __half *)mix_b, (const __half *)mix_c, (__half *)out_a,
+                                                                              (__half *)out_b, (__half *)out_c, rows, dim);
+  PT_LAUNCH_CHECK("pt_rwkv_mix");
+  return PT_OK;
+}
+
+extern "C" int pt_rwkv_act(int mode, const void *a, const void *b, void *out, int64_t n, void *stream) {
+  PT_REQUIRE(a && out && n > 0 && mode >= 0 && mode <= 2 && (mode != 0 || b), "pt_rwkv_act: bad arguments (mode %d)", mode);
+  rwkv_act_kernel<<<grid_for((size_t)n), 256, 0, as_stream(stream)>>>(mode, (const __half *)a, (const __half *)b, (__half *)out, (size_t)n);
+  PT_LAUNCH_CHECK("pt_rwkv_act");
   return PT_OK;
 }
 

@@ -105,6 +105,43 @@ def chatglm2_state_dict(n_layer, d_model, n_head, n_group, ffn, vocab, seed=0, d
     return sd
 
 
+def rwkv_state_dict(n_layer, d_model, ffn, vocab, rescale_every=6, seed=0, device="cpu"):
+    """RWKV-4 architecture with the reference's key names after its checkpoint pre-processing (rwkv/model.py:150-155: attention.output
+    and feed_forward.value weights divided by 2^(block // rescale_every)).  fp16 weights N(0, 0.02) (key / receptance / value of
+    the mixers N(0, 0.05) so that the WKV states move), time_decay ~ U(-5, -1), time_first ~ U(-1, 1), time_mix_* ~ U(0, 1)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    uni = lambda lo, hi: (torch.rand((d_model,), generator=gen, device=device) * (hi - lo) + lo)
+    sd = {"rwkv.embeddings.weight": _normal((vocab, d_model), gen, device, std=1.0)}
+
+    def ln(key):
+        sd[key + ".weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
+        sd[key + ".bias"] = _normal((d_model,), gen, device)
+
+    for i in range(n_layer):
+        p = f"rwkv.blocks.{i}."
+        if i == 0:
+            ln(p + "pre_ln")
+        ln(p + "ln1")
+        ln(p + "ln2")
+        div = float(2 ** (i // rescale_every)) if rescale_every > 0 else 1.0
+        a, m = p + "attention.", p + "feed_forward."
+        sd[a + "time_decay"], sd[a + "time_first"] = uni(-5.0, -1.0).float(), uni(-1.0, 1.0).float()
+        for nm in ("time_mix_key", "time_mix_value", "time_mix_receptance"):
+            sd[a + nm] = uni(0.0, 1.0).to(torch.float16).reshape(1, 1, d_model)
+        for nm in ("key", "value", "receptance"):
+            sd[a + nm + ".weight"] = _normal((d_model, d_model), gen, device, std=0.05)
+        sd[a + "output.weight"] = (_normal((d_model, d_model), gen, device, std=0.05).float() / div).to(torch.float16)
+        for nm in ("time_mix_key", "time_mix_receptance"):
+            sd[m + nm] = uni(0.0, 1.0).to(torch.float16).reshape(1, 1, d_model)
+        sd[m + "key.weight"] = _normal((ffn, d_model), gen, device, std=0.05)
+        sd[m + "receptance.weight"] = _normal((d_model, d_model), gen, device, std=0.05)
+        sd[m + "value.weight"] = (_normal((d_model, ffn), gen, device, std=0.05).float() / div).to(torch.float16)
+    ln("rwkv.ln_out")
+    sd["head.weight"] = _normal((vocab, d_model), gen, device)
+    return sd
+
+
 def prompt_ids(batch, prompt_len, max_len, vocab, pad_id, seed=0):
     """Uniform-random prompt ids excluding pad_id, right-padded to max_len with pad_id (int32, CPU)."""
     gen = torch.Generator().manual_seed(seed)
