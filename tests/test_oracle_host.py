@@ -241,3 +241,55 @@ def test_chatglm2_oracle_matches_plain_fp32_transformer():
         x = x + (u * g / (1 + np.exp(-g))) @ f(p + "mlp.dense_4h_to_h.weight").T
     exp = rms(x, "transformer.encoder.final_layernorm.weight") @ f("transformer.output_layer.weight").T
     np.testing.assert_allclose(got, exp, rtol=3e-2, atol=3e-2)
+
+
+def test_rwkv_oracle_matches_plain_float_recurrence():
+    """The fp16 restatement of the reference's RWKV decode graph (token shift, max-shifted WKV states, rescale) against the
+    textbook float64 RWKV-4 recurrence with explicit exponential sums."""
+    from oracle import rwkv_np
+    from poptransformer_b200 import synth
+    dims = dict(n_layer=2, d_model=64, ffn=128, vocab=200, rescale_every=1)
+    T = 8
+    sd = {k: v.numpy() for k, v in synth.rwkv_state_dict(**dims, seed=8).items()}
+    orc = rwkv_np.RWKVOracle(rwkv_np.RWKVConfig(**dims, max_len=T), sd, 1)
+    ids = synth.prompt_ids(1, T, T, dims["vocab"], dims["vocab"] - 1, seed=9).numpy()
+    got = np.stack([orc.logits(ids[:, t])[0][0].astype(np.float64) for t in range(T)])
+
+    f = lambda k: sd[k].astype(np.float64).reshape(sd[k].shape[-2:] if sd[k].ndim > 2 else sd[k].shape)
+    d = dims["d_model"]
+
+    def ln(x, p):
+        return (x - x.mean()) / np.sqrt(x.var() + 1e-5) * f(p + ".weight") + f(p + ".bias")
+
+    sig = lambda z: 1 / (1 + np.exp(-z))
+    prev_a = [np.zeros(d) for _ in range(2)]
+    prev_f = [np.zeros(d) for _ in range(2)]
+    hist = [[] for _ in range(2)]          # (k, v) history per layer: wkv_t = sum_{i<t} e^{-(t-1-i) w + k_i} v_i + e^{u + k_t} v_t over the same with v = 1
+    exp = []
+    for t in range(T):
+        x = f("rwkv.embeddings.weight")[ids[0, t]]
+        for i in range(2):
+            p = f"rwkv.blocks.{i}."
+            if i == 0:
+                x = ln(x, p + "pre_ln")
+            h = ln(x, p + "ln1")
+            a = p + "attention."
+            mix = lambda nm, prev: h * f(a + nm).reshape(-1) + (1 - f(a + nm).reshape(-1)) * prev
+            k = f(a + "key.weight") @ mix("time_mix_key", prev_a[i])
+            v = f(a + "value.weight") @ mix("time_mix_value", prev_a[i])
+            r = sig(f(a + "receptance.weight") @ mix("time_mix_receptance", prev_a[i]))
+            prev_a[i] = h
+            w, u = np.exp(f(a + "time_decay")), f(a + "time_first")
+            num = sum(np.exp(-(len(hist[i]) - 1 - j) * w + kj) * vj for j, (kj, vj) in enumerate(hist[i])) + np.exp(u + k) * v
+            den = sum(np.exp(-(len(hist[i]) - 1 - j) * w + kj) for j, (kj, vj) in enumerate(hist[i])) + np.exp(u + k)
+            hist[i].append((k, v))
+            x = x + f(a + "output.weight") @ (r * num / den)
+            h = ln(x, p + "ln2")
+            m = p + "feed_forward."
+            kk = np.maximum(f(m + "key.weight") @ (h * f(m + "time_mix_key").reshape(-1) + (1 - f(m + "time_mix_key").reshape(-1)) * prev_f[i]), 0) ** 2
+            rr = sig(f(m + "receptance.weight") @ (h * f(m + "time_mix_receptance").reshape(-1) + (1 - f(m + "time_mix_receptance").reshape(-1)) * prev_f[i]))
+            prev_f[i] = h
+            x = x + rr * (f(m + "value.weight") @ kk)
+            x = x / 2                      # rescale_every = 1
+        exp.append(f("head.weight") @ ln(x, "rwkv.ln_out"))
+    np.testing.assert_allclose(got, np.stack(exp), rtol=3e-2, atol=3e-2)
