@@ -99,7 +99,7 @@ class Builder:
     # ---- naming
     def _new_id(self, hint):
         self.root._counter += 1
-        return f"{hint}:{self.root._counter}"
+        return f"{self.getNameScope()}{hint}:{self.root._counter}"      # popart prefixes ids with the name scope
 
     @contextlib.contextmanager
     def nameScope(self, name):
@@ -319,7 +319,8 @@ def _exec(node, env):
     if op == "onnx.tile":
         return [np.tile(x[0], [int(v) for v in np.asarray(x[1])])]
     if op == "onnx.expand":
-        return [np.broadcast_to(x[0], [int(v) for v in np.asarray(x[1])]).copy()]
+        # ONNX Expand: the result shape is the broadcast of the input shape with the requested shape
+        return [np.broadcast_to(x[0], np.broadcast_shapes(np.shape(x[0]), tuple(int(v) for v in np.asarray(x[1])))).copy()]
     if op == "gc.swish":
         return [O.swish_f16(x[0])]
     if op == "gc.gelu":

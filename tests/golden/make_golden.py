@@ -26,6 +26,69 @@ CASES = {
     "llama_tiny_int4": (dict(n_layer=2, d_model=256, n_head=2, ffn=512, vocab=1000), "int4", -1, 1, 40, 6, 12),
     "llama_small_int4": (dict(n_layer=3, d_model=512, n_head=4, ffn=1024, vocab=2000), "int4", -1, 2, 72, 10, 13),
 }
+# other model families: name: (model kind, dims, batch, max_len, prompt_len, seed); fp16 weights
+OTHER = {
+    "gpt2_tiny_fp16": ("gpt2", dict(n_layer=2, d_model=256, n_head=4, vocab=1000, n_positions=64), 2, 40, 6, 21),
+    "chatglm2_tiny_fp16": ("chatglm2", dict(n_layer=2, d_model=512, n_head=4, n_group=2, ffn=768, vocab=1000), 2, 40, 6, 22),
+    "rwkv_tiny_fp16": ("rwkv", dict(n_layer=4, d_model=256, ffn=1024, vocab=1000, rescale_every=2), 2, 40, 6, 23),
+}
+
+
+def run_other(name):
+    """GPT-2 / ChatGLM2 / RWKV: the reference's own model classes on seeded synthetic checkpoints (fp16)."""
+    kind, dims, batch, max_len, prompt, seed = OTHER[name]
+    import popart                                       # the numpy stand-in
+    from poptransformer_b200 import synth
+    tmp = tempfile.mkdtemp()
+    os.makedirs(os.path.join(tmp, "examples", kind))
+    from oracle import c_ref
+    os.symlink(c_ref.build(), os.path.join(tmp, "custom_ops.so"))
+    os.chdir(os.path.join(tmp, "examples", kind))
+    from poptransformer.utils.registry import REGISTRY
+    from poptransformer.utils.tensor_type import TensorType
+    for k, v in dict(num_replicas=1, batch_size=batch, batch_per_step=1, model_type="shard", enable_pipeline=False, precision="fp16").items():
+        REGISTRY.register(k, v)
+    REGISTRY.register("tensor_type", TensorType("fp16"))
+    REGISTRY.register("logger", logging.getLogger("poptransformer"))
+    pad_id = dims["vocab"] - 1
+    tok = types.SimpleNamespace(pad_token_id=pad_id, eos_token_id=pad_id - 1)
+    if kind == "gpt2":
+        from poptransformer.models.gpt2.model import GPT2DecModel as Base
+        sd = synth.gpt2_state_dict(**dims, seed=seed)
+        cfg = types.SimpleNamespace(vocab_size=dims["vocab"], n_embd=dims["d_model"], layer_norm_epsilon=1e-5, n_head=dims["n_head"],
+                                    n_layer=dims["n_layer"], n_positions=dims["n_positions"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+        n_layer = dims["n_layer"]
+    elif kind == "chatglm2":
+        from poptransformer.models.chatglm2.model import ChatGLM2DecModel as Base
+        sd = synth.chatglm2_state_dict(**dims, seed=seed)
+        cfg = types.SimpleNamespace(padded_vocab_size=dims["vocab"], hidden_size=dims["d_model"], layernorm_epsilon=1e-5,
+                                    multi_query_group_num=dims["n_group"], num_attention_heads=dims["n_head"], ffn_hidden_size=dims["ffn"],
+                                    num_layers=dims["n_layer"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+        n_layer = dims["n_layer"]
+    else:
+        from poptransformer.models.rwkv.model import RWKVDecodeModel as Base
+        sd = synth.rwkv_state_dict(**dims, seed=seed)
+        cfg = types.SimpleNamespace(vocab_size=dims["vocab"], hidden_size=dims["d_model"], intermediate_size=dims["ffn"],
+                                    attention_hidden_size=dims["d_model"], layer_norm_epsilon=1e-5, num_hidden_layers=dims["n_layer"],
+                                    rescale_every=dims["rescale_every"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+        n_layer = dims["n_layer"]
+
+    class Golden(Base):
+        def prepare_state_dict(self):
+            self.hf_tokenizer, self.hf_config = tok, cfg
+            self.state_dict = sd
+            self.register_state_dict()
+
+    model = Golden(max_length=max_len, max_loop=max_len - 1, layer_per_ipu=[n_layer], early_stop=False, topk=1, outline_blocks=None)
+    model.build_graph()
+    ids = synth.prompt_ids(batch, prompt, max_len, dims["vocab"], pad_id, seed=seed).numpy()
+    env = popart.run_graph(model.graph, {"input_ids": ids})
+    out_ids, out_step = env["Loop:0"], env["Loop:1"]
+    os.chdir(ROOT)
+    np.savez(os.path.join(ROOT, "tests", "golden", name + ".npz"), input_ids=ids, output_ids=np.asarray(out_ids, dtype=np.int32),
+             step=np.asarray(out_step, dtype=np.int32), kind=kind, dims_keys=np.array(list(dims.keys())), dims_vals=np.array(list(dims.values())),
+             batch=batch, max_len=max_len, prompt=prompt, seed=seed, pad_id=pad_id, n_nodes=len(model.graph.nodes))
+    print(name, "ok: step", out_step, "ids[0, :12]", np.asarray(out_ids)[0, :12])
 
 
 def run_case(name):
@@ -76,7 +139,7 @@ def run_case(name):
 
 if __name__ == "__main__":
     if len(sys.argv) > 2:
-        run_case(sys.argv[2])
+        (run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
     else:
-        for case in CASES:
+        for case in list(CASES) + list(OTHER):
             subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)
