@@ -186,8 +186,14 @@ __device__ __forceinline__ bool wait_flags(const uint32_t *flags, int rows, int 
   const int lane = threadIdx.x & 31;
   for (int it = 0; it < POLL_LIMIT; ++it) {
     bool ok = true;
-    for (int r = 0; r < rows; ++r)
-      for (int i = lane; i < cols; i += 32) ok &= (int)(ld_word(flags + r * 256 + i) - want) >= 0;
+    for (int r = 0; r < rows; ++r) {
+      // all of a lane's words (cols <= 256: up to eight) are requested before the first is looked at: one round trip per row
+      uint32_t f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = (lane + 32 * j < cols) ? ld_word(flags + r * 256 + lane + 32 * j) : want;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ok &= (int)(f[j] - want) >= 0;
+    }
     if (__all_sync(0xffffffffu, ok)) return true;
     if ((it & 63) == 63 && *abort_flag) break;
   }
@@ -216,6 +222,7 @@ struct Shared {           // fixed-size part, placed after the ring / activation
   float ps[NGRP][PAGE];   // one row per 4-warp attention group
   float pw[NCW][PAGE];    // softmax weights of the page, one private copy per warp
   float ml[NGRP][2];
+  int phys[MAXU];         // physical page of each unit of the attention pass (for the append of the new token)
   float stat[BMAX];
   float wred[32];
   float bestv[32][BMAX];
@@ -506,7 +513,8 @@ struct Split {
 // Finished sums of row tile `rt` of this SM: lane (g, tig) with tig < B holds batch tig, rows g (lo) and g + 8 (hi) of the tile.
 // Phases between layers write tagged words; the LM head keeps its arg-max and optionally writes fp16 logits.
 template <bool HEAD, bool TP>
-__device__ __forceinline__ void tile_epilogue(const Params &p, const volatile PhaseInfo *pi, float lo, float hi, int rt, int lane, Best *best) {
+__device__ __forceinline__ void tile_epilogue(const Params &p, const volatile PhaseInfo *pi, float lo, float hi, int rt, int lane, Best *best,
+                                              const uint32_t *pre = nullptr) {
   const int g = lane >> 2, b = lane & 3;
   if (b >= p.B) return;
   const int epi = pi->epi, N = pi->N;
@@ -540,7 +548,7 @@ __device__ __forceinline__ void tile_epilogue(const Params &p, const volatile Ph
       uint32_t *w = outw + (size_t)b * N + n;
       // the residual is the value this SM wrote to the same word one or two phases ago (or the embedding, which the first
       // staging of this launch has already seen complete)
-      if (epi == EPI_RESID) y = h_add(__ushort_as_half((unsigned short)(ld_word(w) & 0xFFFFu)), y);
+      if (epi == EPI_RESID) y = h_add(__ushort_as_half((unsigned short)((pre ? pre[hr] : ld_word(w)) & 0xFFFFu)), y);
       st_word(w, tag, y);
     }
   }
@@ -603,6 +611,16 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best
     }
   }
 
+  // Residual words of the row tile whose sum this warp will finish after the loop (row tiles shared by several warps, the usual
+  // case of the residual phases): requested now, so that their round trip is not at the end of the phase.
+  uint32_t pre[2] = {0u, 0u};
+  bool has_pre = false;
+  if (I4 && pi->epi == EPI_RESID && !(TP && pi->push) && warp < m && tig < p.B) {
+    const uint32_t *w = pi->outw + (size_t)tig * pi->N + (size_t)(r0 + warp) * 16 + g;
+    pre[0] = ld_word(w);
+    pre[1] = ld_word(w + 8);
+    has_pre = true;
+  }
   auto store_partial = [&](int slot) { *reinterpret_cast<float2 *>(&c.sh->red[warp][slot][lane][0]) = make_float2(acc0, acc1); };
   auto load_tile = [&](uint32_t t_s, TileRegs &t) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.a.x), "=r"(t.a.y), "=r"(t.a.z), "=r"(t.a.w) : "r"(t_s));
@@ -684,7 +702,7 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best
       v0 += t.x;
       v1 += t.y;
     }
-    tile_epilogue<!I4, TP>(p, pi, v0, v1, r, lane, best);
+    tile_epilogue<!I4, TP>(p, pi, v0, v1, r, lane, best, (has_pre && r == warp) ? pre : nullptr);
   }
   if (pi->out_seq) {  // tell the other SMs (of every rank, for pushed partial sums) that this SM's rows of the phase are written
     consumer_sync();
@@ -719,6 +737,10 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
   const __half *sin_r = p.sin_t + (size_t)step * (H / 2), *cos_r = p.cos_t + (size_t)step * (H / 2);
   for (int u0 = c.sm; u0 < n_units; u0 += MAXU * c.G) {
     const int nu = min(MAXU, (n_units - u0 + c.G - 1) / c.G);  // units of this pass: u0 + k G
+    if (tid < nu) {  // page-table entries of the pass, requested now so that their latency hides behind the poll below
+      const int u = u0 + tid * c.G;
+      sh->phys[tid] = p.page_table[(size_t)(u / (n_active * p.n_head)) * p.max_pages + u % n_active];
+    }
     // ---- q (and the new token's k, v) of every unit in one go.  The words carry the tag of this layer's QKV phase; all six
     // loads of a thread are in flight together, so once the producing SMs are done this costs one L2 round trip.
     {
@@ -777,7 +799,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
         c.advance();
       }
       if (owner && tid < H && !sh->abort) {  // append the new token to the pool
-        const int phys = p.page_table[(size_t)b * p.max_pages + pg];
+        const int phys = sh->phys[k];
         __half *gK = (__half *)L.pool + (((size_t)phys * 2 + 0) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
         __half *gV = (__half *)L.pool + (((size_t)phys * 2 + 1) * p.n_head + head) * PAGE * H + (size_t)(n_valid - 1) * H;
         gK[tid] = sh->newk[k][tid];
@@ -982,15 +1004,28 @@ struct Producer {
   __device__ void push_attention(const pt_llama_layer &L, int step) {
     const int n_active = step / PAGE + 1;
     const int n_units = p.B * p.n_head * n_active;
-    for (int u = sm; u < n_units && ok; u += G) {
-      const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
-      const int n_valid = min(PAGE, step + 1 - pg * PAGE);
-      const int n_load = (pg == n_active - 1) ? n_valid - 1 : n_valid;
-      if (n_load <= 0) continue;
-      const int phys = p.page_table[(size_t)b * p.max_pages + pg];
-      const __half *gK = (const __half *)L.pool + (((size_t)phys * 2 + 0) * p.n_head + head) * PAGE * H;
-      const __half *gV = (const __half *)L.pool + (((size_t)phys * 2 + 1) * p.n_head + head) * PAGE * H;
-      push(gK, (uint32_t)n_load * H * 2, gV, (uint32_t)n_load * H * 2);
+    for (int u0 = sm; u0 < n_units && ok; u0 += MAXU * G) {
+      // the page-table entries of a pass first (independent loads, one round trip), then the copies
+      int phys[MAXU];
+#pragma unroll
+      for (int k = 0; k < MAXU; ++k) {
+        const int u = u0 + k * G;
+        phys[k] = u < n_units ? p.page_table[(size_t)(u / (n_active * p.n_head)) * p.max_pages + u % n_active] : 0;
+      }
+#pragma unroll
+      for (int k = 0; k < MAXU; ++k) {
+        const int u = u0 + k * G;
+        if (u < n_units && ok) {
+          const int pg = u % n_active, head = (u / n_active) % p.n_head;
+          const int n_valid = min(PAGE, step + 1 - pg * PAGE);
+          const int n_load = (pg == n_active - 1) ? n_valid - 1 : n_valid;
+          if (n_load > 0) {
+            const __half *gK = (const __half *)L.pool + (((size_t)phys[k] * 2 + 0) * p.n_head + head) * PAGE * H;
+            const __half *gV = (const __half *)L.pool + (((size_t)phys[k] * 2 + 1) * p.n_head + head) * PAGE * H;
+            push(gK, (uint32_t)n_load * H * 2, gV, (uint32_t)n_load * H * 2);
+          }
+        }
+      }
     }
   }
 };
