@@ -37,11 +37,11 @@ constexpr int TILE_I4 = 1056, TILE_F16 = 1024;
 constexpr int STAGE_TILES = 2 * NCW;              // two tiles per consumer warp per stage
 constexpr int STAGE_BYTES = ((STAGE_TILES * TILE_I4 + 127) / 128 * 128) > 33792 ? ((STAGE_TILES * TILE_I4 + 127) / 128 * 128) : 33792;
 constexpr int V_OFFSET = 16896;                   // a K page and a V page (2 x 16 KB) share one attention stage
-constexpr int MAXU = 8;                           // attention units handled per SM per pass
+constexpr int MAXU = NCT / 64;                    // attention units handled per SM per pass (64 threads fetch q / k / v of one)
 constexpr int BMAX = 2;
 constexpr int H = 128, PAGE = 64;
 constexpr int SPIN_LIMIT = 1 << 22;
-static_assert(NCT == 8 * PAGE, "the attention scores use eight lanes per token of a page");
+static_assert(NCT % 64 == 0 || NCT % 32 == 0, "consumer threads come in whole warps");
 
 struct Params {
   int B, d, n_head, ffn, vocab, n_layer, max_len, max_pages, ns, xs_stride, pad_id, eos_id, debug;
@@ -715,8 +715,7 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best
 }
 
 // RoPE (rotate_half form) on elements i and i + H/2 of one head vector -> dst (shared), reference fp16 roundings.
-__device__ __forceinline__ void rope_pair(__half a, __half b, const __half *sin_r, const __half *cos_r, int i, __half *dst) {
-  const __half s = sin_r[i], co = cos_r[i];
+__device__ __forceinline__ void rope_pair(__half a, __half b, __half s, __half co, int i, __half *dst) {
   dst[i] = h_add(h_mul(a, co), h_mul(__hneg(b), s));
   dst[i + H / 2] = h_add(h_mul(b, co), h_mul(a, s));
 }
@@ -750,6 +749,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
         const int pg = u % n_active, head = (u / n_active) % p.n_head, b = u / (n_active * p.n_head);
         const bool owner = (pg == n_active - 1);
         const uint32_t *qw = p.qkvw + (size_t)b * row_elems + (size_t)head * H + i;
+        const __half rs = sin_r[i], rc = cos_r[i];  // requested before the poll: their latency hides behind it
         uint32_t w[6];
         bool got = false;
         for (int it = 0; it < POLL_LIMIT && !got; ++it) {
@@ -768,9 +768,9 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
           if (p.error_flag) atomicExch(p.error_flag, 8);
         }
         auto val = [&](int j) { return __ushort_as_half((unsigned short)(w[j] & 0xFFFFu)); };
-        rope_pair(val(0), val(1), sin_r, cos_r, i, sh->qs[k]);
+        rope_pair(val(0), val(1), rs, rc, i, sh->qs[k]);
         if (owner) {
-          rope_pair(val(2), val(3), sin_r, cos_r, i, sh->newk[k]);
+          rope_pair(val(2), val(3), rs, rc, i, sh->newk[k]);
           sh->newv[k][i] = val(4);
           sh->newv[k][i + 64] = val(5);
         }
@@ -807,8 +807,9 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
       }
       // scores: 8 lanes per cached token, all 64 tokens of the page at once
       float *ps = sh->ps[0];
-      {
-        const int sub = lane & 7, t = tid >> 3;
+#pragma unroll
+      for (int tb = 0; tb < PAGE; tb += NCT / 8) {   // one pass with 16 consumer warps
+        const int sub = lane & 7, t = tb + (tid >> 3);
         float sc0 = 0.f, sc1 = 0.f;
         if (t < n_valid && !sh->abort) {
           const __half *kr = (t < n_load) ? Ks + (size_t)t * H : sh->newk[k];
@@ -854,7 +855,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
         float o[4] = {0.f, 0.f, 0.f, 0.f};
         if (!sh->abort) {
 #pragma unroll
-          for (int j = 0; j < PAGE / NCW; ++j) {
+          for (int j = 0; j < (PAGE + NCW - 1) / NCW; ++j) {
             const int t = warp + NCW * j;
             if (t < n_valid) {
               const uint2 raw = *reinterpret_cast<const uint2 *>((t < n_load ? Vs + (size_t)t * H : sh->newv[k]) + 4 * lane);
@@ -918,9 +919,12 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
       for (int i0 = 0; i0 < n_active; i0 += 32) {
         if (i0) group_sync(grp);
         if (tq == 0 && i0 + lane < n_active) {
-          uint32_t mb, lb;
-          got &= poll_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 0], attn_tag, mb, &sh->abort);
-          got &= poll_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 1], attn_tag, lb, &sh->abort);
+          uint32_t mb, lb;   // already seen complete in pass 1 (same lane, same page); the two loads go out together
+          const uint2 a0 = ld_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 0]), a1 = ld_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 1]);
+          mb = a0.x;
+          lb = a1.x;
+          if (a0.y != attn_tag) got &= poll_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 0], attn_tag, mb, &sh->abort);
+          if (a1.y != attn_tag) got &= poll_tagged(&p.ws_ml[(hd * p.max_pages + i0 + lane) * 2 + 1], attn_tag, lb, &sh->abort);
           const float w = expf(__uint_as_float(mb) - M);
           wts[lane] = w;
           wts[32 + lane] = __uint_as_float(lb) * w;
