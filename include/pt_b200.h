@@ -249,8 +249,8 @@ typedef struct pt_llama_step_args {
    * full hidden size, n_head = this rank's heads, ffn = width of this rank's k window of down_proj (a multiple of 128
    * holding its ffn_valid activations at ffn_offset; weights outside are zero), vocab = this rank's LM-head rows, first id
    * vocab_offset.  The all-reduce after o_proj / down_proj is fused into the kernel: every rank stores its fp16 partial
-   * sums into its slot of every rank's exchange buffer (plain peer stores, tagged words), and the next staging step on
-   * every rank adds the slots in rank order.  tp_buffers[r] is rank r's exchange buffer as mapped in this process
+   * sums into its slot of every rank's exchange buffer (plain peer stores of tagged words, then one system-scope atomic
+   * increment of an arrival counter per SM and rank), and the next staging step on every rank adds the slots in rank order.  tp_buffers[r] is rank r's exchange buffer as mapped in this process
    * (pt_llama_tp_buffer_bytes each, zeroed once); x must then hold two copies ([2, batch, d_model] words). */
   int tp_size, tp_rank, ffn_offset, ffn_valid, vocab_offset;
   int emb_rows;                      /* tp_size > 1: rows of the embedding table (the full vocabulary; the table is replicated) */

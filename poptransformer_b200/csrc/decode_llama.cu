@@ -154,6 +154,7 @@ __device__ __forceinline__ uint2 ld_sys2(const uint2 *p) {
   asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void red_add_sys(uint32_t *p, uint32_t v) { asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ void st_flag(uint32_t *p, uint32_t v) { asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ void st_word(uint32_t *p, uint32_t tag, __half v) { *p = (tag << 16) | (uint32_t)__half_as_ushort(v); }
 // Eight consecutive tagged words -> eight fp16 values (as a uint4).  Bounded: on time-out returns false.
@@ -194,6 +195,17 @@ __device__ __forceinline__ bool wait_flags(const uint32_t *flags, int rows, int 
 #pragma unroll
       for (int j = 0; j < 8; ++j) ok &= (int)(f[j] - want) >= 0;
     }
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if ((it & 63) == 63 && *abort_flag) break;
+  }
+  return false;
+}
+// Tensor parallelism: one arrival counter per source rank (row stride 256 words), incremented once by every SM of that rank when
+// its partial sums of a row-parallel linear are pushed.  Lane r looks at rank r's counter: one round trip per poll.
+__device__ __forceinline__ bool wait_counters(const uint32_t *counters, int rows, uint32_t want, const volatile int *abort_flag) {
+  const int lane = threadIdx.x & 31;
+  for (int it = 0; it < POLL_LIMIT; ++it) {
+    const bool ok = lane >= rows || (int)(ld_word(counters + lane * 256) - want) >= 0;
     if (__all_sync(0xffffffffu, ok)) return true;
     if ((it & 63) == 63 && *abort_flag) break;
   }
@@ -243,6 +255,9 @@ struct Ctx {
   uint32_t tag0;       // tag of phase 0 of this launch
   __device__ __forceinline__ uint32_t tag(int phase) const { return ((tag0 + (uint32_t)phase) & 0x7FFFu) | 0x8000u; }
   __device__ __forceinline__ uint32_t seq(int phase) const { return tag0 + (uint32_t)phase + 1u; }  // never 0 in the first launches
+  uint32_t push0;      // row-parallel linears pushed by every SM before this launch (tp > 1)
+  // arrivals expected once the o_proj (which = 0) / down_proj (which = 1) of layer l has been pushed by all G SMs of a rank
+  __device__ __forceinline__ uint32_t arrivals(int l, int which) const { return (push0 + 2u * (uint32_t)l + (uint32_t)which + 1u) * (uint32_t)G; }
   __device__ __forceinline__ void advance() {
     if (++slot == (uint32_t)p.ns) { slot = 0; par ^= 1u; }
   }
@@ -348,7 +363,8 @@ __device__ __forceinline__ bool add_partial_sums(const uint32_t *parts, int n_pa
 struct StageSrc {
   const uint32_t *x;        // tagged words [B][K]
   uint32_t x_tag;
-  const uint32_t *flags;    // progress words to wait for first: rows x cols (row stride 256), sequence number `want`
+  const uint32_t *flags;    // progress words to wait for first: rows x cols (row stride 256), sequence number `want`;
+                            // cols == 0: one arrival counter per row instead, `want` arrivals
   int flag_rows, flag_cols;
   uint32_t want;
   // tensor parallelism: the input is x + the sum over ranks of the partial sums of a row-parallel linear
@@ -388,7 +404,8 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
       }
     }
   }
-  if (tid < 32 && !wait_flags(src.flags, src.flag_rows, src.flag_cols, src.want, &c.sh->abort)) {
+  if (tid < 32 && !(src.flag_cols == 0 ? wait_counters(src.flags, src.flag_rows, src.want, &c.sh->abort)
+                                       : wait_flags(src.flags, src.flag_rows, src.flag_cols, src.want, &c.sh->abort))) {
     c.sh->abort = 1;
     if (p.error_flag) atomicExch(p.error_flag, 10);
   }
@@ -707,7 +724,7 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best
   if (pi->out_seq) {  // tell the other SMs (of every rank, for pushed partial sums) that this SM's rows of the phase are written
     consumer_sync();
     if (TP && pi->push) {
-      if (tid < p.tp) st_sys(p.peer_flag[tid] + p.rank * 256 + c.sm, pi->out_seq);
+      if (tid < p.tp) red_add_sys(p.peer_flag[tid] + p.rank * 256, 1u);
     } else if (tid == 0) {
       st_flag(p.flag_sm + c.sm, pi->out_seq);
     }
@@ -1078,7 +1095,9 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   const unsigned which = __ldcg(p.barrier + 2) & 1u;
   // Word [3] counts launches; it numbers the tags of this launch (block 0 advances it after the final barrier).
   const int n_phases = 5 * p.n_layer + 1;  // phase 0: embedding; layer l: 1 + 5 l + {0 qkv, 1 attention, 2 o, 3 gate|up, 4 down}
-  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, 0u, __ldcg(p.barrier + 3) * (uint32_t)n_phases, nullptr};
+  const uint32_t launches = __ldcg(p.barrier + 3);
+  Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, 0u, launches * (uint32_t)n_phases,
+        launches * 2u * (uint32_t)p.n_layer, nullptr};
 
   // embedding: the SMs share the gather; the copy in global memory feeds the first staging and the residual adds
   for (int i = tid; i < p.B * (p.d / 8); i += NCT) {
@@ -1121,7 +1140,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
         if (tpar && l > 0) {
           src.x = p.xw + xcur * xsz; src.x_tag = c.tag(ph0 - 2);   // written by the staging before gate|up of the previous layer
           src.parts = p.peer_part[p.rank] + psz; src.n_parts = p.tp; src.part_tag = c.tag(ph0 - 1);
-          src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.want = c.seq(ph0 - 1);
+          src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.flag_cols = 0; src.want = c.arrivals(l - 1, 1);
           src.x_out = p.xw + (xcur ^ 1) * xsz; src.x_out_tag = c.tag(ph0);
         } else {
           src.x = p.xw + xcur * xsz; src.x_tag = c.tag(ph0 - 1); src.want = c.seq(ph0 - 1);
@@ -1136,7 +1155,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
         if (tpar) {
           src.x = p.xw + xcur * xsz; src.x_tag = (l == 0) ? c.tag(0) : c.tag(ph0);  // the embedding, or this layer's phase-0 staging
           src.parts = p.peer_part[p.rank]; src.n_parts = p.tp; src.part_tag = c.tag(ph0 + 2);
-          src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.want = c.seq(ph0 + 2);
+          src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.flag_cols = 0; src.want = c.arrivals(l, 0);
           src.x_out = p.xw + (xcur ^ 1) * xsz; src.x_out_tag = c.tag(ph0 + 3);
         } else {
           src.x = p.xw; src.x_tag = c.tag(ph0 + 2); src.want = c.seq(ph0 + 2);
@@ -1190,7 +1209,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
     if (TP) {
       src.x_tag = c.tag(last - 1);   // staging before gate|up of the last layer
       src.parts = p.peer_part[p.rank] + (size_t)p.tp * p.B * p.d; src.n_parts = p.tp; src.part_tag = c.tag(last);
-      src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.flag_cols = c.G; src.want = c.seq(last);
+      src.flags = p.peer_flag[p.rank]; src.flag_rows = p.tp; src.flag_cols = 0; src.want = c.arrivals(p.n_layer - 1, 1);
     } else {
       src.x_tag = c.tag(last);
       src.flags = p.flag_sm; src.flag_rows = 1; src.flag_cols = c.G; src.want = c.seq(last);
