@@ -11,6 +11,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 MODEL = dict(n_layer=3, d_model=512, n_head=4, ffn=1408, vocab=2000)   # ffn / 2 = 704 = 5.5 scale groups: the k window is exercised
+MODEL8 = dict(n_layer=2, d_model=1024, n_head=8, ffn=2816, vocab=2000)  # for 8 ranks: one head and 2.75 scale groups per rank
 
 
 def _free_port():
@@ -19,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, persistent, out_dir):
+def _worker(rank, world, port, persistent, out_dir, MODEL=MODEL):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
@@ -44,17 +45,17 @@ def _worker(rank, world, port, persistent, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("persistent", [True, False])
-def test_tp_stream_matches_oracle(persistent, tmp_path):
-    world = 2
+@pytest.mark.parametrize("world,persistent", [(2, True), (2, False), (4, True), (8, True)])
+def test_tp_stream_matches_oracle(world, persistent, tmp_path):
+    MODEL = MODEL8 if world == 8 else globals()["MODEL"]
     if torch.cuda.device_count() < world:
-        pytest.skip("needs two GPUs")
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     from oracle import llama_np
     from poptransformer_b200 import synth
-    mp.spawn(_worker, args=(world, _free_port(), persistent, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), persistent, str(tmp_path), MODEL), nprocs=world, join=True)
     got = [np.load(tmp_path / f"ids{r}.npy") for r in range(world)]
-    assert np.array_equal(got[0], got[1]), "ranks disagree on the generated ids"
+    assert all(np.array_equal(got[0], g) for g in got[1:]), "ranks disagree on the generated ids"
     batch, max_len, prompt = 2, 72, 6
     sd = synth.llama_state_dict(**MODEL, seed=11, device="cpu", int4_group=128)
     ocfg = llama_np.LlamaConfig(**MODEL, max_len=max_len, group=128)
