@@ -244,10 +244,10 @@ def run_b200(args):
     step_bytes = dec.weight_bytes_total() + batch * dec.kv_bytes_per_token_total() * (ctx_mean + 1)
     if dec.persistent:
         # the dominant kernel IS the step: one persistent launch per token, timed by the CUDA events of the timed region above
-        # traffic: dram__bytes_read + dram__bytes_write of one launch, captured with ncu on the 8-block case (1.011 x its
+        # traffic: dram__bytes_read + dram__bytes_write of one launch, captured with ncu on the 8-block case (1.012 x its
         # algorithmic bytes, profiles/llama_step_kernel_llama7b_8layers.md) and scaled to this launch by the bytes it processes
         roof = {"bound": "hbm", "achieved": step_bytes / (ms / K * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                "traffic": (1.011 * step_bytes) if world == 1 else None,
+                "traffic": (1.012 * step_bytes) if world == 1 else None,
                 "kernel": "llama_step_kernel (persistent, 1 launch per token)", "peak_source": peak_src, "launch_us": ms / K * 1e3,
                 "bytes_per_launch": step_bytes}
     else:
