@@ -5,7 +5,7 @@ checkout) through the numpy stand-in for `popart` in oracle/popart_cpu, on seede
 inputs' seeds and the resulting id containers.  Only usable where the reference tree is available (the development
 container); the fixtures it writes (tests/golden/*.npz) travel with the repository.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/PopTransformer [case]
 """
 import logging
 import os
@@ -17,7 +17,9 @@ import types
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("POPTRANSFORMER_REFERENCE", "")
+if not REF:
+    raise SystemExit("usage: make_golden.py /path/to/PopTransformer [case]")
 sys.path[:0] = [ROOT, os.path.join(ROOT, "oracle", "popart_cpu"), REF]
 
 CASES = {
