@@ -4,13 +4,20 @@
 Per block: RMSNorm -> query | key_value (+bias) -> interleaved RoPE on the first half of each head, multi-query KV append and
 attention with the fp16 softmax (chatglm2/attention.py:98-302) -> dense (+residual) -> RMSNorm -> SwiGLU MLP (chatglm2/mlp.py:51-59)
 -> dense_4h_to_h (+residual); final RMSNorm and the output layer.  The RMSNorms and (for FP8) the activation casts run as
-prologues of the linears.  Weights: fp16, or E4M3 bytes with a float `<key>_scale` per tensor."""
+prologues of the linears.  Weights: fp16, or E4M3 bytes with a float `<key>_scale` per tensor.
+
+Tensor parallel (model_type 'tp', one process per GPU): the query heads of every KV group are split over the ranks and key_value
+is replicated (chatglm2/attention.py:316-346 with the weight rearrangement of chatglm2/model.py:29-49), dense and dense_4h_to_h
+are 'end' layers followed by an NCCL all-reduce of the fp16 partial sums, dense_h_to_4h_1/2 are 'start' layers
+(chatglm2/mlp.py:62-72), the output layer is vocab-sharded with the value/id merge of layers/lm_head.py:75-116; the embedding
+stays replicated (the reference's sharded gather plus all-reduce adds exact zeros)."""
 import ctypes
 
 import numpy as np
 import torch
 
 from . import ops
+from .tp import multi_query_head_index, rows, vocab_rows
 
 
 class ChatGLM2Config:
@@ -33,8 +40,12 @@ def chatglm2_rope_tables(max_len, head_dim, device):
 
 
 class ChatGLM2Decoder:
-    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1):
+    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None):
         c = cfg
+        self.tp, self.rank, self.group = tp_size, tp_rank, group
+        tp, r = tp_size, tp_rank
+        if (c.n_head // c.n_group) % tp or c.ffn % tp:
+            raise ops.PtError(f"{c.n_head // c.n_group} query heads per group / ffn={c.ffn} not divisible by tp={tp}")
         if c.head_dim not in (64, 128) or c.n_head % c.n_group:
             raise ops.PtError(f"head size {c.head_dim} / groups {c.n_group} not supported")
         self.cfg, self.batch, self.device = cfg, batch, device
@@ -43,8 +54,8 @@ class ChatGLM2Decoder:
         dev, fp8 = device, c.precision == "fp8"
         t = lambda k: state_dict[k].to(dev)
 
-        def packed(keys, interleave=False):
-            ws = [t(k) for k in keys]
+        def packed(keys, interleave=False, pick=None):
+            ws = [t(k) if pick is None or pick[j] is None else pick[j](t(k)) for j, k in enumerate(keys)]
             if fp8:
                 scales = {float(state_dict[k + "_scale"]) for k in keys}
                 if len(scales) != 1:
@@ -53,19 +64,23 @@ class ChatGLM2Decoder:
             return ops.PackedLinear(ops.W_FP16, torch.cat(ws, 0).to(torch.float16).contiguous(), interleave_gate_up=interleave)
 
         self.emb = t("transformer.embedding.word_embeddings.weight").to(torch.float16).contiguous()
+        self.h_loc, self.d_loc, self.f_loc = c.n_head // tp, c.d_model // tp, c.ffn // tp
+        mine = multi_query_head_index(c.n_head, c.n_group, c.head_dim, r, tp).to(dev)       # rank r's query features
+        q_rows, start = (lambda w: w[mine]), (lambda w: rows(w, r, tp))
         self.layers = []
         for i in range(c.n_layer):
             p = f"transformer.encoder.layers.{i}."
             self.layers.append({
                 "ln1": t(p + "input_layernorm.weight").contiguous(), "ln2": t(p + "post_attention_layernorm.weight").contiguous(),
-                "qkv": packed([p + "self_attention.query.weight", p + "self_attention.key_value.weight"]),
-                "b_qkv": torch.cat([t(p + "self_attention.query.bias"), t(p + "self_attention.key_value.bias")]).to(torch.float16).contiguous(),
-                "dense": packed([p + "self_attention.dense.weight"]),
-                "gu": packed([p + "mlp.dense_h_to_4h_1.weight", p + "mlp.dense_h_to_4h_2.weight"], interleave=True),
-                "down": packed([p + "mlp.dense_4h_to_h.weight"]),
+                "qkv": packed([p + "self_attention.query.weight", p + "self_attention.key_value.weight"], pick=[q_rows, None]),
+                "b_qkv": torch.cat([t(p + "self_attention.query.bias")[mine], t(p + "self_attention.key_value.bias")]).to(torch.float16).contiguous(),
+                "dense": packed([p + "self_attention.dense.weight"], pick=[lambda w: w[:, mine]]),
+                "gu": packed([p + "mlp.dense_h_to_4h_1.weight", p + "mlp.dense_h_to_4h_2.weight"], interleave=True, pick=[start, start]),
+                "down": packed([p + "mlp.dense_4h_to_h.weight"], pick=[lambda w: w[:, r * self.f_loc:(r + 1) * self.f_loc]]),
             })
         self.norm = t("transformer.encoder.final_layernorm.weight").contiguous()
-        self.head = packed(["transformer.output_layer.weight"])
+        self.vocab_loc = -(-c.vocab // tp) if tp > 1 else c.vocab
+        self.head = packed(["transformer.output_layer.weight"], pick=[(lambda w: vocab_rows(w, r, tp)[0]) if tp > 1 else None])
         self.sin, self.cos = chatglm2_rope_tables(c.max_len, c.head_dim, dev)
         self.score_scale = float(np.float16(1.0 / np.sqrt(c.head_dim)))
         B, d = batch, c.d_model
@@ -74,10 +89,14 @@ class ChatGLM2Decoder:
         self.step_t = torch.zeros(1, dtype=torch.int32, device=dev)
         self.stop_mask = torch.zeros(B, dtype=torch.int32, device=dev)
         self.x = torch.empty((B, d), **f16)
-        self.qkv = torch.empty((B, (c.n_head + 2 * c.n_group) * c.head_dim), **f16)
-        self.attn = torch.empty((B, d), **f16)
-        self.act = torch.empty((B, c.ffn), **f16)
-        self.logits = torch.empty((B, c.vocab), **f16)
+        self.qkv = torch.empty((B, (self.h_loc + 2 * c.n_group) * c.head_dim), **f16)
+        self.attn = torch.empty((B, self.d_loc), **f16)
+        self.act = torch.empty((B, self.f_loc), **f16)
+        self.part = torch.empty((B, d), **f16)                       # row-parallel partial sums (tp > 1)
+        self.logits = torch.empty((B, self.vocab_loc), **f16)
+        if tp > 1:
+            self.gather_val = torch.empty((tp, B), **f16)
+            self.gather_ids = torch.empty((tp, B), dtype=torch.int32, device=dev)
         self.next_val = torch.empty((B, 1), **f16)
         self.next_ids = torch.empty((B, 1), dtype=torch.int32, device=dev)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -87,8 +106,8 @@ class ChatGLM2Decoder:
             kc = ops.PagedKVCache(B, c.n_group, c.head_dim, c.max_len, page_size, dev, page_table)
             page_table = kc.page_table
             self.caches.append(kc)
-        self.attn_ws = ops.attn_workspace(B, c.n_head, c.head_dim, self.caches[0].max_pages, dev)
-        self.lin_ws = ops.linear_workspace(B, max(2 * c.ffn, c.vocab, self.qkv.shape[1]), 16, dev)
+        self.attn_ws = ops.attn_workspace(B, self.h_loc, c.head_dim, self.caches[0].max_pages, dev)
+        self.lin_ws = ops.linear_workspace(B, max(2 * self.f_loc, self.vocab_loc, self.qkv.shape[1], d), 16, dev)
         self.graph = None
         torch.cuda.synchronize()
 
@@ -100,20 +119,32 @@ class ChatGLM2Decoder:
                             error_flag=self.error_flag)
         ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
 
+    def _row_parallel(self, x_in, pl, site):
+        """x <- fp16(x + all_reduce(fp16(x_in . W_r^T)))  (Linear 'end' + the block's ops.add, chatglm2/model.py:113,117)."""
+        if self.tp == 1:
+            self._linear(x_in, pl, self.x, site, epilogue=ops.EPI_RESIDUAL, residual=self.x)
+            return
+        self._linear(x_in, pl, self.part, site)
+        torch.distributed.all_reduce(self.part, group=self.group)
+        ops.check(ops._lib.lib().pt_add_f16(ops._ptr(self.x), ops._ptr(self.part), self.x.numel(), ops._ptr(self.x), ops._stream()), "pt_add_f16")
+
     def enqueue_step(self):
         c, L_ = self.cfg, ops._lib.lib()
         ops.embedding(self.emb, self.ids, self.step_t, out=self.x)
         for li, L in enumerate(self.layers):
             self._linear(self.x, L["qkv"], self.qkv, "norm", gamma=L["ln1"], epilogue=ops.EPI_BIAS, bias=L["b_qkv"])
-            a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, c.n_head, ops.ROPE_CHATGLM2, ops.SOFTMAX_F16, self.score_scale,
+            a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_CHATGLM2, ops.SOFTMAX_F16, self.score_scale,
                               self.sin, self.cos, self.attn_ws, self.error_flag)
             ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
-            self._linear(self.attn, L["dense"], self.x, "attn", epilogue=ops.EPI_RESIDUAL, residual=self.x)
+            self._row_parallel(self.attn, L["dense"], "attn")
             self._linear(self.x, L["gu"], self.act, "norm", gamma=L["ln2"], epilogue=ops.EPI_SWIGLU)
-            self._linear(self.act, L["down"], self.x, "mlp", epilogue=ops.EPI_RESIDUAL, residual=self.x)
+            self._row_parallel(self.act, L["down"], "mlp")
         self._linear(self.x, self.head, self.logits, "norm", gamma=self.norm)
-        ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids), ops._stream()),
-                  "topk")
+        if self.tp == 1:
+            ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids),
+                                 ops._stream()), "topk")
+        else:
+            ops.lm_head_tp_merge(self)
         ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
 
     def reset(self, input_ids):

@@ -5,13 +5,20 @@ Per block (gpt2/model.py:41-50): NormCE -> c_attn (+bias) -> KV append + attenti
 weights, softmax with the exponent in fp16, gpt2/attention.py:59-77) -> c_proj (+bias, +residual) -> NormCE -> c_fc
 (+bias, GELU) -> c_proj (+bias, +residual); learned position embedding added to the token embedding
 (gpt2/embedding.py:31-36); final NormCE and the LM head tied to wte (gpt2/model.py:139-146).
-The state dict uses the reference's key names after `process_hf_model_state_dict` ([out, in] weights, pre-scaled query)."""
+The state dict uses the reference's key names after `process_hf_model_state_dict` ([out, in] weights, pre-scaled query).
+
+Tensor parallel (model_type 'tp', one process per GPU): c_attn 'fused_qkv', c_fc 'start', both c_proj 'end' with an NCCL
+all-reduce of the fp16 partial sums and the bias added once afterwards (gpt2/attention.py:88-96, layers/mlp.py:44-58,
+layers/linear.py:42-46), the tied head on the vocab-sharded wte with the value/id merge of layers/lm_head.py:75-116.  The
+embedding stays replicated: the reference's vocab-sharded gathers summed by an all-reduce (gpt2/embedding.py:38-46) add
+exact zeros to fp16(wte[id] + wpe[step])."""
 import ctypes
 
 import numpy as np
 import torch
 
 from . import ops
+from .tp import fused_qkv_rows, rows, vocab_rows
 
 
 class GPT2Config:
@@ -22,8 +29,12 @@ class GPT2Config:
 
 
 class GPT2Decoder:
-    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1):
+    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None):
         c = cfg
+        self.tp, self.rank, self.group = tp_size, tp_rank, group
+        tp, r = tp_size, tp_rank
+        if c.n_head % tp:
+            raise ops.PtError(f"n_head={c.n_head} not divisible by tp={tp} (gpt2/attention.py:95)")
         if c.head_dim not in (64, 128):
             raise ops.PtError(f"head size {c.head_dim} not supported by the attention kernel (64, 128)")
         if c.max_len > c.n_positions:
@@ -34,40 +45,50 @@ class GPT2Decoder:
         dev = device
         t = lambda k: state_dict[k].to(dev).to(torch.float16).contiguous()
         self.wte, self.wpe = t("transformer.wte.weight"), t("transformer.wpe.weight")
+        B, d = batch, c.d_model
+        self.d_loc, self.h_loc = d // tp, c.n_head // tp
+        cols = lambda w, k: w[:, r * (k // tp):(r + 1) * (k // tp)].contiguous()        # 'end': rank r's input features
+        end_bias = lambda b: b if tp == 1 else b.repeat(B, 1).contiguous()           # added once, after the all-reduce
         self.layers = []
         for i in range(c.n_layer):
             p = f"transformer.h.{i}."
             self.layers.append({
                 "ln1": (t(p + "ln_1.weight"), t(p + "ln_1.bias")), "ln2": (t(p + "ln_2.weight"), t(p + "ln_2.bias")),
-                "c_attn": ops.PackedLinear(ops.W_FP16, t(p + "attn.c_attn.weight")), "b_attn": t(p + "attn.c_attn.bias"),
-                "c_proj": ops.PackedLinear(ops.W_FP16, t(p + "attn.c_proj.weight")), "b_proj": t(p + "attn.c_proj.bias"),
-                "c_fc": ops.PackedLinear(ops.W_FP16, t(p + "mlp.c_fc.weight")), "b_fc": t(p + "mlp.c_fc.bias"),
-                "m_proj": ops.PackedLinear(ops.W_FP16, t(p + "mlp.c_proj.weight")), "b_mproj": t(p + "mlp.c_proj.bias"),
+                "c_attn": ops.PackedLinear(ops.W_FP16, fused_qkv_rows(t(p + "attn.c_attn.weight"), r, tp).contiguous()),
+                "b_attn": fused_qkv_rows(t(p + "attn.c_attn.bias"), r, tp).contiguous(),
+                "c_proj": ops.PackedLinear(ops.W_FP16, cols(t(p + "attn.c_proj.weight"), d)), "b_proj": end_bias(t(p + "attn.c_proj.bias")),
+                "c_fc": ops.PackedLinear(ops.W_FP16, rows(t(p + "mlp.c_fc.weight"), r, tp).contiguous()),
+                "b_fc": rows(t(p + "mlp.c_fc.bias"), r, tp).contiguous(),
+                "m_proj": ops.PackedLinear(ops.W_FP16, cols(t(p + "mlp.c_proj.weight"), 4 * d)), "b_mproj": end_bias(t(p + "mlp.c_proj.bias")),
             })
         self.ln_f = (t("transformer.ln_f.weight"), t("transformer.ln_f.bias"))
-        self.head = ops.PackedLinear(ops.W_FP16, self.wte)                       # tied: logits = h . wte^T
-        B, d = batch, c.d_model
+        head, self.vocab_loc = vocab_rows(self.wte, r, tp) if tp > 1 else (self.wte, c.vocab)
+        self.head = ops.PackedLinear(ops.W_FP16, head)                           # tied: logits = h . wte^T
         f16 = dict(dtype=torch.float16, device=dev)
         self.ids = torch.full((B, c.max_len), self.pad_id, dtype=torch.int32, device=dev)
         self.pos = torch.arange(c.max_len, dtype=torch.int32, device=dev).repeat(B, 1).contiguous()   # position ids = step
         self.step_t = torch.zeros(1, dtype=torch.int32, device=dev)
         self.stop_mask = torch.zeros(B, dtype=torch.int32, device=dev)
         self.x, self.tok, self.pe, self.h = (torch.empty((B, d), **f16) for _ in range(4))
-        self.qkv = torch.empty((B, 3 * d), **f16)
-        self.attn = torch.empty((B, d), **f16)
-        self.act = torch.empty((B, 4 * d), **f16)
-        self.logits = torch.empty((B, c.vocab), **f16)
+        self.qkv = torch.empty((B, 3 * self.d_loc), **f16)
+        self.attn = torch.empty((B, self.d_loc), **f16)
+        self.act = torch.empty((B, 4 * self.d_loc), **f16)
+        self.part = torch.empty((B, d), **f16)                       # row-parallel partial sums (tp > 1)
+        self.logits = torch.empty((B, self.vocab_loc), **f16)
+        if tp > 1:
+            self.gather_val = torch.empty((tp, B), **f16)
+            self.gather_ids = torch.empty((tp, B), dtype=torch.int32, device=dev)
         self.next_val = torch.empty((B, 1), **f16)
         self.next_ids = torch.empty((B, 1), dtype=torch.int32, device=dev)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
         page_table = None
         self.caches = []
         for _ in range(c.n_layer):
-            kc = ops.PagedKVCache(B, c.n_head, c.head_dim, c.max_len, page_size, dev, page_table)
+            kc = ops.PagedKVCache(B, self.h_loc, c.head_dim, c.max_len, page_size, dev, page_table)
             page_table = kc.page_table
             self.caches.append(kc)
-        self.attn_ws = ops.attn_workspace(B, c.n_head, c.head_dim, self.caches[0].max_pages, dev)
-        self.lin_ws = ops.linear_workspace(B, max(4 * d, c.vocab), 16, dev)
+        self.attn_ws = ops.attn_workspace(B, self.h_loc, c.head_dim, self.caches[0].max_pages, dev)
+        self.lin_ws = ops.linear_workspace(B, max(4 * d, self.vocab_loc), 16, dev)
         self.graph = None
         torch.cuda.synchronize()
 
@@ -79,6 +100,17 @@ class GPT2Decoder:
         ops.check(ops._lib.lib().pt_norm_ce(ops._ptr(x), ops._ptr(gb[0]), ops._ptr(gb[1]), self.batch, self.cfg.d_model, self.cfg.eps,
                                             ops._ptr(out), ops._stream()), "pt_norm_ce")
 
+    def _row_parallel(self, x_in, pl, bias):
+        """x <- fp16(x + fp16(all_reduce(fp16(x_in . W_r^T)) + bias))  (Linear 'end' + the block's ops.add, gpt2/model.py:44-49)."""
+        if self.tp == 1:
+            self._linear(x_in, pl, self.x, ops.EPI_BIAS_RESIDUAL, bias, residual=self.x)
+            return
+        L_ = ops._lib.lib()
+        self._linear(x_in, pl, self.part, ops.EPI_STORE, None)
+        torch.distributed.all_reduce(self.part, group=self.group)
+        ops.check(L_.pt_add_f16(ops._ptr(self.part), ops._ptr(bias), self.part.numel(), ops._ptr(self.part), ops._stream()), "pt_add_f16")
+        ops.check(L_.pt_add_f16(ops._ptr(self.x), ops._ptr(self.part), self.x.numel(), ops._ptr(self.x), ops._stream()), "pt_add_f16")
+
     def enqueue_step(self):
         c, L_ = self.cfg, ops._lib.lib()
         ops.embedding(self.wte, self.ids, self.step_t, out=self.tok)
@@ -87,17 +119,20 @@ class GPT2Decoder:
         for li, L in enumerate(self.layers):
             self._norm(self.x, L["ln1"], self.h)
             self._linear(self.h, L["c_attn"], self.qkv, ops.EPI_BIAS, L["b_attn"])
-            a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, c.n_head, ops.ROPE_NONE, ops.SOFTMAX_F16, 1.0, None, None,
+            a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_NONE, ops.SOFTMAX_F16, 1.0, None, None,
                               self.attn_ws, self.error_flag)
             ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
-            self._linear(self.attn, L["c_proj"], self.x, ops.EPI_BIAS_RESIDUAL, L["b_proj"], residual=self.x)
+            self._row_parallel(self.attn, L["c_proj"], L["b_proj"])
             self._norm(self.x, L["ln2"], self.h)
             self._linear(self.h, L["c_fc"], self.act, ops.EPI_BIAS_GELU, L["b_fc"])
-            self._linear(self.act, L["m_proj"], self.x, ops.EPI_BIAS_RESIDUAL, L["b_mproj"], residual=self.x)
+            self._row_parallel(self.act, L["m_proj"], L["b_mproj"])
         self._norm(self.x, self.ln_f, self.h)
         self._linear(self.h, self.head, self.logits, ops.EPI_STORE, None)
-        ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids), ops._stream()),
-                  "topk")
+        if self.tp == 1:
+            ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids),
+                                 ops._stream()), "topk")
+        else:
+            ops.lm_head_tp_merge(self)
         ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
 
     def capture(self):

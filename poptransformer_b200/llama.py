@@ -268,12 +268,7 @@ class LlamaDecoder:
             ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids),
                                  ops._stream()), "topk")
         else:
-            ops.check(L_.pt_lm_head_local_topk(ops._ptr(self.logits), self.batch, self.vocab_loc, self.rank * self.vocab_loc,
-                                               ops._ptr(self.next_val), ops._ptr(self.next_ids), ops._stream()), "pt_lm_head_local_topk")
-            torch.distributed.all_gather_into_tensor(self.gather_val, self.next_val.view(1, -1), group=self.group)
-            torch.distributed.all_gather_into_tensor(self.gather_ids, self.next_ids.view(1, -1), group=self.group)
-            ops.check(L_.pt_lm_head_tp_pick(ops._ptr(self.gather_val), ops._ptr(self.gather_ids), self.tp, self.batch,
-                                            ops._ptr(self.next_ids), ops._stream()), "pt_lm_head_tp_pick")
+            ops.lm_head_tp_merge(self)
         ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
 
     def _norm_linear_raw(self, x, gamma, pl, out_ptr, out_ld):

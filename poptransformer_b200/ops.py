@@ -346,6 +346,19 @@ def step_containers(ids, step, next_ids, pad_id, eos_id=-1, stop_mask=None):
                                         _stream()), "pt_step_containers")
 
 
+def lm_head_tp_merge(dec):
+    """TPLMHead.__call__ after the matmul (layers/lm_head.py:86-115) for a decoder holding its vocab shard's logits: exact-zero
+    logits -> -10000, local top-1, + rank * vocab_per_rank, all-gather of (value, id) over the TP group, arg-max over ranks.
+    Uses the decoder's logits, next_val, next_ids, gather_val, gather_ids, vocab_loc, rank, tp and group."""
+    L = _lib.lib()
+    check(L.pt_lm_head_local_topk(_ptr(dec.logits), dec.batch, dec.vocab_loc, dec.rank * dec.vocab_loc, _ptr(dec.next_val),
+                                  _ptr(dec.next_ids), _stream()), "pt_lm_head_local_topk")
+    torch.distributed.all_gather_into_tensor(dec.gather_val, dec.next_val.view(1, -1), group=dec.group)
+    torch.distributed.all_gather_into_tensor(dec.gather_ids, dec.next_ids.view(1, -1), group=dec.group)
+    check(L.pt_lm_head_tp_pick(_ptr(dec.gather_val), _ptr(dec.gather_ids), dec.tp, dec.batch, _ptr(dec.next_ids), _stream()),
+          "pt_lm_head_tp_pick")
+
+
 def add(a, b):
     out = torch.empty_like(a)
     check(_lib.lib().pt_add_f16(_ptr(a), _ptr(b), a.numel(), _ptr(out), _stream()), "pt_add_f16")

@@ -139,9 +139,54 @@ def run_case(name):
     print(name, "ok: step", out_step, "ids[0, :12]", np.asarray(out_ids)[0, :12])
 
 
+def run_tp_strategies(name="tp_strategies"):
+    """The reference's load-time weight slicing (utils/param_handler/tensor_parallel_strategy.py:21-70, the sharded embedding
+    weight of :38-45 and ChatGLM2's rearrange_tp_weights, models/chatglm2/model.py:29-49) on small seeded integer-valued arrays.
+    Weights are in the reference's [in, out] orientation; every result has the replica axis first."""
+    import popart                                       # the numpy stand-in
+    import torch
+    from oracle import c_ref
+    tmp = tempfile.mkdtemp()                            # poptransformer/ops/customized.py:17-18 loads ../../custom_ops.so
+    os.makedirs(os.path.join(tmp, "examples", "tp"))
+    os.symlink(c_ref.build(), os.path.join(tmp, "custom_ops.so"))
+    os.chdir(os.path.join(tmp, "examples", "tp"))
+    from poptransformer.utils.registry import REGISTRY
+    from poptransformer.utils.tensor_type import TensorType
+    for k, v in dict(num_replicas=2, batch_size=1, batch_per_step=1, model_type="tp", enable_pipeline=False, precision="fp16").items():
+        REGISTRY.register(k, v)
+    REGISTRY.register("tensor_type", TensorType("fp16"))
+    REGISTRY.register("logger", logging.getLogger("poptransformer"))
+    from poptransformer.utils.param_handler import tensor_parallel_strategy as T
+    from poptransformer.models.chatglm2.model import rearrange_tp_weights
+    rng = np.random.default_rng(31)
+    arr = lambda *shape: rng.integers(-99, 100, size=shape).astype(np.float32)
+    out = {}
+    w, b = arr(6, 10), arr(10)
+    out.update(start_w=w, start_b=b, start_w_tp4=T.shard(w, 4, -1), start_b_tp4=T.shard(b, 4, -1),     # 10 outputs padded to 12
+               end_w=arr(8, 6), end_b=arr(6))
+    out.update(end_w_tp2=T.shard(out["end_w"], 2, 0), end_b_tp2=T.repeat(out["end_b"], 2))
+    qkv_w, qkv_b = arr(4, 24), arr(24)
+    out.update(qkv_w=qkv_w, qkv_b=qkv_b, qkv_w_tp2=T.shard_fused_qkv(qkv_w, 2, -1), qkv_b_tp2=T.shard_fused_qkv(qkv_b, 2, -1))
+    REGISTRY.register("query_size", 16)
+    REGISTRY.register("key_value_size", 4)
+    mq_w, mq_b = arr(4, 16), arr(16)                    # the ChatGLM2 query weight: the key/value parts of the split are empty
+    out.update(mq_w=mq_w, mq_b=mq_b, mq_w_tp2=T.shard_multi_query_qkv(mq_w, 2, -1), mq_b_tp2=T.shard_multi_query_qkv(mq_b, 2, -1))
+    mqf_w = arr(4, 24)                                  # a fused q | k | v weight: 16 query, 4 key, 4 value features
+    out.update(mqf_w=mqf_w, mqf_w_tp2=T.shard_multi_query_qkv(mqf_w, 2, -1))
+    emb = arr(11, 4)
+    out.update(emb=emb, emb_tp4=T.build_sharded_weight(emb, 4, 11, 4))
+    q_hf, dense_hf = arr(16, 4), arr(4, 16)            # HF orientation: query [out = 8 heads x 2, in], dense [out, in = 8 heads x 2]
+    for n in (2, 4):
+        out[f"rearr_q_tp{n}"] = rearrange_tp_weights(torch.from_numpy(q_hf), 8, n, axis=0).numpy()
+        out[f"rearr_dense_tp{n}"] = rearrange_tp_weights(torch.from_numpy(dense_hf), 8, n, axis=1).numpy()
+    out.update(rearr_q=q_hf, rearr_dense=dense_hf)
+    np.savez(os.path.join(ROOT, "tests", "golden", name + ".npz"), **out)
+    print(name, "ok:", sorted(out))
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 2:
-        (run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
+        (run_tp_strategies if sys.argv[2] == "tp_strategies" else run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
     else:
-        for case in list(CASES) + list(OTHER):
+        for case in list(CASES) + list(OTHER) + ["tp_strategies"]:
             subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)
