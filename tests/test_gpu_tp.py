@@ -152,4 +152,5 @@ def test_tp2_other_families_match_oracle(kind, tmp_path):
             gap = lg[b].max() - lg[b][got[0][b, t + 1]]
             assert gap <= tol * max(1.0, abs(lg[b].max())), f"{kind} row {b} position {t + 1}: GPU token is {gap} below the oracle's best"
             exact += int(gap == 0)
-    assert exact >= 0.9 * F_BATCH * (F_MAX_LEN - F_PROMPT)
+    # FP8: an activation whose last fp16 bit differs can land on the neighbouring E4M3 value, so fewer positions agree exactly
+    assert exact >= (0.75 if kind.endswith("fp8") else 0.9) * F_BATCH * (F_MAX_LEN - F_PROMPT)
