@@ -131,3 +131,31 @@ class GPT2Oracle:
                 all_logits.append(lg)
             ids, step, _ = O.step_containers(ids, step, nxt, pad_id)
         return (ids, all_logits) if return_logits else ids
+
+    def generate_beam(self, prompt, new_tokens, beam):
+        """Beam decode with the reference's `BeamSearch` op (custom_ops/beam_search_custom_op.cpp:333-478) on top of the GPT-2 step.
+        The reference registers the op but none of its Python models calls it, so the composition is the one the op's interface
+        implies: every hypothesis is a cache row (this oracle is built with batch = prompts x beam, row = prompt * beam + slot),
+        the prompt is fed token by token to all slots, and from the last prompt token on the fp16 logits are the scores the op
+        adds to the running `prob`; the op's next ids are the next input tokens and every slot continues from the cache row of
+        the hypothesis it extends.  prompt int [n_prompts, P].  Returns (hyp [n, new_tokens, beam], prob [n, beam])."""
+        if self.tp != 1:
+            raise ValueError("beam decode is defined for one rank")
+        prompt = np.asarray(prompt, dtype=np.int32)
+        n, P = prompt.shape
+        assert n * beam == self.batch
+        self.reset()
+        hyp, prob = np.zeros((n, new_tokens, beam), np.int32), np.zeros((n, beam), F16)
+        tok = np.repeat(prompt[:, 0], beam)
+        for t in range(P + new_tokens - 1):
+            lg, _ = self.logits(tok, t)
+            if t + 1 < P:
+                tok = np.repeat(prompt[:, t + 1], beam)
+                continue
+            g = t + 1 - P
+            nxt, gid, hyp, prob = O.beam_search_step(lg.reshape(n, beam, -1), hyp, prob, g, beam)
+            parent = (np.arange(n)[:, None] * beam + (np.zeros((n, beam), np.int64) if g == 0 else gid // beam)).reshape(-1)
+            for layer in self.kv:
+                layer[0].cache = O.kv_reorder_dense(layer[0].cache, parent)
+            tok = nxt.reshape(-1)
+        return hyp, prob

@@ -29,7 +29,8 @@ class GPT2Config:
 
 
 class GPT2Decoder:
-    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None):
+    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None,
+                 spare_pages=0):
         c = cfg
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         tp, r = tp_size, tp_rank
@@ -84,7 +85,7 @@ class GPT2Decoder:
         page_table = None
         self.caches = []
         for _ in range(c.n_layer):
-            kc = ops.PagedKVCache(B, self.h_loc, c.head_dim, c.max_len, page_size, dev, page_table)
+            kc = ops.PagedKVCache(B, self.h_loc, c.head_dim, c.max_len, page_size, dev, page_table, extra_pages=spare_pages)
             page_table = kc.page_table
             self.caches.append(kc)
         self.attn_ws = ops.attn_workspace(B, self.h_loc, c.head_dim, self.caches[0].max_pages, dev)
@@ -112,6 +113,11 @@ class GPT2Decoder:
         ops.check(L_.pt_add_f16(ops._ptr(self.x), ops._ptr(self.part), self.x.numel(), ops._ptr(self.x), ops._stream()), "pt_add_f16")
 
     def enqueue_step(self):
+        self.enqueue_logits()
+        self.enqueue_next()
+
+    def enqueue_logits(self):
+        """Embedding, every block, final norm and the (tied) head: fills self.logits for the token at position *step."""
         c, L_ = self.cfg, ops._lib.lib()
         ops.embedding(self.wte, self.ids, self.step_t, out=self.tok)
         ops.embedding(self.wpe, self.pos, self.step_t, out=self.pe)
@@ -128,6 +134,10 @@ class GPT2Decoder:
             self._row_parallel(self.act, L["m_proj"], L["b_mproj"])
         self._norm(self.x, self.ln_f, self.h)
         self._linear(self.h, self.head, self.logits, ops.EPI_STORE, None)
+
+    def enqueue_next(self):
+        """Greedy head and the loop carry (layers/lm_head.py:47-57, models/base_model.py:313-335)."""
+        c, L_ = self.cfg, ops._lib.lib()
         if self.tp == 1:
             ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids),
                                  ops._stream()), "topk")
@@ -173,3 +183,80 @@ class GPT2Decoder:
         if int(self.error_flag.item()) != 0:
             raise ops.PtError("a bounded device-side wait gave up")
         return {"Loop:0": self.ids.cpu().numpy(), "Loop:1": self.step_t.cpu().numpy()}
+
+
+class GPT2BeamDecoder(GPT2Decoder):
+    """Beam decode: the `BeamSearch` custom op (custom_ops/beam_search_custom_op.cpp:333-478) on top of the GPT-2 step, with the
+    beam reorder of the paged KV cache.
+
+    The reference registers the op but none of its Python models calls it, so the composition is the one the op's interface
+    implies: every hypothesis is a cache row (row = prompt * beam + slot), the prompt is fed token by token to all slots, and
+    from the last prompt token on the fp16 logits [prompts, beam, vocab] are the scores the op adds to the running `prob`; its
+    next ids become the next input tokens and every slot continues from the cache row of the hypothesis it extends (`parent`).
+    Full cache pages are shared between rows through the page table; only the page being filled is copied, into a spare page
+    per row."""
+
+    def __init__(self, cfg, state_dict, n_prompts, beam, new_tokens, device="cuda", page_size=64, pad_id=None):
+        rows = n_prompts * beam
+        super().__init__(cfg, state_dict, rows, device=device, page_size=page_size, pad_id=pad_id, spare_pages=rows)
+        self.n_prompts, self.beam, self.new_tokens = n_prompts, beam, new_tokens
+        dev = device
+        kc = self.caches[0]
+        self.spare = (torch.arange(rows, dtype=torch.int32, device=dev) + rows * kc.max_pages).contiguous()
+        self.table_tmp = torch.empty_like(kc.page_table)
+        self.table0 = kc.page_table.clone()
+        self.hyp = torch.zeros((n_prompts, new_tokens, beam), dtype=torch.int32, device=dev)
+        self.prob = torch.zeros((n_prompts, beam), dtype=torch.float16, device=dev)
+        self.gen_step = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.parent = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.beam_next = torch.empty((n_prompts, beam), dtype=torch.int32, device=dev)
+        self.beam_best = torch.empty((n_prompts, beam), dtype=torch.int32, device=dev)
+        L = ops._lib.lib()
+        self.beam_ws = torch.empty(L.pt_beam_search_workspace_bytes(n_prompts, beam, new_tokens), dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize()
+
+    def enqueue_beam(self):
+        """BeamSearch on this step's logits, the loop carry, and the cache reorder for the next step."""
+        c, L, P, S = self.cfg, ops._lib.lib(), ops._ptr, ops._stream
+        ops.check(L.pt_beam_search(P(self.logits), P(self.hyp), P(self.prob), P(self.gen_step), self.n_prompts, self.beam, c.vocab,
+                                   self.new_tokens, 0, P(self.beam_next), P(self.beam_best), P(self.parent), P(self.beam_ws),
+                                   self.beam_ws.numel(), S()), "BeamSearch")
+        # the chosen ids go into the (still padded) next column of every row's container; *step becomes the next position
+        ops.step_containers(self.ids, self.step_t, self.beam_next.view(-1, 1), self.pad_id, -1, self.stop_mask)
+        kc = self.caches[0]
+        for cache in self.caches:
+            ops.check(L.pt_kv_reorder_pages(P(cache.pool), P(kc.page_table), P(self.spare), P(self.parent), P(self.step_t), self.batch,
+                                            cache.n_kv, cache.head_dim, cache.page_size, cache.max_pages, S()), "pt_kv_reorder_pages")
+        ops.check(L.pt_kv_reorder_table(P(kc.page_table), P(self.table_tmp), P(self.spare), P(self.parent), P(self.step_t), self.batch,
+                                        kc.page_size, kc.max_pages, S()), "pt_kv_reorder_table")
+        self.gen_step.add_(1)
+
+    def start_beam(self, prompt):
+        """Loads prompt int [n_prompts, P] (equal lengths, no pad ids) into every slot's container and clears the cache mapping,
+        the hypothesis / score containers and the step counters.  Returns P."""
+        prompt = torch.as_tensor(prompt, dtype=torch.int32)
+        n, P = prompt.shape
+        if n != self.n_prompts or P + self.new_tokens > self.cfg.max_len:
+            raise ops.PtError(f"prompt shape {tuple(prompt.shape)} does not fit {self.n_prompts} prompts / max_len {self.cfg.max_len}")
+        ids = torch.full((self.batch, self.cfg.max_len), self.pad_id, dtype=torch.int32)
+        ids[:, :P] = prompt.repeat_interleave(self.beam, dim=0)
+        self.reset(ids)
+        self.caches[0].page_table.copy_(self.table0)
+        self.spare.copy_(torch.arange(self.batch, dtype=torch.int32, device=self.device) + self.batch * self.caches[0].max_pages)
+        self.hyp.zero_(); self.prob.zero_(); self.gen_step.zero_()
+        return P
+
+    def run_beam(self, prompt):
+        """Returns {'hyp': [n_prompts, new_tokens, beam], 'prob': [n_prompts, beam]}: the op's hypothesis and score containers
+        after `new_tokens` generated positions."""
+        P = self.start_beam(prompt)
+        for t in range(P + self.new_tokens - 1):
+            self.enqueue_logits()
+            if t + 1 < P:
+                self.enqueue_next()          # the container already holds the next prompt token: only *step advances
+            else:
+                self.enqueue_beam()
+        torch.cuda.synchronize()
+        if int(self.error_flag.item()) != 0:
+            raise ops.PtError("a bounded device-side wait gave up")
+        return {"hyp": self.hyp.cpu().numpy(), "prob": self.prob.cpu().numpy()}

@@ -293,3 +293,22 @@ def test_rwkv_oracle_matches_plain_float_recurrence():
             x = x / 2                      # rescale_every = 1
         exp.append(f("head.weight") @ ln(x, "rwkv.ln_out"))
     np.testing.assert_allclose(got, np.stack(exp), rtol=3e-2, atol=3e-2)
+
+
+def test_gpt2_beam_oracle_width_one_is_greedy_and_scores_are_sorted():
+    """Beam decode composed from the BeamSearch op: width 1 reproduces the greedy stream; for width 3 the running scores stay
+    sorted (the op's global top-k is sorted)."""
+    from oracle import gpt2_np
+    from poptransformer_b200 import synth
+    dims = dict(n_layer=2, d_model=128, n_head=2, vocab=301, n_positions=64)
+    sd = {k: v.numpy() for k, v in synth.gpt2_state_dict(**dims, seed=3).items()}
+    prompt = np.random.default_rng(0).integers(0, 300, (2, 5)).astype(np.int32)
+    one = gpt2_np.GPT2Oracle(gpt2_np.GPT2Config(**dims, max_len=24), sd, 2)
+    h1, _ = one.generate_beam(prompt, 8, 1)
+    ids = np.full((2, 24), 300, np.int32)
+    ids[:, :5] = prompt
+    greedy = one.generate(ids, 12, 300)
+    assert np.array_equal(h1[:, :, 0], greedy[:, 5:13])
+    three = gpt2_np.GPT2Oracle(gpt2_np.GPT2Config(**dims, max_len=24), sd, 6)
+    hyp, prob = three.generate_beam(prompt, 8, 3)
+    assert hyp.shape == (2, 8, 3) and (np.diff(prob.astype(np.float32), axis=1) <= 0).all()
