@@ -308,6 +308,145 @@ def run_b200(args):
     shutdown()
 
 
+# The other configurations of the benchmark definition: parity-test cases that can also be timed (one GPU).  Not the headline line.
+SECONDARY = {
+    # name: (family, dims, batch, prompt, new tokens)
+    "gpt2-small": ("gpt2", dict(n_layer=12, d_model=768, n_head=12, vocab=50257, n_positions=1024), 1, 32, 128),
+    "gpt2-xl-beam4": ("gpt2-beam", dict(n_layer=48, d_model=1600, n_head=25, vocab=50257, n_positions=1024), 4, 128, 256),
+    "chatglm2-6b-fp8": ("chatglm2", dict(n_layer=28, d_model=4096, n_head=32, n_group=2, ffn=13696, vocab=65024), 8, 1024, 256),
+    "rwkv4-1b5": ("rwkv", dict(n_layer=24, d_model=2048, ffn=8192, vocab=50277), 32, 256, 512),
+}
+
+
+def run_secondary(args):
+    """One of SECONDARY on cuda:0: state as after the prompt (seeded ids, random KV pages / WKV states), one CUDA-graph replay
+    per decode step, CUDA events around K steps.  The JSON line is marked `secondary` and carries a step-level roofline: the
+    bytes one step has to move (every packed linear once + the rows' KV history or recurrent state) over the step time."""
+    import torch
+    from poptransformer_b200 import chatglm2, gpt2, ops, rwkv, synth
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    fam, dims, batch, prompt, new = SECONDARY[args.workload]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    max_len = prompt + new
+    K, W = min(args.steps, new - 1), max(3, args.warmup)
+    beam = 4 if fam == "gpt2-beam" else 1
+    rows = batch * beam
+    if fam.startswith("gpt2"):
+        sd = synth.gpt2_state_dict(**dims, seed=0, device=dev)
+        cfg = gpt2.GPT2Config(**dims, max_len=max_len)
+        dec = gpt2.GPT2BeamDecoder(cfg, sd, batch, beam, new, device=dev) if beam > 1 else gpt2.GPT2Decoder(cfg, sd, batch, device=dev)
+        kv_tok = 2 * cfg.n_layer * cfg.d_model * 2
+        dtype = "fp16"
+    elif fam == "chatglm2":
+        sd = synth.chatglm2_state_dict(**dims, seed=0, device=dev, precision="fp8")
+        cfg = chatglm2.ChatGLM2Config(**dims, max_len=max_len, precision="fp8")
+        dec = chatglm2.ChatGLM2Decoder(cfg, sd, batch, device=dev)
+        kv_tok = 2 * cfg.n_layer * cfg.n_group * cfg.head_dim * 2
+        dtype = "fp8 e4m3 weights and activations, fp32 accumulate"
+    else:
+        sd = synth.rwkv_state_dict(**dims, seed=0, device=dev)
+        cfg = rwkv.RWKVConfig(**dims, max_len=max_len)
+        dec = rwkv.RWKVDecoder(cfg, sd, batch, device=dev)
+        kv_tok = 0
+        dtype = "fp16 (float32 WKV states)"
+    del sd
+    torch.cuda.empty_cache()
+    ids_host = synth.prompt_ids(rows, prompt, max_len, cfg.vocab, dec.pad_id, seed=0).pin_memory()
+    gen = torch.Generator(device=dev).manual_seed(1)
+    for kc in getattr(dec, "caches", []):
+        kc.pool.copy_((torch.randn(kc.pool.shape, generator=gen, device=dev) * 0.5).to(torch.float16))
+
+    def set_state():
+        dec.ids.copy_(ids_host, non_blocking=True)
+        dec.step_t.fill_(prompt)
+        if beam > 1:
+            dec.gen_step.fill_(1)
+            dec.prob.zero_()
+
+    def one_step():
+        if beam > 1:
+            dec.enqueue_logits()
+            dec.enqueue_beam()
+        else:
+            dec.enqueue_step()
+
+    set_state()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        one_step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    set_state()
+    n0 = ops.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_step()
+    launches_per_step = ops.launch_count() - n0
+    set_state()
+    for _ in range(W):
+        graph.replay()
+    set_state()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    if int(dec.error_flag.item()) != 0:
+        raise SystemExit("device-side bounded wait gave up during the timed region")
+    out_host = torch.empty_like(ids_host).pin_memory()
+    e2e_t = []
+    for _ in range(3):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        set_state()
+        for _ in range(K):
+            graph.replay()
+        out_host.copy_(dec.ids, non_blocking=True)
+        torch.cuda.synchronize()
+        e2e_t.append(time.perf_counter() - t0)
+    e2e_s = min(e2e_t[1:])
+
+    def packed(o):
+        if isinstance(o, ops.PackedLinear):
+            return o.nbytes
+        if isinstance(o, dict):
+            return sum(packed(v) for v in o.values())
+        return 0
+    w_bytes = sum(packed(L) for L in dec.layers) + dec.head.nbytes
+    if fam == "rwkv":
+        state_bytes = rows * cfg.n_layer * cfg.d_model * (2 * 2 + 3 * 4) * 2          # every state read and written once
+    else:
+        state_bytes = rows * kv_tok * (prompt + (K - 1) / 2.0 + 1)
+    step_bytes = w_bytes + state_bytes
+    peak, peak_src = peaks()
+    ms_step = ms / K
+    ach = step_bytes / (ms_step * 1e-3) / 1e9
+    print(json.dumps({
+        "secondary": "not the headline workload; a parity configuration timed on one GPU",
+        "metric": f"decode tokens/s ({args.workload}, batch {batch}{' x beam 4' if beam > 1 else ''}, prompt {prompt})",
+        "value": batch * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": f"{args.workload} decode b{batch} prompt{prompt}", "rows": rows, "cuda_graph": True,
+                   "l2": "inputs_larger_than_L2" if w_bytes > 126e6 * 2 else "weights comparable to L2: L2-resident reuse is part of the number"},
+        "clocks": clocks,
+        "e2e": {"value": batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": ids_host.numel() * 4 / K,
+                "d2h_bytes_per_step": ids_host.numel() * 4 / K},
+        "gpu_launches": int(launches_per_step * K),
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                     "kernel": f"all {launches_per_step} launches of one step (per-op kernels, one CUDA graph)", "peak_source": peak_src,
+                     "launch_us": ms_step * 1e3, "bytes_per_launch": step_bytes},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -319,9 +458,13 @@ def main():
     ap.add_argument("--per-op", action="store_true", help="use the per-op kernels instead of the persistent whole-step kernel")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only the first N transformer blocks, so that a profiler capture "
                     "stays small; the line is then marked profiling_only and is not a benchmark result")
+    ap.add_argument("--workload", default="llama2-7b-int4", choices=["llama2-7b-int4"] + list(SECONDARY),
+                    help="llama2-7b-int4 is the benchmark; the others time a parity configuration on one GPU (line marked `secondary`)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in SECONDARY:
+        run_secondary(args)
     else:
         run_b200(args)
 

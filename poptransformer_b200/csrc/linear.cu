@@ -35,7 +35,9 @@ namespace pt {
 
 constexpr int kWarps = 8;  // warps per block = row tiles per block
 constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 4;  // ring depth per warp
+// Ring depth per warp.  (Measured on B200 at 16 and 32 batch rows: 8 stages are slower than 4, the doubled ring costs more
+// in resident blocks than the deeper prefetch gains.)
+constexpr int kRingStages = 4;
 
 struct LinearParams {
   const unsigned char *w;
@@ -57,7 +59,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // Grid: (ceil(row_tiles / 8), ksplit).  Block: 8 warps; warp w owns row tile blockIdx.x * 8 + w and the block's
 // k-slice.  Dynamic shared memory: [activations, B rows, swizzled per chunk][INT4 offset corrections]
 // [ring: 8 warps x kStages tiles].
-template <int WFMT, int NB>
+template <int WFMT, int NB, int kStages>
 __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) {
   constexpr int UNITS = WTraits<WFMT>::kUnits;
   constexpr int CHUNK_K = WTraits<WFMT>::kChunkK;
@@ -79,7 +81,6 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
   float *corr = reinterpret_cast<float *>(smem + xs_bytes);  // [slice chunks][BP] (INT4 only)
   const size_t corr_bytes = WFMT == PT_W_INT4 ? ((size_t)p.chunks_per_split * BP * sizeof(float) + 127) / 128 * 128 : 0;
   unsigned char *ring = smem + xs_bytes + corr_bytes + (size_t)warp * kStages * TILE;
-  __shared__ float s_red[32];
   __shared__ float s_stat[32];
   __shared__ int s_last;
 
@@ -125,15 +126,16 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
       if (tid + q * kThreads < total_units) pre[q] = __ldcg(unit_src(tid + q * kThreads));
   }
   if (do_norm) {
-    // r_b = fp16(1 / sqrt(mean(x^2) + eps)) over the whole row (all chunks, not only this slice)
+    // r_b = fp16(1 / sqrt(mean(x^2) + eps)) over the whole row (all chunks, not only this slice); warp w takes rows w, w + 8, ...
+    // (fixed lane order and a fixed shuffle tree: deterministic)
     const int units = p.K / 8;
-    for (int b = 0; b < p.B; ++b) {
+    for (int b = warp; b < p.B; b += kWarps) {
       float ss = 0.f;
       const uint4 *xr = reinterpret_cast<const uint4 *>(p.x + (size_t)b * p.K);
-      for (int i0 = tid; i0 < units; i0 += 4 * kThreads) {
+      for (int i0 = lane; i0 < units; i0 += 4 * 32) {
         uint4 v[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) v[q] = (i0 + q * kThreads < units) ? __ldcg(xr + i0 + q * kThreads) : make_uint4(0, 0, 0, 0);
+        for (int q = 0; q < 4; ++q) v[q] = (i0 + q * 32 < units) ? __ldcg(xr + i0 + q * 32) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const __half2 *h = reinterpret_cast<const __half2 *>(&v[q]);
@@ -144,8 +146,9 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
           }
         }
       }
-      ss = block_sum(ss, s_red);
-      if (tid == 0) s_stat[b] = __half2float(__float2half_rn(1.0f / sqrtf(ss / (float)p.K + p.eps)));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_stat[b] = __half2float(__float2half_rn(1.0f / sqrtf(ss / (float)p.K + p.eps)));
     }
     __syncthreads();
   }
@@ -173,8 +176,18 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
 #pragma unroll
     for (int q = 0; q < PRE; ++q)
       if (tid + q * kThreads < total_units) stage_unit(tid + q * kThreads, pre[q]);
-  } else {
+  } else if constexpr (NB == 1) {
     for (int i = tid; i < total_units; i += kThreads) stage_unit(i, __ldcg(unit_src(i)));
+  } else {
+    for (int i0 = tid; i0 < total_units; i0 += PRE * kThreads) {   // PRE loads in flight per thread
+      uint4 v[PRE];
+#pragma unroll
+      for (int q = 0; q < PRE; ++q)
+        if (i0 + q * kThreads < total_units) v[q] = __ldcg(unit_src(i0 + q * kThreads));
+#pragma unroll
+      for (int q = 0; q < PRE; ++q)
+        if (i0 + q * kThreads < total_units) stage_unit(i0 + q * kThreads, v[q]);
+    }
   }
   __syncthreads();
   if constexpr (WFMT == PT_W_INT4) {
@@ -281,16 +294,33 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
     __threadfence();
     if (tid == 0) p.counters[blockIdx.x] = 0;  // ready for the next launch on this stream
     if (active) {
+      // Sum in split order (deterministic).  The loads of two splits (2 x 4 NB values) are issued together, so the reduction
+      // costs ksplit / 2 trips to L2 instead of one per (value, split).
 #pragma unroll
       for (int t = 0; t < NB; ++t)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int bcol = t * 8 + 2 * tig + (j & 1), row = g + 8 * (j >> 1);
-          float v = 0.f;
-          if (bcol < p.B)
-            for (int s = 0; s < p.ksplit; ++s) v += __ldcg(p.partial + ((size_t)s * p.B + bcol) * npad + rt * 16 + row);
-          acc[t][j] = v;
-        }
+        for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
+      const float *base = p.partial + (size_t)rt * 16 + g;
+      for (int s0 = 0; s0 < p.ksplit; s0 += 2) {
+        float a0[NB][4], a1[NB][4];
+        const bool two = s0 + 1 < p.ksplit;
+#pragma unroll
+        for (int t = 0; t < NB; ++t)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int bcol = t * 8 + 2 * tig + (j & 1), row8 = 8 * (j >> 1);
+            const bool ok = bcol < p.B;
+            a0[t][j] = ok ? __ldcg(base + ((size_t)s0 * p.B + bcol) * npad + row8) : 0.f;
+            a1[t][j] = (ok && two) ? __ldcg(base + ((size_t)(s0 + 1) * p.B + bcol) * npad + row8) : 0.f;
+          }
+#pragma unroll
+        for (int t = 0; t < NB; ++t)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[t][j] += a0[t][j];
+            if (two) acc[t][j] += a1[t][j];
+          }
+      }
     }
   }
   if (!active) return;
@@ -385,10 +415,10 @@ __global__ void repack_kernel(const uint4 *__restrict__ src, const __half *__res
   }
 }
 
-template <int WFMT, int NB> static int launch_linear(const LinearParams &p, size_t smem, cudaStream_t st) {
+template <int WFMT, int NB, int ST> static int launch_linear(const LinearParams &p, size_t smem, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
-    PT_CUDA(cudaFuncSetAttribute(linear_kernel<WFMT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    PT_CUDA(cudaFuncSetAttribute(linear_kernel<WFMT, NB, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -401,16 +431,16 @@ template <int WFMT, int NB> static int launch_linear(const LinearParams &p, size
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_kernel<WFMT, NB>, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_kernel<WFMT, NB, ST>, p);
   if (e != cudaSuccess) return pt::set_error(PT_ERR_CUDA, "pt_linear: %s", cudaGetErrorString(e));
   PT_LAUNCH_CHECK("pt_linear");
   return PT_OK;
 }
 
 template <int WFMT> static int dispatch_nb(const LinearParams &p, size_t smem, cudaStream_t st) {
-  if (p.B <= 8) return launch_linear<WFMT, 1>(p, smem, st);
-  if (p.B <= 16) return launch_linear<WFMT, 2>(p, smem, st);
-  return launch_linear<WFMT, 4>(p, smem, st);
+  if (p.B <= 8) return launch_linear<WFMT, 1, kRingStages>(p, smem, st);
+  if (p.B <= 16) return launch_linear<WFMT, 2, kRingStages>(p, smem, st);
+  return launch_linear<WFMT, 4, kRingStages>(p, smem, st);
 }
 
 }  // namespace pt
@@ -502,7 +532,7 @@ extern "C" int pt_linear(const pt_linear_args *a, void *stream) {
     ksplit = std::max(1, std::min(ksplit, p.nchunks / 4));
   }
   ksplit = std::max(1, std::min(ksplit, p.nchunks));
-  const size_t ring_bytes = (size_t)kWarps * kStages * tile_bytes(a->wfmt);
+  const size_t ring_bytes = (size_t)kWarps * kRingStages * tile_bytes(a->wfmt);
   const size_t smem_budget = 200 * 1024;
   auto smem_bytes = [&](int ksp) {
     const int cps = ceil_div(p.nchunks, ksp);
