@@ -333,22 +333,25 @@ def run_secondary(args):
     K, W = min(args.steps, new - 1), max(3, args.warmup)
     beam = 4 if fam == "gpt2-beam" else 1
     rows = batch * beam
+    pdl = {} if args.pdl < 0 else dict(pdl_linear=args.pdl & 1, pdl_attn=(args.pdl >> 1) & 1)
+    if fam == "rwkv":
+        pdl.pop("pdl_attn", None)
     if fam.startswith("gpt2"):
         sd = synth.gpt2_state_dict(**dims, seed=0, device=dev)
         cfg = gpt2.GPT2Config(**dims, max_len=max_len)
-        dec = gpt2.GPT2BeamDecoder(cfg, sd, batch, beam, new, device=dev) if beam > 1 else gpt2.GPT2Decoder(cfg, sd, batch, device=dev)
+        dec = gpt2.GPT2BeamDecoder(cfg, sd, batch, beam, new, device=dev, **pdl) if beam > 1 else gpt2.GPT2Decoder(cfg, sd, batch, device=dev, **pdl)
         kv_tok = 2 * cfg.n_layer * cfg.d_model * 2
         dtype = "fp16"
     elif fam == "chatglm2":
         sd = synth.chatglm2_state_dict(**dims, seed=0, device=dev, precision="fp8")
         cfg = chatglm2.ChatGLM2Config(**dims, max_len=max_len, precision="fp8")
-        dec = chatglm2.ChatGLM2Decoder(cfg, sd, batch, device=dev)
+        dec = chatglm2.ChatGLM2Decoder(cfg, sd, batch, device=dev, **pdl)
         kv_tok = 2 * cfg.n_layer * cfg.n_group * cfg.head_dim * 2
         dtype = "fp8 e4m3 weights and activations, fp32 accumulate"
     else:
         sd = synth.rwkv_state_dict(**dims, seed=0, device=dev)
         cfg = rwkv.RWKVConfig(**dims, max_len=max_len)
-        dec = rwkv.RWKVDecoder(cfg, sd, batch, device=dev)
+        dec = rwkv.RWKVDecoder(cfg, sd, batch, device=dev, **pdl)
         kv_tok = 0
         dtype = "fp16 (float32 WKV states)"
     del sd
@@ -458,6 +461,8 @@ def main():
     ap.add_argument("--per-op", action="store_true", help="use the per-op kernels instead of the persistent whole-step kernel")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only the first N transformer blocks, so that a profiler capture "
                     "stays small; the line is then marked profiling_only and is not a benchmark result")
+    ap.add_argument("--pdl", type=int, default=-1, help="secondary workloads: programmatic dependent launch, bit 0 = linear kernels, bit 1 = "
+                    "attention kernel (-1: the decoder's default)")
     ap.add_argument("--workload", default="llama2-7b-int4", choices=["llama2-7b-int4"] + list(SECONDARY),
                     help="llama2-7b-int4 is the benchmark; the others time a parity configuration on one GPU (line marked `secondary`)")
     args = ap.parse_args()

@@ -20,6 +20,10 @@ from . import ops
 from .tp import multi_query_head_index, rows, vocab_rows
 
 
+# Programmatic dependent launch of the (linear, attention) kernels; off by default: measured neutral to 4 % slower at 8 rows on B200.
+PDL_DEFAULT = (0, 0)
+
+
 class ChatGLM2Config:
     def __init__(self, n_layer, d_model, n_head, n_group, ffn, vocab, max_len, eps=1e-5, precision="fp16", act_scales=None):
         self.n_layer, self.d_model, self.n_head, self.n_group, self.ffn, self.vocab, self.max_len, self.eps = (
@@ -40,8 +44,10 @@ def chatglm2_rope_tables(max_len, head_dim, device):
 
 
 class ChatGLM2Decoder:
-    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None):
+    def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None,
+                 pdl_linear=None, pdl_attn=None):
         c = cfg
+        self.pdl_linear, self.pdl_attn = PDL_DEFAULT[0] if pdl_linear is None else int(pdl_linear), PDL_DEFAULT[1] if pdl_attn is None else int(pdl_attn)
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         tp, r = tp_size, tp_rank
         if (c.n_head // c.n_group) % tp or c.ffn % tp:
@@ -116,7 +122,7 @@ class ChatGLM2Decoder:
         pro = (ops.PRO_RMSNORM_CAST_FP8 if fp8 else ops.PRO_RMSNORM) if gamma is not None else (ops.PRO_CAST_FP8 if fp8 else ops.PRO_NONE)
         a = ops.linear_args(x, pl, out, prologue=pro, epilogue=epilogue, gamma=gamma, eps=self.cfg.eps,
                             act_scale=self.cfg.act_scales[site] if fp8 else 0.0, bias=bias, residual=residual, workspace=self.lin_ws,
-                            error_flag=self.error_flag)
+                            error_flag=self.error_flag, pdl=self.pdl_linear)
         ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
 
     def _row_parallel(self, x_in, pl, site):
@@ -134,7 +140,7 @@ class ChatGLM2Decoder:
         for li, L in enumerate(self.layers):
             self._linear(self.x, L["qkv"], self.qkv, "norm", gamma=L["ln1"], epilogue=ops.EPI_BIAS, bias=L["b_qkv"])
             a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_CHATGLM2, ops.SOFTMAX_F16, self.score_scale,
-                              self.sin, self.cos, self.attn_ws, self.error_flag)
+                              self.sin, self.cos, self.attn_ws, self.error_flag, pdl=self.pdl_attn)
             ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
             self._row_parallel(self.attn, L["dense"], "attn")
             self._linear(self.x, L["gu"], self.act, "norm", gamma=L["ln2"], epilogue=ops.EPI_SWIGLU)

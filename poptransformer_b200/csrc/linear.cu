@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
   const size_t corr_bytes = WFMT == PT_W_INT4 ? ((size_t)p.chunks_per_split * BP * sizeof(float) + 127) / 128 * 128 : 0;
   unsigned char *ring = smem + xs_bytes + corr_bytes + (size_t)warp * kStages * TILE;
   __shared__ float s_stat[32];
+  __shared__ float s_part[32 * kWarps];
   __shared__ int s_last;
 
   // ---- start streaming this warp's tiles before anything else (they do not depend on the previous kernel)
@@ -126,16 +127,19 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
       if (tid + q * kThreads < total_units) pre[q] = __ldcg(unit_src(tid + q * kThreads));
   }
   if (do_norm) {
-    // r_b = fp16(1 / sqrt(mean(x^2) + eps)) over the whole row (all chunks, not only this slice); warp w takes rows w, w + 8, ...
-    // (fixed lane order and a fixed shuffle tree: deterministic)
+    // r_b = fp16(1 / sqrt(mean(x^2) + eps)) over the whole row (all chunks, not only this slice).  The 8 warps are spread over
+    // the rows: with 8 or more rows warp w takes rows w, w + 8, ...; with fewer rows each row gets 8 / B warps that sum
+    // interleaved parts of it.  Lane order, shuffle tree and the order of the parts are fixed: deterministic.
     const int units = p.K / 8;
-    for (int b = warp; b < p.B; b += kWarps) {
+    const int wpr = p.B >= kWarps ? 1 : kWarps / p.B;           // warps per row
+    const int part = warp % wpr;
+    for (int b = warp / wpr; b < p.B; b += kWarps / wpr) {
       float ss = 0.f;
       const uint4 *xr = reinterpret_cast<const uint4 *>(p.x + (size_t)b * p.K);
-      for (int i0 = lane; i0 < units; i0 += 4 * 32) {
+      for (int i0 = part * 32 + lane; i0 < units; i0 += 4 * 32 * wpr) {
         uint4 v[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) v[q] = (i0 + q * 32 < units) ? __ldcg(xr + i0 + q * 32) : make_uint4(0, 0, 0, 0);
+        for (int q = 0; q < 4; ++q) v[q] = (i0 + q * 32 * wpr < units) ? __ldcg(xr + i0 + q * 32 * wpr) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const __half2 *h = reinterpret_cast<const __half2 *>(&v[q]);
@@ -148,7 +152,13 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) s_stat[b] = __half2float(__float2half_rn(1.0f / sqrtf(ss / (float)p.K + p.eps)));
+      if (lane == 0) s_part[b * kWarps + part] = ss;
+    }
+    __syncthreads();
+    if (tid < p.B) {
+      float ss = 0.f;
+      for (int q = 0; q < wpr; ++q) ss += s_part[tid * kWarps + q];
+      s_stat[tid] = __half2float(__float2half_rn(1.0f / sqrtf(ss / (float)p.K + p.eps)));
     }
     __syncthreads();
   }
@@ -522,14 +532,16 @@ extern "C" int pt_linear(const pt_linear_args *a, void *stream) {
   p.out_scale = 1.0f;
   if (a->wfmt == PT_W_FP8) p.out_scale = (a->w_scale > 0.f ? a->w_scale : 1.0f) * (cast ? a->act_scale : 1.0f);
 
-  // k-split: about 24 warps per SM in total (one warp per (row tile, k-slice)), at least 4 chunks per warp, and an
+  // k-split: about 24 warps per SM in total (one warp per (row tile, k-slice)); at least 8 chunks (8 KB of weights) per warp
+  // for FP16 / FP8 so that the fixed cost of a warp (prologue, split-k reduction) stays small, 4 chunks for INT4, whose
+  // tiles carry four times the math (both measured on B200 over the decode shapes of the supported models); and an
   // activation slice that fits shared memory next to the rings.
   const int nb = a->batch <= 8 ? 1 : (a->batch <= 16 ? 2 : 4);
   int ksplit = a->ksplit;
   if (ksplit <= 0) {
     const int want_warps = 148 * 24;
     ksplit = std::max(1, want_warps / p.n_rt);
-    ksplit = std::max(1, std::min(ksplit, p.nchunks / 4));
+    ksplit = std::max(1, std::min(ksplit, p.nchunks / (a->wfmt == PT_W_INT4 ? 4 : 8)));
   }
   ksplit = std::max(1, std::min(ksplit, p.nchunks));
   const size_t ring_bytes = (size_t)kWarps * kRingStages * tile_bytes(a->wfmt);

@@ -21,6 +21,13 @@ from . import ops
 from .tp import fused_qkv_rows, rows, vocab_rows
 
 
+def pdl_default(rows):
+    """Programmatic dependent launch of the (linear, attention) kernels: a kernel launched this way starts its weight prefetch
+    while the previous kernel of the stream drains.  Measured on B200: 5 % faster steps for GPT-2 small at one row, where every
+    kernel is a single short wave; neutral or slower (waiting blocks hold shared memory) at 16 rows."""
+    return (1, 1) if rows <= 2 else (0, 0)
+
+
 class GPT2Config:
     def __init__(self, n_layer, d_model, n_head, vocab, n_positions, max_len, eps=1e-5):
         self.n_layer, self.d_model, self.n_head, self.vocab, self.n_positions, self.max_len, self.eps = (
@@ -30,9 +37,11 @@ class GPT2Config:
 
 class GPT2Decoder:
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None,
-                 spare_pages=0):
+                 spare_pages=0, pdl_linear=None, pdl_attn=None):
         c = cfg
         self.tp, self.rank, self.group = tp_size, tp_rank, group
+        self.pdl_linear = pdl_default(batch)[0] if pdl_linear is None else int(pdl_linear)
+        self.pdl_attn = pdl_default(batch)[1] if pdl_attn is None else int(pdl_attn)
         tp, r = tp_size, tp_rank
         if c.n_head % tp:
             raise ops.PtError(f"n_head={c.n_head} not divisible by tp={tp} (gpt2/attention.py:95)")
@@ -94,7 +103,8 @@ class GPT2Decoder:
         torch.cuda.synchronize()
 
     def _linear(self, x, pl, out, epilogue, bias, residual=None):
-        a = ops.linear_args(x, pl, out, epilogue=epilogue, bias=bias, residual=residual, workspace=self.lin_ws, error_flag=self.error_flag)
+        a = ops.linear_args(x, pl, out, epilogue=epilogue, bias=bias, residual=residual, workspace=self.lin_ws, error_flag=self.error_flag,
+                            pdl=self.pdl_linear)
         ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
 
     def _norm(self, x, gb, out):
@@ -126,7 +136,7 @@ class GPT2Decoder:
             self._norm(self.x, L["ln1"], self.h)
             self._linear(self.h, L["c_attn"], self.qkv, ops.EPI_BIAS, L["b_attn"])
             a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_NONE, ops.SOFTMAX_F16, 1.0, None, None,
-                              self.attn_ws, self.error_flag)
+                              self.attn_ws, self.error_flag, pdl=self.pdl_attn)
             ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
             self._row_parallel(self.attn, L["c_proj"], L["b_proj"])
             self._norm(self.x, L["ln2"], self.h)
@@ -196,9 +206,9 @@ class GPT2BeamDecoder(GPT2Decoder):
     Full cache pages are shared between rows through the page table; only the page being filled is copied, into a spare page
     per row."""
 
-    def __init__(self, cfg, state_dict, n_prompts, beam, new_tokens, device="cuda", page_size=64, pad_id=None):
+    def __init__(self, cfg, state_dict, n_prompts, beam, new_tokens, device="cuda", page_size=64, pad_id=None, **kw):
         rows = n_prompts * beam
-        super().__init__(cfg, state_dict, rows, device=device, page_size=page_size, pad_id=pad_id, spare_pages=rows)
+        super().__init__(cfg, state_dict, rows, device=device, page_size=page_size, pad_id=pad_id, spare_pages=rows, **kw)
         self.n_prompts, self.beam, self.new_tokens = n_prompts, beam, new_tokens
         dev = device
         kc = self.caches[0]

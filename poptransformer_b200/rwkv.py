@@ -19,6 +19,10 @@ from . import ops
 from .tp import rows, vocab_rows
 
 
+# Programmatic dependent launch of the linear kernels; off by default: measured 2 % slower at 32 rows on B200.
+PDL_DEFAULT = 0
+
+
 class RWKVConfig:
     def __init__(self, n_layer, d_model, ffn, vocab, max_len, rescale_every=6, eps=1e-5):
         self.n_layer, self.d_model, self.ffn, self.vocab, self.max_len, self.rescale_every, self.eps = (
@@ -26,8 +30,9 @@ class RWKVConfig:
 
 
 class RWKVDecoder:
-    def __init__(self, cfg, state_dict, batch, device="cuda", pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None):
+    def __init__(self, cfg, state_dict, batch, device="cuda", pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None, pdl_linear=None):
         c = cfg
+        self.pdl_linear = PDL_DEFAULT if pdl_linear is None else int(pdl_linear)
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         tp, r = tp_size, tp_rank
         if c.d_model % (32 * tp) or c.ffn % (32 * tp):
@@ -89,7 +94,7 @@ class RWKVDecoder:
         torch.cuda.synchronize()
 
     def _linear(self, x, pl, out, epilogue=ops.EPI_STORE, residual=None):
-        a = ops.linear_args(x, pl, out, epilogue=epilogue, residual=residual, workspace=self.lin_ws, error_flag=self.error_flag)
+        a = ops.linear_args(x, pl, out, epilogue=epilogue, residual=residual, workspace=self.lin_ws, error_flag=self.error_flag, pdl=self.pdl_linear)
         ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
 
     def _norm(self, x, gb, out):
