@@ -15,7 +15,7 @@
 namespace pt {
 
 struct AttnParams {
-  int B, n_head, n_kv, qpk, H, page, max_pages, rope_mode, softmax_mode, rot_half, out_ld, pdl;
+  int B, n_head, n_kv, qpk, qsplit, H, page, max_pages, rope_mode, softmax_mode, rot_half, out_ld, pdl;
   __half scale_h;
   int use_scale;
   const int *step;
@@ -25,7 +25,7 @@ struct AttnParams {
   __half *out;
   float *ws_o;     // [B, n_head, max_pages, H]
   float2 *ws_ml;   // [B, n_head, max_pages]
-  int *counters;   // [B, n_kv]
+  int *counters;   // [B, n_kv, qsplit]
   int *error_flag;
 };
 
@@ -92,14 +92,19 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
   const int PAGE = p.page;
   __half *Ks = reinterpret_cast<__half *>(smem);
   __half *Vs = Ks + (size_t)PAGE * H;
-  __half *qs = Vs + (size_t)PAGE * H;                      // [qpk][H]
-  float *ps = reinterpret_cast<float *>(qs + (size_t)p.qpk * H);  // [qpk][PAGE]
-  float *ml = ps + (size_t)p.qpk * PAGE;                   // [qpk][2]
+  const int nq_s = p.qpk / p.qsplit;                       // q heads handled by this block
+  __half *qs = Vs + (size_t)PAGE * H;                      // [nq][H]
+  float *ps = reinterpret_cast<float *>(qs + (size_t)nq_s * H);  // [nq][PAGE]
+  float *ml = ps + (size_t)nq_s * PAGE;                    // [nq][2]
   __shared__ __align__(8) uint64_t bar;
   __shared__ int s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int pg = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // With many q heads per kv head (multi-query attention) the heads of a group are shared out over `qsplit` blocks: each
+  // re-reads the group's K/V page (through L2) and handles nq of the group's heads, which shortens both the per-page work
+  // and the serial combine of the last block.
+  const int pg = blockIdx.x, kvh = blockIdx.y / p.qsplit, qpart = blockIdx.y - kvh * p.qsplit, b = blockIdx.z;
+  const int nq = p.qpk / p.qsplit, q_lo = qpart * nq;   // this block's heads of the group: q_lo .. q_lo + nq - 1
   if (p.pdl) {
     // let the next kernel start prefetching its weights; everything this kernel reads was produced upstream
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -131,9 +136,9 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
   const __half *qrow = p.qkv + (size_t)b * row_elems;
   const __half *sin_r = p.sin_t + (size_t)step * p.rot_half;
   const __half *cos_r = p.cos_t + (size_t)step * p.rot_half;
-  for (int i = tid; i < p.qpk * (H / 2); i += kAttnThreads) {
+  for (int i = tid; i < nq * (H / 2); i += kAttnThreads) {
     const int qh = i / (H / 2), j = i - qh * (H / 2);
-    rope_pair(p, qrow + (size_t)(kvh * p.qpk + qh) * H, sin_r, cos_r, j, qs + (size_t)qh * H);
+    rope_pair(p, qrow + (size_t)(kvh * p.qpk + q_lo + qh) * H, sin_r, cos_r, j, qs + (size_t)qh * H);
   }
   if (owner) {
     const int slot = n_valid - 1;
@@ -142,9 +147,11 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
     for (int j = tid; j < H / 2; j += kAttnThreads) rope_pair(p, knew, sin_r, cos_r, j, Ks + (size_t)slot * H);
     for (int j = tid; j < H; j += kAttnThreads) Vs[(size_t)slot * H + j] = vnew[j];
     __syncthreads();
-    for (int j = tid; j < H; j += kAttnThreads) {
-      gK[(size_t)slot * H + j] = Ks[(size_t)slot * H + j];
-      gV[(size_t)slot * H + j] = Vs[(size_t)slot * H + j];
+    if (qpart == 0) {   // one block of the group appends to the pool; the others only need the new token in their tile
+      for (int j = tid; j < H; j += kAttnThreads) {
+        gK[(size_t)slot * H + j] = Ks[(size_t)slot * H + j];
+        gV[(size_t)slot * H + j] = Vs[(size_t)slot * H + j];
+      }
     }
   }
   __syncthreads();  // barrier initialised, q staged
@@ -177,7 +184,7 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
 #pragma unroll
         for (int j = 0; j < EPL; ++j) kf[j] = 0.f;
       }
-      for (int qh = 0; qh < p.qpk; ++qh) {
+      for (int qh = 0; qh < nq; ++qh) {
         float s = 0.f;
 #pragma unroll
         for (int v = 0; v < EPL / 8; ++v) {
@@ -204,7 +211,7 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
   __syncthreads();
 
   // ---- per-head softmax statistics (one warp per q head, warp-shuffle reductions)
-  for (int qh = warp; qh < p.qpk; qh += kAttnThreads / 32) {
+  for (int qh = warp; qh < nq; qh += kAttnThreads / 32) {
     float *pr = ps + (size_t)qh * PAGE;
     float m = -INFINITY;
     if (p.softmax_mode == PT_SOFTMAX_F32) {
@@ -226,35 +233,35 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
   __syncthreads();
 
   // ---- P.V: one thread per output channel, V element reused across the group's q heads
-  const size_t head0 = (size_t)b * p.n_head + (size_t)kvh * p.qpk;
+  const size_t head0 = (size_t)b * p.n_head + (size_t)kvh * p.qpk + q_lo;
   if (tid < H) {
-    for (int q0 = 0; q0 < p.qpk; q0 += 4) {
+    for (int q0 = 0; q0 < nq; q0 += 4) {
       float o[4] = {0.f, 0.f, 0.f, 0.f};
-      const int nq = min(4, p.qpk - q0);
+      const int n4 = min(4, nq - q0);
       for (int t = 0; t < n_valid; ++t) {
         const float v = __half2float(Vs[(size_t)t * H + tid]);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (k < nq) o[k] += ps[(size_t)(q0 + k) * PAGE + t] * v;
+          if (k < n4) o[k] += ps[(size_t)(q0 + k) * PAGE + t] * v;
       }
-      for (int k = 0; k < nq; ++k) p.ws_o[((head0 + q0 + k) * p.max_pages + pg) * H + tid] = o[k];
+      for (int k = 0; k < n4; ++k) p.ws_o[((head0 + q0 + k) * p.max_pages + pg) * H + tid] = o[k];
     }
   }
-  if (tid < p.qpk) p.ws_ml[(head0 + tid) * p.max_pages + pg] = make_float2(ml[2 * tid], ml[2 * tid + 1]);
-  for (int qh = tid + kAttnThreads; qh < p.qpk; qh += kAttnThreads)
+  if (tid < nq) p.ws_ml[(head0 + tid) * p.max_pages + pg] = make_float2(ml[2 * tid], ml[2 * tid + 1]);
+  for (int qh = tid + kAttnThreads; qh < nq; qh += kAttnThreads)
     p.ws_ml[(head0 + qh) * p.max_pages + pg] = make_float2(ml[2 * qh], ml[2 * qh + 1]);
 
   // ---- last block to arrive for this (sequence, kv-head) combines the pages in page order
   __threadfence();
   __syncthreads();
-  int *ctr = p.counters + (size_t)b * p.n_kv + kvh;
+  int *ctr = p.counters + ((size_t)b * p.n_kv + kvh) * p.qsplit + qpart;
   if (tid == 0) s_last = (atomicAdd(ctr, 1) == n_active - 1);
   __syncthreads();
   if (!s_last) return;
   __threadfence();
   if (tid == 0) *ctr = 0;
   if (tid < H) {
-    for (int qh = 0; qh < p.qpk; ++qh) {
+    for (int qh = 0; qh < nq; ++qh) {
       const size_t hd = head0 + qh;
       float M = -INFINITY;
       for (int i = 0; i < n_active; ++i) M = fmaxf(M, __ldcg(&p.ws_ml[hd * p.max_pages + i]).x);
@@ -265,7 +272,7 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
         L += v.y * w;
         o += __ldcg(&p.ws_o[(hd * p.max_pages + i) * H + tid]) * w;
       }
-      p.out[(size_t)b * p.out_ld + ((size_t)kvh * p.qpk + qh) * H + tid] = __float2half_rn(o / L);
+      p.out[(size_t)b * p.out_ld + ((size_t)kvh * p.qpk + q_lo + qh) * H + tid] = __float2half_rn(o / L);
     }
   }
 }
@@ -351,6 +358,7 @@ extern "C" int pt_kv_append_attn(const pt_attn_args *a, void *stream) {
 
   AttnParams p{};
   p.B = a->batch; p.n_head = a->n_head; p.n_kv = a->n_kv; p.qpk = a->n_head / a->n_kv; p.H = a->head_dim;
+  p.qsplit = (p.qpk > 4 && p.qpk % 4 == 0) ? p.qpk / 4 : 1;   // four q heads per block for multi-query groups
   p.page = a->page_size; p.max_pages = a->max_pages; p.rope_mode = a->rope_mode; p.softmax_mode = a->softmax_mode;
   p.rot_half = a->rope_mode == PT_ROPE_CHATGLM2 ? a->head_dim / 4 : a->head_dim / 2;
   p.out_ld = a->out_ld > 0 ? a->out_ld : a->n_head * a->head_dim;
@@ -367,11 +375,12 @@ extern "C" int pt_kv_append_attn(const pt_attn_args *a, void *stream) {
   p.error_flag = a->error_flag;
   p.pdl = a->pdl ? 1 : 0;
 
-  const size_t smem = (size_t)2 * p.page * p.H * sizeof(__half) + (size_t)p.qpk * p.H * sizeof(__half) +
-                      (size_t)p.qpk * p.page * sizeof(float) + (size_t)p.qpk * 2 * sizeof(float);
+  const int nq = p.qpk / p.qsplit;
+  const size_t smem = (size_t)2 * p.page * p.H * sizeof(__half) + (size_t)nq * p.H * sizeof(__half) +
+                      (size_t)nq * p.page * sizeof(float) + (size_t)nq * 2 * sizeof(float);
   PT_REQUIRE(smem <= 200 * 1024, "pt_kv_append_attn: tile needs %zu bytes of shared memory", smem);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(a->max_pages, a->n_kv, a->batch);
+  cfg.gridDim = dim3(a->max_pages, a->n_kv * p.qsplit, a->batch);
   cfg.blockDim = dim3(kAttnThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = as_stream(stream);

@@ -271,7 +271,10 @@ def test_kv_cache_pipeline(cuda):
 # ------------------------------------------------------------------ fused RoPE + paged append + attention
 @pytest.mark.parametrize("B,N,G,H,L,page,mode", [(1, 4, 4, 128, 40, 16, "llama"), (2, 8, 8, 128, 150, 64, "llama"),
                                                 (2, 4, 4, 64, 70, 32, "gpt2"), (2, 8, 2, 128, 70, 64, "none_gqa"),
-                                                (2, 8, 2, 128, 70, 64, "chatglm2")])
+                                                (2, 8, 2, 128, 70, 64, "chatglm2"),
+                                                # 8 and 16 q heads per kv group: the group's heads are shared out over 2 and 4 blocks
+                                                (2, 16, 2, 128, 70, 64, "chatglm2"), (1, 32, 2, 128, 150, 64, "chatglm2"),
+                                                (2, 16, 2, 64, 40, 16, "none_gqa")])
 def test_kv_append_attn(cuda, B, N, G, H, L, page, mode):
     from poptransformer_b200 import ops
     from poptransformer_b200.llama import rope_tables
