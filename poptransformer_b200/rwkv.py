@@ -91,11 +91,32 @@ class RWKVDecoder:
         self.st_den = [torch.zeros((B, dl), dtype=torch.float32, device=dev) for _ in range(c.n_layer)]
         self.st_max = [torch.full((B, dl), -1e30, dtype=torch.float32, device=dev) for _ in range(c.n_layer)]
         self.lin_ws = ops.linear_workspace(B, max(fl, self.vocab_loc, d), 16, dev)
+        # The key / value / receptance linears of a block read different mixes of the same hidden state and are independent:
+        # on one GPU they run on three streams (fork / join by events, also inside a captured CUDA graph), each with its own
+        # split-k workspace, so three short waves share the SMs instead of running back to back.
+        self.side = [torch.cuda.Stream(device=dev) for _ in range(2)] if tp == 1 else []
+        self.side_ws = [ops.linear_workspace(B, d, 16, dev) for _ in self.side]
         torch.cuda.synchronize()
 
-    def _linear(self, x, pl, out, epilogue=ops.EPI_STORE, residual=None):
-        a = ops.linear_args(x, pl, out, epilogue=epilogue, residual=residual, workspace=self.lin_ws, error_flag=self.error_flag, pdl=self.pdl_linear)
-        ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
+    def _linear(self, x, pl, out, epilogue=ops.EPI_STORE, residual=None, side=None):
+        """side = None: on the current stream; side = i: on side stream i (between _fork and _join), with that stream's workspace."""
+        ws = self.lin_ws if side is None else self.side_ws[side]
+        a = ops.linear_args(x, pl, out, epilogue=epilogue, residual=residual, workspace=ws, error_flag=self.error_flag, pdl=self.pdl_linear)
+        if side is None:
+            ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
+        else:
+            with torch.cuda.stream(self.side[side]):
+                ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
+
+    def _fork(self):
+        main = torch.cuda.current_stream()
+        for s in self.side:
+            s.wait_stream(main)
+
+    def _join(self):
+        main = torch.cuda.current_stream()
+        for s in self.side:
+            main.wait_stream(s)
 
     def _norm(self, x, gb, out):
         ops.check(ops._lib.lib().pt_norm_ce(ops._ptr(x), ops._ptr(gb[0]), ops._ptr(gb[1]), self.batch, self.cfg.d_model, self.cfg.eps,
@@ -117,9 +138,14 @@ class RWKVDecoder:
             self._norm(self.x, L["ln1"], self.t)
             mk, mv, mr = L["a_mix"]
             ops.check(L_.pt_rwkv_mix(P(self.t), P(self.st_att[i]), P(mk), P(mv), P(mr), P(self.k), P(self.v), P(self.r), B, d, S()), "pt_rwkv_mix")
+            par = bool(self.side)
+            if par:
+                self._fork()
             self._linear(self.k, L["a_key"], self.kk)
-            self._linear(self.v, L["a_value"], self.vl)
-            self._linear(self.r, L["a_recept"], self.rl)
+            self._linear(self.v, L["a_value"], self.vl, side=0 if par else None)
+            self._linear(self.r, L["a_recept"], self.rl, side=1 if par else None)
+            if par:
+                self._join()
             ops.check(L_.pt_wkv(P(self.kk), P(self.vl), P(L["time_first"]), P(L["time_decay"]), P(self.st_num[i]), P(self.st_den[i]),
                                 P(self.st_max[i]), B, dl, P(self.wl), S()), "pt_wkv")
             ops.check(L_.pt_rwkv_act(0, P(self.rl), P(self.wl), P(self.wl), B * dl, S()), "pt_rwkv_act")
@@ -131,11 +157,15 @@ class RWKVDecoder:
             self._norm(self.x, L["ln2"], self.t)
             fk, fr = L["f_mix"]
             ops.check(L_.pt_rwkv_mix(P(self.t), P(self.st_ffn[i]), P(fk), P(fr), None, P(self.k), P(self.r), None, B, d, S()), "pt_rwkv_mix")
+            if par:
+                self._fork()
             self._linear(self.k, L["f_key"], self.fk)
             ops.check(L_.pt_rwkv_act(1, P(self.fk), None, P(self.fk2), B * fl, S()), "pt_rwkv_act")
             self._end(self.fk2, L["f_value"], self.vv)
             if self.tp == 1:
-                self._linear(self.r, L["f_recept"], self.rr)
+                self._linear(self.r, L["f_recept"], self.rr, side=0 if par else None)
+                if par:
+                    self._join()
             else:       # rwkv/ffn.py:95: all-gather of the receptance shards, read as a concatenation over the channels
                 self._linear(self.r, L["f_recept"], self.rl)
                 torch.distributed.all_gather_into_tensor(self.gather_r, self.rl, group=self.group)
