@@ -1,13 +1,16 @@
 #!/usr/bin/env python
 """Decode benchmark: Llama-2-7B architecture, INT4 (group 128) weight-only linears, fp16 KV cache,
-batch 1, context 512 -> 512+K (prompt 512, K decode steps), tensor parallel over --gpus.
+batch 1, prompt 512, K decode steps (the step that consumes the last prompt token and the K - 1 after it),
+tensor parallel over --gpus.
 
     python bench.py --gpus 1 --steps 256 --warmup 8            # this implementation (needs a B200)
-    python bench.py --impl reference --steps 2 --warmup 1      # CPU restatement of the reference path
+    python bench.py --impl reference --steps 20 --warmup 5     # CPU restatement of the reference path
 
 Prints ONE JSON line.  A "step" is one decode step (one new token per sequence).  `value` is decode
 tokens/s with weights, KV cache and ids resident in HBM; `e2e` is the same through LlamaDecoder's
-host-facing call (pinned host ids in, ids out, copies inside the timed region).
+host-facing call (pinned host ids in, ids out, copies inside the timed region).  Both arms print the same
+`metric` string; the context range a run covered is in `config.ctx`.  After the timed region the first
+generated ids of the benched state are checked against the C restatement (`ids_checked`).
 """
 import argparse
 import json
@@ -24,6 +27,11 @@ sys.path.insert(0, ROOT)
 
 LLAMA7B = dict(n_layer=32, d_model=4096, n_head=32, ffn=11008, vocab=32000)
 PROMPT, MAX_LEN, GROUP = 512, 768, 128
+TRAFFIC_RATIO = 1.012   # DRAM bytes moved / algorithmic bytes of one persistent-kernel launch, from the ncu capture of the 8-block case
+
+
+def metric_name(batch):
+    return "decode tokens/s (Llama-2-7B INT4 g128, batch %d, prompt %d)" % (batch, PROMPT)
 
 
 def peaks():
@@ -113,7 +121,7 @@ def cpu_baseline(steps, warmup, sample_layers=2, ctx=PROMPT):
     for it in range(warmup + steps):
         t0 = time.perf_counter()
         for s in orc.layers:
-            L.oracle_llama_layer_step(ctypes.byref(s), ctx + it, c_ref._p(x), c_ref._p(orc.scratch))
+            L.oracle_llama_layer_step(ctypes.byref(s), min(ctx + it, MAX_LEN - 1), c_ref._p(x), c_ref._p(orc.scratch))
         t1 = time.perf_counter()
         L.oracle_llama_head(c_ref._p(x), c_ref._p(orc.norm), c_ref._p(orc.head), 1, d, v, cfg.eps, c_ref._p(orc.h), c_ref._p(orc.lg),
                             c_ref._p(orc.nxt))
@@ -132,17 +140,52 @@ def cpu_baseline(steps, warmup, sample_layers=2, ctx=PROMPT):
 
 
 def run_reference(args):
+    """The CPU arm: the C restatement of the reference's decode step on all host cores, the --steps / --warmup it is given,
+    every step a bounded sample of the workload (2 of the 32 blocks + the head, block time scaled)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
-    cb = cpu_baseline(steps, warmup)
-    line = {"impl": "reference", "metric": "decode tokens/s (Llama-2-7B INT4 g128, batch 1, ctx 512->768)", "value": cb["value"],
+    steps, warmup = max(1, min(args.steps, MAX_LEN - PROMPT)), max(0, args.warmup)
+    cb = cpu_baseline(steps, warmup, ctx=PROMPT - 1)
+    line = {"impl": "reference", "metric": metric_name(1), "value": cb["value"],
             "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": cb["ms_per_token"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate",
-            "data": "synthetic", "config": {"workload": "llama2-7b-int4-g128 decode b1 prompt512", "parallelism": "host cores (OpenMP)"},
+            "data": "synthetic", "config": {"workload": "llama2-7b-int4-g128 decode b1 prompt512", "parallelism": "host cores (OpenMP)",
+                                            "ctx": [PROMPT - 1 + warmup, PROMPT - 1 + warmup + steps]},
             "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
+
+
+def check_ids(dec, sd_host, ids_host, out_host, n):
+    """Checks the first `n` ids the benched state generated (`out_host`, from the end-to-end leg) against the C restatement
+    of the reference step, teacher-forced along the GPU's stream: at every checked position the GPU's id must be the
+    restatement's arg-max, or a logit within the fp16 logit tolerance (2e-2) of its best.  The restatement starts from the
+    same checkpoint and the same cached prompt (the pages below position 511, which decode never rewrites)."""
+    import torch
+    from oracle import c_ref, llama_np
+    c = dec.cfg
+    ocfg = llama_np.LlamaConfig(n_layer=c.n_layer, d_model=c.d_model, n_head=c.n_head, ffn=c.ffn, vocab=c.vocab, max_len=c.max_len, group=c.int4_group)
+    orc = c_ref.LlamaOracleC(ocfg, sd_host, dec.batch)
+    before = torch.full((1,), PROMPT - 2, dtype=torch.int32, device=dec.device)       # newest cached position
+    for li, kc in enumerate(dec.caches):
+        dense = kc.export(before, c.max_len).cpu().numpy()                             # [2, rows, heads, max_len, H], newest first
+        orc.set_cache(li, dense[0], dense[1])
+    got = out_host.numpy()
+    exact = ties = 0
+    for i in range(n):
+        step = PROMPT - 1 + i
+        logits, best = orc.logits(got[:, step], step)
+        for b in range(dec.batch):
+            tok = int(got[b, step + 1])
+            lg = logits[b].astype(np.float32)
+            if tok == int(best[b]):
+                exact += 1
+            elif lg.max() - lg[tok] <= 2e-2:
+                ties += 1
+            else:
+                raise SystemExit(f"id check failed: position {step + 1} row {b}: GPU id {tok} is {lg.max() - lg[tok]:.4f} below the "
+                                 f"restatement's best id {int(best[b])}")
+    return {"ids_checked": n * dec.batch, "ids_exact": exact, "ids_within_logit_tolerance": ties}
 
 
 # ------------------------------------------------------------------------------------------ this implementation
@@ -171,10 +214,12 @@ def run_b200(args):
     sd = synth.llama_state_dict(**dims, seed=0, device=dev, int4_group=GROUP)
     dec = llama.LlamaDecoder(cfg, sd, batch, device=dev, tp_rank=rank, tp_size=world, persistent=False if args.per_op else None,
                              keep_logits=False)
+    sd_host = {k: v.cpu().numpy() for k, v in sd.items()} if (world == 1 and args.check_ids > 0) else None
     del sd
     torch.cuda.empty_cache()
 
-    # state as it is after the 512-token prompt: ids hold the prompt, caches hold 512 tokens
+    # state as it is before the last prompt token is consumed: ids hold the 512-token prompt, the caches hold its first 511
+    # tokens (random pages), step = 511; the first timed step produces the id of position 512
     ids_host = synth.prompt_ids(batch, PROMPT, MAX_LEN, cfg.vocab, dec.pad_id, seed=0).pin_memory()
     gen = torch.Generator(device=dev).manual_seed(1)
     for kc in dec.caches:
@@ -182,7 +227,7 @@ def run_b200(args):
 
     def set_state():
         dec.ids.copy_(ids_host, non_blocking=True)
-        dec.step_t.fill_(PROMPT)
+        dec.step_t.fill_(PROMPT - 1)
 
     n0 = ops.launch_count()
     dec.capture()
@@ -226,7 +271,7 @@ def run_b200(args):
         barrier()
         t0 = time.perf_counter()
         dec.ids.copy_(ids_host, non_blocking=True)
-        dec.step_t.fill_(PROMPT)
+        dec.step_t.fill_(PROMPT - 1)
         for _ in range(K):
             dec.step()
         out_host.copy_(dec.ids, non_blocking=True)
@@ -240,14 +285,15 @@ def run_b200(args):
         e2e_s = float(t.item())
 
     peak, peak_src = peaks()
-    ctx_mean = PROMPT + (K - 1) / 2.0
+    # step s reads the s cached tokens of every sequence and writes one: s + 1 tokens' worth of KV, s = 511 .. 510 + K
+    ctx_mean = PROMPT - 1 + (K - 1) / 2.0
     step_bytes = dec.weight_bytes_total() + batch * dec.kv_bytes_per_token_total() * (ctx_mean + 1)
     if dec.persistent:
         # the dominant kernel IS the step: one persistent launch per token, timed by the CUDA events of the timed region above
-        # traffic: dram__bytes_read + dram__bytes_write of one launch, captured with ncu on the 8-block case (1.012 x its
-        # algorithmic bytes, profiles/llama_step_kernel_llama7b_8layers.md) and scaled to this launch by the bytes it processes
+        # traffic: dram__bytes_read + dram__bytes_write of one launch, captured with ncu on the 8-block case (TRAFFIC_RATIO x its
+        # algorithmic bytes) and scaled to this launch by the bytes it processes
         roof = {"bound": "hbm", "achieved": step_bytes / (ms / K * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                "traffic": (1.012 * step_bytes) if world == 1 else None,
+                "traffic": (TRAFFIC_RATIO * step_bytes) if world == 1 else None,
                 "kernel": "llama_step_kernel (persistent, 1 launch per token)", "peak_source": peak_src, "launch_us": ms / K * 1e3,
                 "bytes_per_launch": step_bytes}
     else:
@@ -284,11 +330,11 @@ def run_b200(args):
         return
     ms_step = ms / K
     line = {
-        "metric": "decode tokens/s (Llama-2-7B INT4 g128, batch %d, ctx 512->%d)" % (batch, PROMPT + K),
+        "metric": metric_name(batch),
         "value": batch * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"llama2-7b-int4-g128 decode b{batch} prompt512", "parallelism": f"tp{world}",
+        "config": {"workload": f"llama2-7b-int4-g128 decode b{batch} prompt512", "parallelism": f"tp{world}", "ctx": [PROMPT - 1, PROMPT - 1 + K],
                    "l2": "inputs_larger_than_L2 (3.6 GB of weights streamed per step)", "cuda_graph": True, "persistent_kernel": bool(dec.persistent)},
         "clocks": clocks,
         "e2e": {"value": batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": ids_host.numel() * 4 / K,
@@ -303,7 +349,9 @@ def run_b200(args):
         line["profiling_only"] = f"first {args.layers} transformer blocks only; not a benchmark result"
         line["config"]["workload"] += f" (truncated to {args.layers} layers)"
     if world == 1 and not args.no_cpu and args.layers <= 0:
-        line["cpu_baseline"] = cpu_baseline(steps=3, warmup=1)
+        line["cpu_baseline"] = cpu_baseline(steps=3, warmup=1, ctx=PROMPT - 1)
+    if world == 1 and args.check_ids > 0:
+        line.update(check_ids(dec, sd_host, ids_host, out_host, min(args.check_ids, K)))
     print(json.dumps(line))
     shutdown()
 
@@ -458,6 +506,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--check-ids", type=int, default=8, help="after the timed region, check this many generated ids per sequence of the "
+                    "benched state against the C restatement on the host (one GPU, full model only; 0 = skip)")
     ap.add_argument("--per-op", action="store_true", help="use the per-op kernels instead of the persistent whole-step kernel")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only the first N transformer blocks, so that a profiler capture "
                     "stays small; the line is then marked profiling_only and is not a benchmark result")

@@ -186,6 +186,9 @@ typedef struct pt_attn_args {
   size_t workspace_bytes;
   int32_t *error_flag;               /* device int, set non-zero if a bounded wait gave up     */
   int pdl;                           /* 1: programmatic dependent launch (see pt_linear_args.pdl) */
+  int max_len;                       /* positions available: rows of rope_sin / rope_cos and of the id container; 0 = page_size *
+                                        max_pages.  A launch that finds *step_dev outside [0, max_len) sets error_flag to 12 and
+                                        does nothing else                                                                  */
 } pt_attn_args;
 
 size_t pt_attn_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);
@@ -241,9 +244,10 @@ typedef struct pt_llama_step_args {
   void *logits;                      /* optional fp16 [batch, vocab]                                                */
   void *workspace;                   /* pt_llama_step_workspace_bytes, zeroed once                                  */
   size_t workspace_bytes;
-  int32_t *error_flag;               /* set non-zero if a bounded wait gave up                                      */
-  uint64_t *trace;                   /* optional [n_sm, n_layer, 32] global-timer stamps (ns) of each phase boundary */
-  int debug;                         /* profiling aid; bit 0: consume the weight tiles without doing the tile math  */
+  int32_t *error_flag;               /* set non-zero if a bounded wait gave up (or, 12, if *step_dev is outside [0, max_len)) */
+  uint64_t *trace;                   /* diagnostics, not a stable interface: optional [n_sm, n_layer, 32] global-timer stamps (ns) */
+  int debug;                         /* diagnostics, not a stable interface: bit 0 = consume the weight tiles without the tile math;
+                                        bits 16..31 = suspend-time hint (ns) of the shared-memory barrier waits (0 = default) */
   /* Tensor parallelism inside the kernel (tp_size > 1; one process and one launch per GPU, all ranks launch every step).
    * The reference's TP layers (layers/linear.py 'start' / 'end' strategies, layers/lm_head.py:75-116) map to: d_model = the
    * full hidden size, n_head = this rank's heads, ffn = width of this rank's k window of down_proj (a multiple of 128
@@ -255,6 +259,15 @@ typedef struct pt_llama_step_args {
   int tp_size, tp_rank, ffn_offset, ffn_valid, vocab_offset;
   int emb_rows;                      /* tp_size > 1: rows of the embedding table (the full vocabulary; the table is replicated) */
   void *tp_buffers[8];
+  /* Early stop (HFDecBaseModel.early_stop, models/base_model.py:348-352).  Optional device int, zeroed by the caller before a
+   * generation: the step that finds every stop_mask entry already set (the mask as it was before that step's own update, like
+   * the reference's keep_going condition) sets it after finishing, and every later launch returns at once without touching
+   * ids, step or the caches, so the host may poll it every few steps and still read the reference's final state. */
+  int32_t *done_flag;
+  /* Trip limit of the kernel's polling loops on global memory (one trip = one L2 / NVLink round trip); 0 = default (about two
+   * seconds).  A wait that runs out sets error_flag, and the launch still terminates.  Applies to the device it is set on until
+   * changed. */
+  int wait_limit;
 } pt_llama_step_args;
 
 size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);
@@ -312,6 +325,12 @@ int pt_embedding(const void *table, const int32_t *ids, int ids_stride, const in
  * ids[b, step'] takes next_ids[b] where it holds pad_id; stop_mask[b] |= (id == eos_id). */
 int pt_step_containers(int32_t *ids, int batch, int max_len, int32_t *step_dev, const int32_t *next_ids,
                        int pad_id, int eos_id, int32_t *stop_mask, void *stream);
+/* The same with the reference's early stop (models/base_model.py:348-352): when *done_flag is set the call changes nothing;
+ * otherwise, if every stop_mask entry was already set before this update, it sets *done_flag after the update (the reference
+ * evaluates keep_going on the incoming mask, so the loop body runs once more after the last sequence produced its eos id).
+ * done_flag: device int, zeroed by the caller before a generation. */
+int pt_step_containers_early_stop(int32_t *ids, int batch, int max_len, int32_t *step_dev, const int32_t *next_ids,
+                                  int pad_id, int eos_id, int32_t *stop_mask, int32_t *done_flag, void *stream);
 /* Elementwise fp16: out = fp16(a + b) (ops.add). */
 int pt_add_f16(const void *a, const void *b, int64_t n, void *out, void *stream);
 

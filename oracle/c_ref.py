@@ -95,8 +95,20 @@ class LlamaOracleC:
         self.lg = np.empty((batch, c.vocab), np.float16)
         self.nxt = np.empty(batch, np.int32)
 
+    def _by_address(self, addr):
+        return [a for a in self.keep if a.ctypes.data == addr][0]
+
     def kcache(self, layer):
-        return self.keep[[i for i, a in enumerate(self.keep) if a.ctypes.data == self.layers[layer].kcache][0]]
+        return self._by_address(self.layers[layer].kcache)
+
+    def vcache(self, layer):
+        return self._by_address(self.layers[layer].vcache)
+
+    def set_cache(self, layer, k, v):
+        """Loads a cache state: k, v [batch, n_head, max_len, head_dim] in the reference op's layout (newest token at index 0,
+        zeros beyond the tokens cached so far), e.g. a paged cache exported with pt_kv_export."""
+        self.kcache(layer)[...] = k
+        self.vcache(layer)[...] = v
 
     def logits(self, ids_col, step):
         L = lib()

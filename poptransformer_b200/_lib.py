@@ -34,7 +34,7 @@ class AttnArgs(ctypes.Structure):
         ("score_scale", c_float),
         ("step_dev", c_void_p), ("qkv", c_void_p), ("rope_sin", c_void_p), ("rope_cos", c_void_p),
         ("pool", c_void_p), ("page_table", c_void_p), ("out", c_void_p), ("out_ld", c_int),
-        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("pdl", c_int),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("pdl", c_int), ("max_len", c_int),
     ]
 
 
@@ -48,7 +48,8 @@ class LlamaStepArgs(ctypes.Structure):
                [(n, c_void_p) for n in ("layers", "norm", "head", "emb", "rope_sin", "rope_cos", "ids", "step_dev", "stop_mask", "next_ids",
                                         "page_table", "x", "qkv", "attn", "act", "logits", "workspace")] + \
                [("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("trace", c_void_p), ("debug", c_int)] + \
-               [(n, c_int) for n in ("tp_size", "tp_rank", "ffn_offset", "ffn_valid", "vocab_offset", "emb_rows")] + [("tp_buffers", c_void_p * 8)]
+               [(n, c_int) for n in ("tp_size", "tp_rank", "ffn_offset", "ffn_valid", "vocab_offset", "emb_rows")] + [("tp_buffers", c_void_p * 8)] + \
+               [("done_flag", c_void_p), ("wait_limit", c_int)]
 
 
 # name -> (restype, argtypes); mirrors include/pt_b200.h one to one
@@ -89,6 +90,7 @@ SIGNATURES = {
     "pt_wkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "pt_embedding": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_step_containers": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "pt_step_containers_early_stop": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_add_f16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
 }
 

@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from . import ops
+from .loop import DecodeLoop
 from .tp import multi_query_head_index, rows, vocab_rows
 
 
@@ -43,9 +44,9 @@ def chatglm2_rope_tables(max_len, head_dim, device):
     return torch.from_numpy(sin).to(device), torch.from_numpy(cos).to(device)
 
 
-class ChatGLM2Decoder:
+class ChatGLM2Decoder(DecodeLoop):
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None,
-                 pdl_linear=None, pdl_attn=None):
+                 pdl_linear=None, pdl_attn=None, early_stop=False):
         c = cfg
         self.pdl_linear, self.pdl_attn = PDL_DEFAULT[0] if pdl_linear is None else int(pdl_linear), PDL_DEFAULT[1] if pdl_attn is None else int(pdl_attn)
         self.tp, self.rank, self.group = tp_size, tp_rank, group
@@ -57,6 +58,7 @@ class ChatGLM2Decoder:
         self.cfg, self.batch, self.device = cfg, batch, device
         self.pad_id = c.vocab - 1 if pad_id is None else pad_id
         self.eos_id = eos_id
+        self._init_loop(device, early_stop)
         dev, fp8 = device, c.precision == "fp8"
         t = lambda k: state_dict[k].to(dev)
 
@@ -151,7 +153,7 @@ class ChatGLM2Decoder:
                                  ops._stream()), "topk")
         else:
             ops.lm_head_tp_merge(self)
-        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
+        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask, done_flag=self._loop_done_flag())
 
     def reset(self, input_ids):
         self.ids.copy_(torch.as_tensor(input_ids, dtype=torch.int32).to(self.device))
@@ -161,12 +163,3 @@ class ChatGLM2Decoder:
     def step(self):
         self.enqueue_step()
 
-    def run(self, input_ids, max_loop=None):
-        """Session.run analogue (poptransformer/sessions.py:47-49): returns the anchors {'Loop:0': ids, 'Loop:1': step}."""
-        self.reset(input_ids)
-        for _ in range(self.cfg.max_len if max_loop is None else max_loop):
-            self.step()
-        torch.cuda.synchronize()
-        if int(self.error_flag.item()) != 0:
-            raise ops.PtError("a bounded device-side wait gave up")
-        return {"Loop:0": self.ids.cpu().numpy(), "Loop:1": self.step_t.cpu().numpy()}

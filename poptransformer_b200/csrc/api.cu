@@ -17,6 +17,18 @@ int set_error(int code, const char *fmt, ...) {
   return code;
 }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+int sm_count() {
+  static int per_device[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (per_device[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    per_device[dev] = n;
+  }
+  return per_device[dev];
+}
 }  // namespace pt
 
 extern "C" const char *pt_last_error(void) { return pt::g_err; }

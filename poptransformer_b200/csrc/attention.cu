@@ -15,7 +15,7 @@
 namespace pt {
 
 struct AttnParams {
-  int B, n_head, n_kv, qpk, qsplit, H, page, max_pages, rope_mode, softmax_mode, rot_half, out_ld, pdl;
+  int B, n_head, n_kv, qpk, qsplit, H, page, max_pages, max_len, rope_mode, softmax_mode, rot_half, out_ld, pdl;
   __half scale_h;
   int use_scale;
   const int *step;
@@ -111,6 +111,10 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
   const int step = *p.step;
+  if (step < 0 || step >= p.max_len) {  // no page / no RoPE row for this position: report it and leave the counters untouched
+    if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 12);
+    return;
+  }
   const int n_active = step / PAGE + 1;
   if (pg >= n_active) return;
   const int n_valid = min(PAGE, step + 1 - pg * PAGE);
@@ -374,6 +378,9 @@ extern "C" int pt_kv_append_attn(const pt_attn_args *a, void *stream) {
   p.ws_o = (float *)ws;
   p.error_flag = a->error_flag;
   p.pdl = a->pdl ? 1 : 0;
+  PT_REQUIRE(a->max_len >= 0 && a->max_len <= a->page_size * a->max_pages, "pt_kv_append_attn: max_len=%d exceeds the %d positions of the page table",
+             a->max_len, a->page_size * a->max_pages);
+  p.max_len = a->max_len > 0 ? a->max_len : a->page_size * a->max_pages;
 
   const int nq = p.qpk / p.qsplit;
   const size_t smem = (size_t)2 * p.page * p.H * sizeof(__half) + (size_t)nq * p.H * sizeof(__half) +
@@ -409,7 +416,7 @@ extern "C" int pt_kv_export(const void *pool, const int32_t *page_table, const i
   PT_REQUIRE(pool && page_table && step_dev && dense_out, "pt_kv_export: null pointer argument");
   PT_REQUIRE(head_dim % 8 == 0 && max_len <= page_size * max_pages, "pt_kv_export: max_len=%d exceeds page capacity %d", max_len,
              page_size * max_pages);
-  kv_export_kernel<<<148 * 4, 256, 0, as_stream(stream)>>>((const __half *)pool, page_table, step_dev, batch, n_kv, head_dim, page_size,
+  kv_export_kernel<<<sm_count() * 4, 256, 0, as_stream(stream)>>>((const __half *)pool, page_table, step_dev, batch, n_kv, head_dim, page_size,
                                                           max_pages, max_len, (__half *)dense_out);
   PT_LAUNCH_CHECK("pt_kv_export");
   return PT_OK;

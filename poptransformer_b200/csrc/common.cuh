@@ -12,6 +12,8 @@ namespace pt {
 // Records a thread-local message for pt_last_error() and returns `code`.
 int set_error(int code, const char *fmt, ...);
 void count_launch(int n = 1);
+// Streaming multiprocessors of the current device (cached per device; 148 on B200).
+int sm_count();
 
 #define PT_REQUIRE(cond, ...)                                \
   do {                                                       \

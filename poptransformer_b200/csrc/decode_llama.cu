@@ -9,15 +9,18 @@
 // latencies (several microseconds each, five kernels per layer) cost more than the data movement.  Here
 //   * warp 16 is a producer: it walks this SM's share of every weight matrix of the whole step, in order, and
 //     keeps a ring of 33 KB shared-memory stages full with 1-D bulk async copies (TMA engine, one mbarrier
-//     per stage).  Weights do not depend on activations, so the producer runs ahead across the grid-wide
-//     barriers and HBM stays busy while the consumers wait for each other;
+//     per stage).  Weights do not depend on activations, so the producer runs ahead across the phase
+//     boundaries and HBM stays busy while the consumers wait for each other's activations;
 //   * warps 0-15 are consumers: consumer w takes tiles w and 16 + w of every stage (a stage = 32 tiles of the packed
 //     layout of linear.cu, re-ordered so that each warp walks a contiguous run of [row tile][chunk] tiles).  INT4 tiles are
 //     multiplied on the integer tensor-core path: the nibbles of a packed word become two u8 operands with one AND each,
 //     the activations are 16-bit block fixed point split into two s8 columns, and the s32 sums are scaled once per
 //     128-k group; sums of a row tile that several warps share meet in shared memory in warp order (deterministic);
 //   * K/V pages travel through the same ring; the attention arithmetic is that of attention.cu;
-//   * phases are separated by a grid barrier (one atomic per block, bounded spin, error flag on time-out).
+//   * there is no grid-wide barrier between phases: activations travel through global memory as 32-bit tagged words
+//     (fp16 value + 16-bit phase tag), every SM publishes one progress word per phase, one warp per SM polls the
+//     progress words and the data words validate themselves when they are loaded.  Every wait is bounded and raises the
+//     error flag when it runs out.  One grid barrier remains, before the arg-max merge at the end of the step.
 // Every SM owns whole row tiles: rows [s * n_rt / G, (s + 1) * n_rt / G).
 #include <algorithm>
 
@@ -40,7 +43,6 @@ constexpr int V_OFFSET = 16896;                   // a K page and a V page (2 x 
 constexpr int MAXU = NCT / 64;                    // attention units handled per SM per pass (64 threads fetch q / k / v of one)
 constexpr int BMAX = 2;
 constexpr int H = 128, PAGE = 64;
-constexpr int SPIN_LIMIT = 1 << 22;
 static_assert(NCT % 64 == 0 || NCT % 32 == 0, "consumer threads come in whole warps");
 
 struct Params {
@@ -57,7 +59,7 @@ struct Params {
   const pt_llama_layer *layers;
   const __half *norm, *emb, *sin_t, *cos_t;
   const unsigned char *head;
-  int *ids, *step, *stop_mask, *next_ids;
+  int *ids, *step, *stop_mask, *next_ids, *done_flag;
   const int *page_table;
   uint32_t *xw, *qkvw, *attnw, *actw;  // activations as tagged words; xw holds two copies [2][B][d] when tp > 1
   __half *logits;
@@ -67,6 +69,9 @@ struct Params {
   int *cand_idx;
   unsigned *barrier;  // [0], [1]: counters used by alternate launches; [2]: which one the next launch uses; [3]: launch count
   uint32_t *flag_sm;  // [256] sequence number of the last linear phase (or embedding) that SM s has finished writing
+  uint2 *flag_ssq;    // [BMAX][256] {sum of squares of the x rows SM s wrote for batch row b (fp32 bits), sequence number}: written by the
+                      // phases that produce x (embedding, o_proj, down_proj) just before flag_sm, so that whoever waits for x gets the
+                      // RMSNorm statistics with the very loads that tell it x is complete
   uint32_t *flag_head;  // [B, n_head] sequence number of the last attention output written for that head
   int *error_flag;
   unsigned long long *trace;  // optional: [grid][n_layer][32] global-timer stamps of the phase boundaries
@@ -88,6 +93,11 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 // failure, so that after an error every loop of the kernel still runs its normal trip count (all named barriers stay
 // matched) but finishes quickly.
 __constant__ uint32_t c_wait_hint = 2000u;  // suspend-time hint (ns) of the mbarrier waits
+// Trip limit of every polling loop on global memory (progress words, tagged words, arrival counters); one trip is one L2 or
+// NVLink round trip, so the default gives a waiter about two seconds before it gives up and raises the error flag.
+constexpr int kDefaultPollLimit = 1 << 21;
+__constant__ int c_poll_limit = kDefaultPollLimit;
+#define POLL_LIMIT c_poll_limit
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int *abort_flag) {
   const uint32_t hint = c_wait_hint;
   for (int it = 0; it < (1 << 18); ++it) {
@@ -115,7 +125,6 @@ __device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_c
 // phases.  Tags grow with every phase and launch (period 32768 phases), every word is rewritten at least once per launch,
 // so a stale word never carries the expected tag.  Re-use of a buffer is safe without barriers because the writer of the
 // next value has (through the chain of phases in between) waited for data that every reader produced after reading.
-constexpr int POLL_LIMIT = 1 << 21;
 __device__ __forceinline__ uint4 ld_words(const uint32_t *p) {
   uint4 v;
   asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -136,7 +145,7 @@ __device__ __forceinline__ void st_tagged(uint2 *p, uint32_t bits, uint32_t tag)
   asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(bits), "r"(tag) : "memory");
 }
 __device__ __forceinline__ bool poll_tagged(const uint2 *p, uint32_t tag, uint32_t &bits, const volatile int *abort_flag) {
-  for (int it = 0; it < (1 << 21); ++it) {
+  for (int it = 0; it < POLL_LIMIT; ++it) {
     const uint2 v = ld_tagged(p);
     if (v.y == tag) { bits = v.x; return true; }
     if ((it & 63) == 63 && *abort_flag) break;
@@ -200,6 +209,43 @@ __device__ __forceinline__ bool wait_flags(const uint32_t *flags, int rows, int 
   }
   return false;
 }
+// The same wait on the entries {partial sum of squares, sequence number} that the producers of x publish (one entry per SM and
+// batch row): when every entry carries `want`, the loads that proved it also hold the RMSNorm statistics.  Lane l sums entries
+// l, l + 32, ... in that order, then the lanes meet in a fixed shuffle tree: the same bits on every SM and in every run.
+// rb[b] <- 1 / sqrt(sum / K + eps) rounded to fp16 (layers/rms_layer_norm.py:26-36).
+__device__ __forceinline__ bool wait_flags_ssq(const uint2 *flags, int B, int cols, uint32_t want, int K, float eps, float *rb,
+                                               const volatile int *abort_flag) {
+  const int lane = threadIdx.x & 31;
+  for (int it = 0; it < POLL_LIMIT; ++it) {
+    bool ok = true;
+    float part[BMAX];
+#pragma unroll
+    for (int b = 0; b < BMAX; ++b) {
+      part[b] = 0.f;
+      if (b < B) {
+        uint2 e[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = (lane + 32 * j < cols) ? ld_tagged(flags + b * 256 + lane + 32 * j) : make_uint2(0u, want);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ok &= e[j].y == want;
+          part[b] += __uint_as_float(e[j].x);
+        }
+      }
+    }
+    if (__all_sync(0xffffffffu, ok)) {
+#pragma unroll
+      for (int b = 0; b < BMAX; ++b)
+        if (b < B) {
+          const float ss = warp_sum(part[b]);
+          if (lane == 0) rb[b] = __half2float(__float2half_rn(1.0f / sqrtf(ss / (float)K + eps)));
+        }
+      return true;
+    }
+    if ((it & 63) == 63 && *abort_flag) break;
+  }
+  return false;
+}
 // Tensor parallelism: one arrival counter per source rank (row stride 256 words), incremented once by every SM of that rank when
 // its partial sums of a row-parallel linear are pushed.  Lane r looks at rank r's counter: one round trip per poll.
 __device__ __forceinline__ bool wait_counters(const uint32_t *counters, int rows, uint32_t want, const volatile int *abort_flag) {
@@ -225,6 +271,18 @@ struct PhaseInfo {
   size_t push_slot; // word offset of this rank's slot for this linear in a rank's partial-sum buffer
 };
 
+// How one matrix is shared out: to this SM (row tiles [r0, r0 + m)) and, inside the SM, to the consumer warps (warp w owns the
+// contiguous tile range [start(w), start(w) + len(w)) in [row tile][chunk] order, ranges differ by at most one tile).  Worked
+// out once per launch, so that no phase starts with divisions.
+constexpr int GEO_RT = 16;  // local row tiles with a precomputed owner range (more: computed on the fly)
+struct Geo {
+  int r0, m, base, rem;
+  short first_rt[NCW];     // local row tile in which warp w's range starts ...
+  short ch0[NCW];          // ... and the chunk inside it
+  unsigned char w_lo[GEO_RT], w_hi[GEO_RT];  // first / last warp holding a part of local row tile r
+};
+enum { MAT_QKV = 0, MAT_O = 1, MAT_GU = 2, MAT_DOWN = 3, MAT_HEAD = 4 };
+
 struct Shared {           // fixed-size part, placed after the ring / activations (128-byte aligned)
   alignas(16) float red[NCW][2][32][2];  // per warp: partial sums of the first / last row tile of its tile range
   int4 corr[96][BMAX];    // [chunk][batch]: C-fragment initialiser {-8 sum(t1), -8 sum(t2)} x 2 rows, up to 96 chunks of 128 k
@@ -235,13 +293,15 @@ struct Shared {           // fixed-size part, placed after the ring / activation
   float pw[NCW][PAGE];    // softmax weights of the page, one private copy per warp
   float ml[NGRP][2];
   int phys[MAXU];         // physical page of each unit of the attention pass (for the append of the new token)
-  float stat[BMAX];
+  float stat[BMAX];       // RMSNorm factor of each batch row for the staging in progress
+  float wssq[NCW][BMAX];  // per warp: sum of squares of the x values its epilogues wrote
   float wred[32];
   float bestv[32][BMAX];
   int besti[32][BMAX];
   volatile int abort;
   uint64_t full[16], empty[16];
   PhaseInfo phase;
+  Geo geo[5];             // this SM's share of q|k|v, o, gate|up, down and the LM head (filled once per launch)
 };
 
 struct Ctx {
@@ -274,7 +334,7 @@ __device__ __forceinline__ void grid_sync(Ctx &c) {
     __threadfence();
     atomicAdd(c.bar_ctr, 1u);
     bool ok = false;
-    for (int it = 0; it < SPIN_LIMIT; ++it) {
+    for (int it = 0, lim = 2 * POLL_LIMIT; it < lim; ++it) {
       unsigned v;
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(c.bar_ctr) : "memory");
       if (v >= c.bar_target) { ok = true; break; }
@@ -282,7 +342,7 @@ __device__ __forceinline__ void grid_sync(Ctx &c) {
     }
     if (!ok) {
       c.sh->abort = 1;
-      if (c.p.error_flag) atomicExch(c.p.error_flag, 3);
+      if (c.p.error_flag) atomicCAS(c.p.error_flag, 0, 3);
     }
   }
   consumer_sync();
@@ -367,6 +427,7 @@ struct StageSrc {
                             // cols == 0: one arrival counter per row instead, `want` arrivals
   int flag_rows, flag_cols;
   uint32_t want;
+  const uint2 *ssq_flags;   // non-null: wait on the {sum of squares, sequence} entries of the x producers instead (rows = batch)
   // tensor parallelism: the input is x + the sum over ranks of the partial sums of a row-parallel linear
   const uint32_t *parts;    // [n_parts][B][K] tagged words (nullptr: no partial sums)
   int n_parts;
@@ -386,6 +447,12 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
   if (!TP) gm = load_gamma(gamma, K);  // requested before the wait, used after it
   unsigned long long *ts = (c.tr && trace_slot && tid == 0) ? c.tr + trace_slot : nullptr;
   if (ts) ts[0] = gtime();
+#ifdef PT_MK_TRACE_WAITS
+  long long sq[6];
+  auto sclk = []() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)); return t; };
+  sq[0] = sclk();
+  sq[1] = sq[2] = sq[3] = sq[4] = sq[0];
+#endif
   // First attempt at this thread's words of batch row 0 right away: an SM that arrives after all producers are done then
   // has its data one round trip earlier.  Words that are not there yet are fetched again after the wait.
   uint4 v[3];
@@ -404,13 +471,17 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
       }
     }
   }
-  if (tid < 32 && !(src.flag_cols == 0 ? wait_counters(src.flags, src.flag_rows, src.want, &c.sh->abort)
-                                       : wait_flags(src.flags, src.flag_rows, src.flag_cols, src.want, &c.sh->abort))) {
+  if (tid < 32 && !(src.ssq_flags ? wait_flags_ssq(src.ssq_flags, p.B, src.flag_cols, src.want, K, p.eps, c.sh->stat, &c.sh->abort)
+                    : src.flag_cols == 0 ? wait_counters(src.flags, src.flag_rows, src.want, &c.sh->abort)
+                                         : wait_flags(src.flags, src.flag_rows, src.flag_cols, src.want, &c.sh->abort))) {
     c.sh->abort = 1;
-    if (p.error_flag) atomicExch(p.error_flag, 10);
+    if (p.error_flag) atomicCAS(p.error_flag, 0, 10);
   }
   consumer_sync();
   if (ts) ts[1] = gtime();
+#ifdef PT_MK_TRACE_WAITS
+  sq[1] = sclk();
+#endif
   for (int b = 0; b < p.B; ++b) {
     bool got = true;
 #pragma unroll
@@ -431,12 +502,17 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
     }
     if (!got) {
       c.sh->abort = 1;
-      if (p.error_flag) atomicExch(p.error_flag, 7);
+      if (p.error_flag) atomicCAS(p.error_flag, 0, 7);
     }
     if (ts && b == 0) ts[2] = gtime();
+#ifdef PT_MK_TRACE_WAITS
+    if (b == 0) asm volatile("{\n\t.reg .u32 z;\n\tadd.u32 z, %1, %2;\n\tand.b32 z, z, 0;\n\tmov.u64 %0, %%clock64;\n\t}" : "=l"(sq[2]) : "r"(v[0].x), "r"(v[0].w));
+#endif
     __half rb = __half(0);
     if (TP) gm = load_gamma(gamma, K);  // tp > 1: requested only now (registers), its latency hides behind the reduction below
-    if (gamma) {
+    if (gamma && src.ssq_flags) {
+      rb = __float2half_rn(c.sh->stat[b]);   // from the producers' statistics, written by warp 0 before the barrier above
+    } else if (gamma) {
       float ss = 0.f;
 #pragma unroll
       for (int q = 0; q < 3; ++q) {
@@ -450,6 +526,9 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
       ss = consumer_sum(c, ss);
       rb = __float2half_rn(1.0f / sqrtf(ss / (float)K + p.eps));
     }
+#ifdef PT_MK_TRACE_WAITS
+    if (b == 0) asm volatile("{\n\t.reg .u32 z;\n\tadd.u32 z, %1, %1;\n\tand.b32 z, z, 0;\n\tmov.u64 %0, %%clock64;\n\t}" : "=l"(sq[3]) : "r"((uint32_t)__half_as_ushort(rb)));
+#endif
 #pragma unroll
     for (int q = 0; q < 3; ++q) {
       if (q * NCT >= units) break;  // uniform: nothing left for any thread
@@ -466,10 +545,11 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
         const uint32_t *hw = reinterpret_cast<const uint32_t *>(&v[q]);
         __half2 mx = __hmax2(__hmax2(u32_as_h2(hw[0] & 0x7FFF7FFFu), u32_as_h2(hw[1] & 0x7FFF7FFFu)),
                              __hmax2(u32_as_h2(hw[2] & 0x7FFF7FFFu), u32_as_h2(hw[3] & 0x7FFF7FFFu)));
-#pragma unroll
-        for (int o = 1; o < 16; o <<= 1) mx = __hmax2(mx, u32_as_h2(__shfl_xor_sync(0xffffffffu, h2_as_u32(mx), o)));
-        const float amax = fmaxf(__low2float(mx), __high2float(mx));
-        const float inv = amax > 0.f ? 32000.0f / amax : 0.f;
+        // non-negative fp16 bit patterns order like integers: one integer max-reduction over the half-warp
+        const unsigned half_mask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
+        const uint32_t mbits = __reduce_max_sync(half_mask, max(h2_as_u32(mx) & 0xFFFFu, h2_as_u32(mx) >> 16));
+        const float amax = __half2float(__ushort_as_half((unsigned short)mbits));
+        const float inv = amax > 0.f ? __fdividef(32000.0f, amax) : 0.f;
         // U = T + 128 as 16-bit halves of four registers: t1 = high byte of U, t2 = low byte of U xor 0x80
         uint32_t U[4];
 #pragma unroll
@@ -483,8 +563,7 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
         const uint32_t t1a = __byte_perm(U[0], U[2], 0x7351), t1b = __byte_perm(U[1], U[3], 0x7351);
         const uint32_t t2a = __byte_perm(U[0], U[2], 0x6240) ^ 0x80808080u, t2b = __byte_perm(U[1], U[3], 0x6240) ^ 0x80808080u;
         int s12 = __dp4a((int)t1a, 0x01010101, __dp4a((int)t1b, 0x01010101, 0)) * 65536 + __dp4a((int)t2a, 0x01010101, __dp4a((int)t2b, 0x01010101, 0));
-#pragma unroll
-        for (int o = 1; o < 16; o <<= 1) s12 += __shfl_xor_sync(0xffffffffu, s12, o);
+        s12 = __reduce_add_sync(half_mask, s12);
         if (valid) {
           // words (0,1) of a lane feed its first mma pair, words (2,3) the second; see linear_phase
           const int chunk = u >> 4, r = u & 15, tk = r >> 2, w = r & 3;
@@ -504,7 +583,15 @@ __device__ __forceinline__ void stage_x(Ctx &c, const StageSrc &src, int K, cons
       }
     }
   }
+#ifdef PT_MK_TRACE_WAITS
+  sq[4] = sclk();
+#endif
   consumer_sync();
+#ifdef PT_MK_TRACE_WAITS
+  sq[5] = sclk();
+  if (c.tr && tid == 0)
+    for (int q = 0; q < 5; ++q) atomicAdd(c.tr + 48 + q, (unsigned long long)(sq[q + 1] - sq[q]));
+#endif
 }
 
 // Epilogue kinds of the linear phases
@@ -531,7 +618,7 @@ struct Split {
 // Phases between layers write tagged words; the LM head keeps its arg-max and optionally writes fp16 logits.
 template <bool HEAD, bool TP>
 __device__ __forceinline__ void tile_epilogue(const Params &p, const volatile PhaseInfo *pi, float lo, float hi, int rt, int lane, Best *best,
-                                              const uint32_t *pre = nullptr) {
+                                              float &ssq, const uint32_t *pre = nullptr) {
   const int g = lane >> 2, b = lane & 3;
   if (b >= p.B) return;
   const int epi = pi->epi, N = pi->N;
@@ -565,7 +652,11 @@ __device__ __forceinline__ void tile_epilogue(const Params &p, const volatile Ph
       uint32_t *w = outw + (size_t)b * N + n;
       // the residual is the value this SM wrote to the same word one or two phases ago (or the embedding, which the first
       // staging of this launch has already seen complete)
-      if (epi == EPI_RESID) y = h_add(__ushort_as_half((unsigned short)((pre ? pre[hr] : ld_word(w)) & 0xFFFFu)), y);
+      if (epi == EPI_RESID) {
+        y = h_add(__ushort_as_half((unsigned short)((pre ? pre[hr] : ld_word(w)) & 0xFFFFu)), y);
+        const float yf = __half2float(y);
+        ssq = fmaf(yf, yf, ssq);   // this lane's share of sum(x^2) of its batch row, for the RMSNorm of the next staging
+      }
       st_word(w, tag, y);
     }
   }
@@ -582,6 +673,13 @@ __device__ __forceinline__ void imma0(int (&d)[4], uint32_t a0, uint32_t a1, uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+// d = a b + {c0, c1, c0, c1}: both rows of the lane start from the same per-column initialiser
+__device__ __forceinline__ void imma_c(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, int c0, int c1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
+}
+
 // One tile in registers: the lane's 16 bytes of rows g (a) and g + 8 (b), and the two rows' group scales (INT4).
 struct TileRegs { uint4 a, b; uint32_t s; };
 
@@ -592,41 +690,56 @@ struct TileRegs { uint4 a, b; uint32_t s; };
 // The loop body is what bounds the kernel once the stream flows, so it is kept to the instructions that the arithmetic
 // needs: two AND per packed word and one integer mma per 512 weights (INT4), operands and accumulator initialisers that
 // arrive from shared memory in fragment order, ring positions advanced without divisions.
+#ifdef PT_MK_TRACE_WAITS
+constexpr bool NOMATH = true;   // diagnostics build: bit 0 of `debug` skips the tile math (bit 1 the tile loads too), waits are timed
+constexpr int TRS = 64;         // trace slots per (SM, layer)
+#else
+constexpr bool NOMATH = false;
+constexpr int TRS = 32;
+#endif
 template <int WFMT, bool TP>
-__device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best *best) {
+__device__ __forceinline__ void linear_phase(Ctx &c, int mat, int nchunks, Best *best) {
   constexpr int TILE = WTraits<WFMT>::kTileBytes;
   constexpr bool I4 = (WFMT == PT_W_INT4);
   const Params &p = c.p;
   const volatile PhaseInfo *pi = &c.sh->phase;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
-  const int r0 = (int)((long long)c.sm * n_rt / c.G), r1 = (int)((long long)(c.sm + 1) * n_rt / c.G);
-  const int m = r1 - r0, total = m * nchunks;
-  const Split sp(total);
-  const int len = sp.len(warp), start = sp.start(warp), nstages = sp.stages();
-  const int first_rt = start / nchunks;
-  int rt = first_rt, ch = start - first_rt * nchunks;
+#ifdef PT_MK_TRACE_WAITS
+  long long pq[6];
+  auto pclk = []() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)); return t; };
+  pq[0] = pclk();
+#endif
+  const Geo &geo = c.sh->geo[mat];
+  const int r0 = geo.r0, m = geo.m;
+  Split sp(0);
+  sp.base = geo.base;
+  sp.rem = geo.rem;
+  const int len = sp.len(warp), nstages = sp.stages();
+  const int first_rt = geo.first_rt[warp];
+  int rt = first_rt, ch = geo.ch0[warp];
   const bool enters_midway = ch != 0;  // another warp holds the beginning of this warp's first row tile
   float acc0 = 0.f, acc1 = 0.f;
+  float ssq = 0.f;   // sum of squares of the x values this lane's epilogues write (residual phases)
   const uint32_t ring_s = smem_addr(c.ring) + warp * TILE + lane * 16;
   const uint32_t full_s = smem_addr(&c.sh->full[0]), empty_s = smem_addr(&c.sh->empty[0]);
-  // per-lane operand addresses: base + chunk * stride, with stride 0 and the zero block for lanes that carry no batch column
-  uint32_t x_s, x_cs, corr_s, corr_cs, xsc_s;
-  {
-    const uint32_t zero_s = smem_addr(&c.sh->zeros[0]);
-    if (I4) {
-      const bool has = g < 2 * p.B;
-      x_s = has ? smem_addr(c.xs) + g * 128 + tig * 32 : zero_s;
-      x_cs = has ? p.B * 256 : 0;
-      corr_s = tig < p.B ? smem_addr(&c.sh->corr[0][tig]) : zero_s;
-      corr_cs = tig < p.B ? (uint32_t)sizeof(int4) * BMAX : 0;
-      xsc_s = smem_addr(&c.sh->xscale[0][tig < p.B ? tig : 0]);
-    } else {
-      const bool has = !(g & 1) && (g >> 1) < p.B;   // batch b sits in column 2b, so that lane tig = b ends up with its sums
-      x_s = has ? smem_addr(c.xs) + (g >> 1) * p.xs_stride + tig * 16 : zero_s;
-      x_cs = has ? 64 : 0;
-      corr_s = corr_cs = xsc_s = 0;
-    }
+  // Per-lane operand addresses.  Column n of the mma's B operand (the activations) only feeds column n of the result, and only
+  // the columns of real batch rows are ever read back, so lanes that hold other columns load nothing: their operand
+  // registers and the sums derived from them are never used.
+  uint32_t x_s, corr_s, xsc_s;
+  bool has_x, has_c;
+  if (I4) {
+    has_x = g < 2 * p.B;                // B-operand columns 2b (t1) and 2b + 1 (t2) of batch row b
+    has_c = tig < p.B;                  // accumulator columns 2 tig, 2 tig + 1 belong to batch row tig
+    x_s = smem_addr(c.xs) + g * 128 + tig * 32;
+    corr_s = smem_addr(&c.sh->corr[0][has_c ? tig : 0]);
+    xsc_s = smem_addr(&c.sh->xscale[0][has_c ? tig : 0]);
+  } else {
+    has_x = !(g & 1) && (g >> 1) < p.B;  // batch b sits in column 2b, so that lane tig = b ends up with its sums
+    has_c = false;
+    x_s = smem_addr(c.xs) + (g >> 1) * p.xs_stride + tig * 16;
+    corr_s = xsc_s = 0;
   }
+  const uint32_t x_cs = I4 ? (uint32_t)p.B * 256u : 64u;
 
   // Residual words of the row tile whose sum this warp will finish after the loop (row tiles shared by several warps, the usual
   // case of the residual phases): requested now, so that their round trip is not at the end of the phase.
@@ -644,91 +757,210 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int n_rt, int nchunks, Best
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.b.x), "=r"(t.b.y), "=r"(t.b.z), "=r"(t.b.w) : "r"(t_s + 512));
     if (I4) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(t.s) : "r"(t_s - lane * 16 + 1024 + g * 4));
   };
-  auto compute = [&](const TileRegs &t) {
-    if (p.debug & 1) return;
-    if (I4) {
-      constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u;
-      uint4 xa;
-      int lo[4], hi[4];
-      float xs;
-      const uint32_t xaddr = x_s + ch * x_cs;
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xa.x), "=r"(xa.y), "=r"(xa.z), "=r"(xa.w) : "r"(xaddr));
-      asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(lo[0]), "=r"(lo[1]), "=r"(lo[2]), "=r"(lo[3]) : "r"(corr_s + ch * corr_cs));
-      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xs) : "r"(xsc_s + ch * (uint32_t)(sizeof(float) * BMAX)));
-      imma0(hi, t.a.x & HI, t.b.x & HI, t.a.y & HI, t.b.y & HI, xa.z, xa.w);
-      imma(lo, t.a.x & LO, t.b.x & LO, t.a.y & LO, t.b.y & LO, xa.x, xa.y);
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xa.x), "=r"(xa.y), "=r"(xa.z), "=r"(xa.w) : "r"(xaddr + 16));
-      imma(hi, t.a.z & HI, t.b.z & HI, t.a.w & HI, t.b.w & HI, xa.z, xa.w);
-      imma(lo, t.a.z & LO, t.b.z & LO, t.a.w & LO, t.b.w & LO, xa.x, xa.y);
-      // value x 16 = 4096 lo(t1) + 16 lo(t2) + 256 hi(t1) + hi(t2); |.| < 2^31 for |t1| <= 125 (see stage_x)
-      const int v0 = ((lo[0] << 8) + lo[1]) * 16 + (hi[0] << 8) + hi[1];
-      const int v1 = ((lo[2] << 8) + lo[3]) * 16 + (hi[2] << 8) + hi[3];
-      const float2 sf = __half22float2(u32_as_h2(t.s));
-      acc0 = fmaf(sf.x * xs, (float)v0, acc0);
-      acc1 = fmaf(sf.y * xs, (float)v1, acc1);
-    } else {
-      uint4 xv;
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w) : "r"(x_s + ch * x_cs));
-      float cc[4] = {acc0, 0.f, acc1, 0.f};
-      mma16816(cc, t.a.x, t.b.x, t.a.y, t.b.y, xv.x, xv.y);
-      mma16816(cc, t.a.z, t.b.z, t.a.w, t.b.w, xv.z, xv.w);
-      acc0 = cc[0];
-      acc1 = cc[2];
-    }
+  // End of a tile: the chunk counter moves on; at the end of a row tile its sum is finished (or parked, when another warp
+  // holds the row tile's beginning).
+  auto next_chunk = [&]() {
     if (++ch == nchunks) {  // this warp reached the end of row tile rt
       if (rt == first_rt && enters_midway) store_partial(0);
-      else tile_epilogue<!I4, TP>(p, pi, acc0, acc1, rt, lane, best);  // had all of it
+      else tile_epilogue<!I4, TP>(p, pi, acc0, acc1, rt, lane, best, ssq);  // had all of it
       ch = 0;
       ++rt;
       acc0 = acc1 = 0.f;
     }
   };
+  constexpr uint32_t LO = 0x0F0F0F0Fu, HI = 0xF0F0F0F0u;
+  // value x 16 = 4096 lo(t1) + 16 lo(t2) + 256 hi(t1) + hi(t2); |.| < 2^31 for |t1| <= 125 (see stage_x)
+  auto fold = [&](const int (&lo)[4], const int (&hi)[4], uint32_t s, float xs) {
+    const int v0 = ((lo[0] << 8) + lo[1]) * 16 + (hi[0] << 8) + hi[1];
+    const int v1 = ((lo[2] << 8) + lo[3]) * 16 + (hi[2] << 8) + hi[3];
+    const float2 sf = __half22float2(u32_as_h2(s));
+    acc0 = fmaf(sf.x * xs, (float)v0, acc0);
+    acc1 = fmaf(sf.y * xs, (float)v1, acc1);
+  };
+  // The activation-side operands of one tile: the chunk's two 16-byte B-operand pieces, the accumulator initialiser
+  // {-8 sum(t1), -8 sum(t2)} and the chunk's scale.  They do not depend on the weight stream, so they are requested BEFORE the
+  // wait for the stage and their latency hides behind it.
+  struct XOps { uint4 x0, x1; int c0, c1; float xs; };
+  auto load_xops = [&](int chunk, XOps &o) {
+    const uint32_t xaddr = x_s + chunk * x_cs;
+    if (has_x) {
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(o.x0.x), "=r"(o.x0.y), "=r"(o.x0.z), "=r"(o.x0.w) : "r"(xaddr));
+      if (I4) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(o.x1.x), "=r"(o.x1.y), "=r"(o.x1.z), "=r"(o.x1.w) : "r"(xaddr + 16));
+    }
+    if (I4) {
+      if (has_c) asm volatile("ld.shared.v2.s32 {%0,%1}, [%2];" : "=r"(o.c0), "=r"(o.c1) : "r"(corr_s + chunk * (uint32_t)(sizeof(int4) * BMAX)));
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(o.xs) : "r"(xsc_s + chunk * (uint32_t)(sizeof(float) * BMAX)));
+    }
+  };
+  // One tile (the last of an odd-length range, and the fp16 tiles of the LM head).
+  auto compute = [&](const TileRegs &t, const XOps &o) {
+    if (NOMATH && (p.debug & 1)) return;
+    if (I4) {
+      int lo[4], hi[4];
+      imma0(hi, t.a.x & HI, t.b.x & HI, t.a.y & HI, t.b.y & HI, o.x0.z, o.x0.w);
+      imma_c(lo, t.a.x & LO, t.b.x & LO, t.a.y & LO, t.b.y & LO, o.x0.x, o.x0.y, o.c0, o.c1);
+      imma(hi, t.a.z & HI, t.b.z & HI, t.a.w & HI, t.b.w & HI, o.x1.z, o.x1.w);
+      imma(lo, t.a.z & LO, t.b.z & LO, t.a.w & LO, t.b.w & LO, o.x1.x, o.x1.y);
+      fold(lo, hi, t.s, o.xs);
+    } else {
+      float cc[4] = {acc0, 0.f, acc1, 0.f};
+      mma16816(cc, t.a.x, t.b.x, t.a.y, t.b.y, o.x0.x, o.x0.y);
+      mma16816(cc, t.a.z, t.b.z, t.a.w, t.b.w, o.x0.z, o.x0.w);
+      acc0 = cc[0];
+      acc1 = cc[2];
+    }
+    next_chunk();
+  };
+  // Two consecutive tiles of the warp's range, interleaved by hand (every shared-memory load and mma here is an ordered asm
+  // statement, so the source order is the issue order): four independent chains of two dependent integer mma each, then the
+  // two folds.  With four warps per scheduler this independence is what keeps the issue slots busy.
+  auto compute2 = [&](const TileRegs &ta, const TileRegs &tb, const XOps &oa, const XOps &ob) {
+    if (NOMATH && (p.debug & 1)) return;
+    if (I4) {
+      int lo_a[4], hi_a[4], lo_b[4], hi_b[4];
+      imma0(hi_a, ta.a.x & HI, ta.b.x & HI, ta.a.y & HI, ta.b.y & HI, oa.x0.z, oa.x0.w);
+      imma_c(lo_a, ta.a.x & LO, ta.b.x & LO, ta.a.y & LO, ta.b.y & LO, oa.x0.x, oa.x0.y, oa.c0, oa.c1);
+      imma0(hi_b, tb.a.x & HI, tb.b.x & HI, tb.a.y & HI, tb.b.y & HI, ob.x0.z, ob.x0.w);
+      imma_c(lo_b, tb.a.x & LO, tb.b.x & LO, tb.a.y & LO, tb.b.y & LO, ob.x0.x, ob.x0.y, ob.c0, ob.c1);
+      imma(hi_a, ta.a.z & HI, ta.b.z & HI, ta.a.w & HI, ta.b.w & HI, oa.x1.z, oa.x1.w);
+      imma(lo_a, ta.a.z & LO, ta.b.z & LO, ta.a.w & LO, ta.b.w & LO, oa.x1.x, oa.x1.y);
+      imma(hi_b, tb.a.z & HI, tb.b.z & HI, tb.a.w & HI, tb.b.w & HI, ob.x1.z, ob.x1.w);
+      imma(lo_b, tb.a.z & LO, tb.b.z & LO, tb.a.w & LO, tb.b.w & LO, ob.x1.x, ob.x1.y);
+      fold(lo_a, hi_a, ta.s, oa.xs);
+      next_chunk();
+      fold(lo_b, hi_b, tb.s, ob.xs);
+      next_chunk();
+    } else {
+      compute(ta, oa);
+      compute(tb, ob);
+    }
+  };
 
-  // Stage j / 2 of this phase holds tiles j and j + 1 of this warp's range.  The first tile is multiplied while the second
-  // is on its way to the registers; the stage is handed back to the producer as soon as the second tile's loads are issued.
+#ifdef PT_MK_TRACE_WAITS
+  pq[1] = pclk();
+  // diagnostics build: SM-cycle accounting of the loop for three sample warps (wait for the stage / operand loads / math)
+  const int dw = (warp == 0) ? 0 : (warp == 5 ? 1 : (warp == NCW - 1 ? 2 : -1));
+  unsigned long long *dslot = (c.tr && dw >= 0 && lane == 0) ? c.tr + 32 + 4 * dw : nullptr;
+  auto clk = []() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)); return t; };
+#endif
+  // Stage j / 2 of this phase holds tiles j and j + 1 of this warp's range.  The activation-side operands are requested first,
+  // then the stage is awaited, both tiles go to registers, the stage is handed back to the producer as soon as those loads
+  // are issued, and the pair is multiplied.
+  XOps oa, ob;
+  oa.x0 = oa.x1 = ob.x0 = ob.x1 = make_uint4(0, 0, 0, 0);
+  oa.c0 = oa.c1 = ob.c0 = ob.c1 = 0;
+  oa.xs = ob.xs = 0.f;
   for (int j = 0; j < nstages; j += 2) {
+    const bool first = j < len, second = j + 1 < len;
+    if (first) load_xops(ch, oa);
+    if (second) load_xops(ch + 1 == nchunks ? 0 : ch + 1, ob);
+#ifdef PT_MK_TRACE_WAITS
+    const unsigned long long t_w = (c.tr && tid == 0) ? gtime() : 0ull;
+    const long long c0 = clk();
+#endif
     const bool got = mbar_wait(full_s + c.slot * 8, c.par, &c.sh->abort);
+#ifdef PT_MK_TRACE_WAITS
+    if (c.tr && tid == 0) c.tr[23] += gtime() - t_w;   // time this phase's consumer spent waiting for the weight stream
+    const long long c1 = clk();
+#endif
     if (!got) {
       c.sh->abort = 1;
-      if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 4);
+      if (lane == 0 && p.error_flag) atomicCAS(p.error_flag, 0, 4);
     }
     const uint32_t t_s = ring_s + c.slot * STAGE_BYTES;
-    TileRegs t;
-    if (j < len && got) {
-      load_tile(t_s, t);
-      compute(t);
-    }
-    const bool second = j + 1 < len && got;
-    if (second) load_tile(t_s + NCW * TILE, t);
+    TileRegs ta, tb;
+#ifdef PT_MK_TRACE_WAITS
+    ta.a = ta.b = tb.a = tb.b = make_uint4(0, 0, 0, 0);
+    ta.s = tb.s = 0;
+    const bool skip_loads = (p.debug & 2) != 0;
+    if (first && got && !skip_loads) load_tile(t_s, ta);
+    if (second && got && !skip_loads) load_tile(t_s + NCW * TILE, tb);
+#else
+    if (first && got) load_tile(t_s, ta);
+    if (second && got) load_tile(t_s + NCW * TILE, tb);
+#endif
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_s + c.slot * 8);
     c.advance();
-    if (second) compute(t);
+#ifdef PT_MK_TRACE_WAITS
+    long long c2;
+    asm volatile("{\n\t.reg .u32 z;\n\tadd.u32 z, %1, %2;\n\tand.b32 z, z, 0;\n\tmov.u64 %0, %%clock64;\n\t}" : "=l"(c2) : "r"(ta.a.x), "r"(tb.b.w));
+#endif
+    if (got) {
+      if (second) compute2(ta, tb, oa, ob);
+      else if (first) compute(ta, oa);
+    }
+#ifdef PT_MK_TRACE_WAITS
+    long long c3;
+    asm volatile("{\n\t.reg .u32 z;\n\tadd.u32 z, %1, %2;\n\tand.b32 z, z, 0;\n\tmov.u64 %0, %%clock64;\n\t}" : "=l"(c3) : "r"(__float_as_uint(acc0)), "r"(__float_as_uint(acc1)));
+    if (dslot) {
+      atomicAdd(dslot + 0, (unsigned long long)(c1 - c0));
+      atomicAdd(dslot + 1, (unsigned long long)(c2 - c1));
+      atomicAdd(dslot + 2, (unsigned long long)(c3 - c2));
+      atomicAdd(dslot + 3, 1ull);
+    }
+#endif
   }
+#ifdef PT_MK_TRACE_WAITS
+  pq[2] = pclk();
+#endif
   if (len > 0 && ch != 0) store_partial(rt == first_rt ? 0 : 1);  // the range ended inside a row tile
   consumer_sync();
+#ifdef PT_MK_TRACE_WAITS
+  pq[3] = pclk();
+#endif
   // ---- row tiles shared by several warps: warp (r % NCW) sums the pieces in warp order
   for (int r = warp; r < m; r += NCW) {
-    const int q0 = r * nchunks, q1 = q0 + nchunks - 1;
-    const int w_lo = sp.owner(q0), w_hi = sp.owner(q1);
+    int w_lo, w_hi;
+    if (r < GEO_RT) {
+      w_lo = geo.w_lo[r];
+      w_hi = geo.w_hi[r];
+    } else {
+      const int q0 = r * nchunks;
+      w_lo = sp.owner(q0);
+      w_hi = sp.owner(q0 + nchunks - 1);
+    }
     if (w_lo == w_hi) continue;  // one warp had the whole row tile and already wrote it
     float v0 = 0.f, v1 = 0.f;
     for (int w = w_lo; w <= w_hi; ++w) {
-      const int s_w = (sp.start(w) / nchunks == r) ? 0 : 1;  // r is the first row tile of w's range, or its last
+      const int s_w = (geo.first_rt[w] == r) ? 0 : 1;  // r is the first row tile of w's range, or its last
       const float2 t = *reinterpret_cast<const float2 *>(&c.sh->red[w][s_w][lane][0]);
       v0 += t.x;
       v1 += t.y;
     }
-    tile_epilogue<!I4, TP>(p, pi, v0, v1, r, lane, best, (has_pre && r == warp) ? pre : nullptr);
+    tile_epilogue<!I4, TP>(p, pi, v0, v1, r, lane, best, ssq, (has_pre && r == warp) ? pre : nullptr);
+  }
+#ifdef PT_MK_TRACE_WAITS
+  pq[4] = pclk();
+#endif
+  const bool makes_x = I4 && pi->epi == EPI_RESID && !(TP && pi->push);
+  if (makes_x) {  // lanes (g, tig) of a warp hold batch row tig: sum over g, lanes 0 .. B-1 keep the warp's sums
+    float v = ssq;
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
+    if (lane < p.B) c.sh->wssq[warp][lane] = v;
   }
   if (pi->out_seq) {  // tell the other SMs (of every rank, for pushed partial sums) that this SM's rows of the phase are written
     consumer_sync();
     if (TP && pi->push) {
       if (tid < p.tp) red_add_sys(p.peer_flag[tid] + p.rank * 256, 1u);
     } else if (tid == 0) {
+      if (makes_x)
+        for (int b = 0; b < p.B; ++b) {
+          float t = 0.f;
+#pragma unroll
+          for (int w = 0; w < NCW; ++w) t += c.sh->wssq[w][b];
+          st_tagged(p.flag_ssq + b * 256 + c.sm, __float_as_uint(t), pi->out_seq);
+        }
       st_flag(p.flag_sm + c.sm, pi->out_seq);
     }
   }
+#ifdef PT_MK_TRACE_WAITS
+  pq[5] = pclk();
+  if (c.tr && tid == 0)
+    for (int q = 0; q < 5; ++q) atomicAdd(c.tr + 56 + q, (unsigned long long)(pq[q + 1] - pq[q]));
+#endif
 }
 
 // RoPE (rotate_half form) on elements i and i + H/2 of one head vector -> dst (shared), reference fp16 roundings.
@@ -782,7 +1014,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
         }
         if (!got) {
           sh->abort = 1;
-          if (p.error_flag) atomicExch(p.error_flag, 8);
+          if (p.error_flag) atomicCAS(p.error_flag, 0, 8);
         }
         auto val = [&](int j) { return __ushort_as_half((unsigned short)(w[j] & 0xFFFFu)); };
         rope_pair(val(0), val(1), rs, rc, i, sh->qs[k]);
@@ -808,7 +1040,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
       if (n_load > 0) {
         if (!mbar_wait(smem_addr(&sh->full[slot]), c.par, &sh->abort)) {
           sh->abort = 1;
-          if (lane == 0 && p.error_flag) atomicExch(p.error_flag, 5);
+          if (lane == 0 && p.error_flag) atomicCAS(p.error_flag, 0, 5);
         }
         if (c.tr && tid == 0 && k == 0) c.tr[15] = gtime();
         Ks = reinterpret_cast<const __half *>(c.ring + (size_t)slot * STAGE_BYTES);
@@ -973,7 +1205,7 @@ __device__ __forceinline__ void attention_phase(Ctx &c, const pt_llama_layer &L,
       }
       if (!got) {
         sh->abort = 1;
-        if (p.error_flag) atomicExch(p.error_flag, 9);
+        if (p.error_flag) atomicCAS(p.error_flag, 0, 9);
       }
       st_word(p.attnw + (size_t)b * p.dq + (size_t)head * H + gt, attn_tag, __float2half_rn(o / Lsum));
       group_sync(grp);  // ps / ml may be reused by the group's next combine; the head's words are all issued
@@ -993,15 +1225,22 @@ struct Producer {
   bool first_round;    // slots have not been used yet: nothing to wait for
   uint32_t ring_s, full_s, empty_s;  // shared-memory addresses
   bool ok;
+  unsigned long long *tr;  // optional stamps of the layer being pushed: [27] += time blocked on a full ring, [31] = layer pushed
   // The loop below competes with the consumer warps for issue slots, so it is kept to a handful of instructions per stage:
   // no divisions, all addresses incremental.  One stage: `bytes` from src at offset 0 and, for attention stages, `bytes2`
   // from src2 at V_OFFSET.
   __device__ __forceinline__ void push(const void *src, uint32_t bytes, const void *src2, uint32_t bytes2) {
+#ifdef PT_MK_TRACE_WAITS
+    const unsigned long long t_w = tr ? gtime() : 0ull;
+#endif
     if (!first_round && !mbar_wait(empty_s + slot * 8, parity, &sh->abort)) {
-      if (ok && p.error_flag) atomicExch(p.error_flag, 6);
+      if (ok && p.error_flag) atomicCAS(p.error_flag, 0, 6);
       ok = false;
       sh->abort = 1;
     }
+#ifdef PT_MK_TRACE_WAITS
+    if (tr) tr[27] += gtime() - t_w;
+#endif
     if (ok) {
       const uint32_t fb = full_s + slot * 8, dst = ring_s + slot * STAGE_BYTES;
       mbar_expect_tx(fb, bytes + bytes2);
@@ -1058,6 +1297,12 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   Shared *sh = reinterpret_cast<Shared *>(xs + (((size_t)p.B * p.xs_stride + 127) / 128) * 128);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int step = *p.step;
+  // Every block takes the same decision here: the words it depends on are only written at the very end of a launch.
+  if (p.done_flag && __ldcg(p.done_flag)) return;  // early stop: every sequence had produced its eos id before the previous step
+  if (step < 0 || step >= p.max_len) {             // no position left in the id container / RoPE tables / page table
+    if (tid == 0 && p.error_flag) atomicCAS(p.error_flag, 0, 12);
+    return;
+  }
 
   if (tid == 0) {
     for (int s = 0; s < p.ns; ++s) {
@@ -1076,15 +1321,26 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   if (warp == NCW) {
     // ---------------- producer: one lane walks the whole step's weight / KV stream of this SM
     if (lane == 0) {
-      Producer pr{p, sh, (int)blockIdx.x, (int)gridDim.x, 0, 0u, true, smem_addr(ring), smem_addr(&sh->full[0]), smem_addr(&sh->empty[0]), true};
+      Producer pr{p, sh, (int)blockIdx.x, (int)gridDim.x, 0, 0u, true, smem_addr(ring), smem_addr(&sh->full[0]), smem_addr(&sh->empty[0]), true, nullptr};
       for (int l = 0; l < p.n_layer; ++l) {
         const pt_llama_layer &L = p.layers[l];
+#ifdef PT_MK_TRACE_WAITS
+        if (p.trace) {
+          if (pr.tr) pr.tr[31] = gtime();
+          pr.tr = p.trace + ((size_t)blockIdx.x * p.n_layer + l) * TRS;
+          pr.tr[27] = 0ull;
+        }
+#endif
         pr.push_matrix((const unsigned char *)L.qkv, n_rt_qkv, nc_d, TILE_I4);
         pr.push_attention(L, step);
         pr.push_matrix((const unsigned char *)L.o, n_rt_o, nc_q, TILE_I4);
         pr.push_matrix((const unsigned char *)L.gu, n_rt_gu, nc_d, TILE_I4);
         pr.push_matrix((const unsigned char *)L.down, n_rt_o, nc_f, TILE_I4);
       }
+#ifdef PT_MK_TRACE_WAITS
+      if (pr.tr) pr.tr[31] = gtime();
+      pr.tr = nullptr;
+#endif
       pr.push_matrix(p.head, n_rt_head, nc_head, TILE_F16);
     }
     return;
@@ -1099,30 +1355,84 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   Ctx c{p, ring, xs, sh, (int)blockIdx.x, (int)gridDim.x, step, p.barrier + which, 0u, 0u, 0u, launches * (uint32_t)n_phases,
         launches * 2u * (uint32_t)p.n_layer, nullptr};
 
+  // this SM's share of every matrix and the warps' tile ranges inside it
+  {
+    const int n_rt_of[5] = {n_rt_qkv, n_rt_o, n_rt_gu, n_rt_o, n_rt_head};
+    const int nch_of[5] = {nc_d, nc_q, nc_d, nc_f, nc_head};
+    if (tid < 5) {
+      Geo &gq = sh->geo[tid];
+      const int a0 = (int)((long long)blockIdx.x * n_rt_of[tid] / (int)gridDim.x), a1 = (int)((long long)(blockIdx.x + 1) * n_rt_of[tid] / (int)gridDim.x);
+      const Split sq((a1 - a0) * nch_of[tid]);
+      gq.r0 = a0; gq.m = a1 - a0; gq.base = sq.base; gq.rem = sq.rem;
+    }
+    consumer_sync();
+    if (tid < 5 * NCW) {
+      const int k = tid / NCW, w = tid - k * NCW;
+      Geo &gq = sh->geo[k];
+      Split sq(0);
+      sq.base = gq.base; sq.rem = gq.rem;
+      const int st = sq.start(w), fr = st / nch_of[k];
+      gq.first_rt[w] = (short)fr;
+      gq.ch0[w] = (short)(st - fr * nch_of[k]);
+    } else if (tid >= 128 && tid < 128 + 5 * GEO_RT) {
+      const int k = (tid - 128) / GEO_RT, r = (tid - 128) - k * GEO_RT;
+      Geo &gq = sh->geo[k];
+      if (r < gq.m) {
+        Split sq(0);
+        sq.base = gq.base; sq.rem = gq.rem;
+        gq.w_lo[r] = (unsigned char)sq.owner(r * nch_of[k]);
+        gq.w_hi[r] = (unsigned char)sq.owner(r * nch_of[k] + nch_of[k] - 1);
+      }
+    }
+  }
   // embedding: the SMs share the gather; the copy in global memory feeds the first staging and the residual adds
-  for (int i = tid; i < p.B * (p.d / 8); i += NCT) {
-    const int b = i / (p.d / 8), u = i - b * (p.d / 8);
-    if ((u % c.G) != c.sm) continue;
-    int id = p.ids[(size_t)b * p.max_len + step];
-    id = min(max(id, 0), p.emb_rows - 1);
-    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.emb + (size_t)id * p.d) + u);
-    const uint32_t hw[4] = {v.x, v.y, v.z, v.w}, t = c.tag(0) << 16;
-    uint32_t *dst = p.xw + (size_t)b * p.d + (size_t)u * 8;
-    reinterpret_cast<uint4 *>(dst)[0] = make_uint4(t | (hw[0] & 0xFFFFu), t | (hw[0] >> 16), t | (hw[1] & 0xFFFFu), t | (hw[1] >> 16));
-    reinterpret_cast<uint4 *>(dst)[1] = make_uint4(t | (hw[2] & 0xFFFFu), t | (hw[2] >> 16), t | (hw[3] & 0xFFFFu), t | (hw[3] >> 16));
+  {
+    float esq[BMAX];
+#pragma unroll
+    for (int b = 0; b < BMAX; ++b) esq[b] = 0.f;
+    for (int i = tid; i < p.B * (p.d / 8); i += NCT) {
+      const int b = i / (p.d / 8), u = i - b * (p.d / 8);
+      if ((u % c.G) != c.sm) continue;
+      int id = p.ids[(size_t)b * p.max_len + step];
+      id = min(max(id, 0), p.emb_rows - 1);
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.emb + (size_t)id * p.d) + u);
+      const uint32_t hw[4] = {v.x, v.y, v.z, v.w}, t = c.tag(0) << 16;
+      uint32_t *dst = p.xw + (size_t)b * p.d + (size_t)u * 8;
+      reinterpret_cast<uint4 *>(dst)[0] = make_uint4(t | (hw[0] & 0xFFFFu), t | (hw[0] >> 16), t | (hw[1] & 0xFFFFu), t | (hw[1] >> 16));
+      reinterpret_cast<uint4 *>(dst)[1] = make_uint4(t | (hw[2] & 0xFFFFu), t | (hw[2] >> 16), t | (hw[3] & 0xFFFFu), t | (hw[3] >> 16));
+      float q = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(u32_as_h2(hw[j]));
+        q += f.x * f.x + f.y * f.y;
+      }
+#pragma unroll
+      for (int bb = 0; bb < BMAX; ++bb)
+        if (bb == b) esq[bb] += q;
+    }
+    if (!TP) {  // this SM's share of sum(x^2) per batch row, published with the progress word (see Params::flag_ssq)
+#pragma unroll
+      for (int b = 0; b < BMAX; ++b) {
+        const float t = (b < p.B) ? consumer_sum(c, esq[b]) : 0.f;
+        if (b < p.B && tid == 0) st_tagged(p.flag_ssq + b * 256 + c.sm, __float_as_uint(t), c.seq(0));
+      }
+    }
   }
   consumer_sync();
   if (tid == 0) st_flag(p.flag_sm + c.sm, c.seq(0));
 
   // The four linear phases of a layer run through one copy of the staging and multiplication code (a loop with a table of
   // operands), which keeps the kernel small enough for the instruction cache and lets the compiler inline everything.
-  unsigned long long *tr = p.trace ? p.trace + ((size_t)blockIdx.x * p.n_layer) * 32 : nullptr;
-#define PT_STAMP(k) do { if (tr && tid == 0) tr[l * 32 + (k)] = gtime(); } while (0)
+  unsigned long long *tr = p.trace ? p.trace + ((size_t)blockIdx.x * p.n_layer) * TRS : nullptr;
+#define PT_STAMP(k) do { if (tr && tid == 0) tr[l * TRS + (k)] = gtime(); } while (0)
   int xcur = 0;  // which copy of x is current (tp > 1)
   for (int l = 0; l < p.n_layer; ++l) {
     const pt_llama_layer &L = p.layers[l];
     const int ph0 = 1 + 5 * l;
     PT_STAMP(0);
+#ifdef PT_MK_TRACE_WAITS
+    if (tr && tid == 0) tr[l * TRS + 23] = 0ull;
+#endif
     for (int ph = 0; ph < 4; ++ph) {
       // x lives in xw[cur] (two copies alternate when tp > 1, where every staging that follows a row-parallel linear forms
       // x + sum of the ranks' partial sums and stores it into the other copy)
@@ -1144,6 +1454,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
           src.x_out = p.xw + (xcur ^ 1) * xsz; src.x_out_tag = c.tag(ph0);
         } else {
           src.x = p.xw + xcur * xsz; src.x_tag = c.tag(ph0 - 1); src.want = c.seq(ph0 - 1);
+          src.ssq_flags = p.flag_ssq;   // written by the embedding / the previous layer's down_proj
         }
       } else if (ph == 1) {
         src.x = p.attnw; src.x_tag = c.tag(ph0 + 1); src.flags = p.flag_head; src.flag_cols = p.B * p.n_head; src.want = c.seq(ph0 + 1);
@@ -1159,6 +1470,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
           src.x_out = p.xw + (xcur ^ 1) * xsz; src.x_out_tag = c.tag(ph0 + 3);
         } else {
           src.x = p.xw; src.x_tag = c.tag(ph0 + 2); src.want = c.seq(ph0 + 2);
+          src.ssq_flags = p.flag_ssq;   // written by this layer's o_proj
         }
       } else {
         src.x = p.actw; src.x_tag = c.tag(ph0 + 3); src.want = c.seq(ph0 + 3);
@@ -1169,15 +1481,15 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
       if (tid == 0) {
         PhaseInfo *w = &sh->phase;
         w->outw = out; w->logits = nullptr; w->tag = c.tag(out_phase); w->out_seq = c.seq(out_phase);
-        w->epi = epi; w->N = N; w->r0 = (int)((long long)c.sm * n_rt / c.G);
+        w->epi = epi; w->N = N; w->r0 = sh->geo[ph].r0;
         w->out_ld = out_ld; w->out_off = out_off;
         w->push = push; w->push_slot = (size_t)(ph == 3 ? 1 : 0) * psz + (size_t)p.rank * xsz;
       }
-      c.tr = tr ? tr + l * 32 : nullptr;
+      c.tr = tr ? tr + l * TRS : nullptr;
       stage_x<true, TP>(c, src, K, gamma, ph == 0 ? 20 : (ph == 3 ? 24 : (ph == 2 ? 28 : 0)));
       if (src.x_out) xcur ^= 1;
       PT_STAMP(ph == 0 ? 1 : (ph == 1 ? 5 : (ph == 2 ? 8 : 10)));
-      linear_phase<PT_W_INT4, TP>(c, n_rt, K / 128, nullptr);
+      linear_phase<PT_W_INT4, TP>(c, ph, K / 128, nullptr);
       PT_STAMP(ph == 0 ? 2 : (ph == 1 ? 6 : (ph == 2 ? 9 : 11)));
       if (ph == 1) PT_STAMP(7);
       if (ph == 0) {
@@ -1198,7 +1510,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   if (tid == 0) {
     PhaseInfo *w = &sh->phase;
     w->outw = nullptr; w->logits = p.logits; w->tag = 0u; w->out_seq = 0u;
-    w->epi = EPI_HEAD; w->N = p.vocab; w->r0 = (int)((long long)c.sm * n_rt_head / c.G);
+    w->epi = EPI_HEAD; w->N = p.vocab; w->r0 = sh->geo[MAT_HEAD].r0;
     w->out_ld = 0; w->out_off = 0; w->push = 0; w->push_slot = 0;
   }
   {
@@ -1213,10 +1525,11 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
     } else {
       src.x_tag = c.tag(last);
       src.flags = p.flag_sm; src.flag_rows = 1; src.flag_cols = c.G; src.want = c.seq(last);
+      src.ssq_flags = p.flag_ssq;
     }
     stage_x<false, TP>(c, src, p.d, p.norm);
   }
-  linear_phase<PT_W_FP16, TP>(c, n_rt_head, nc_head, &best);
+  linear_phase<PT_W_FP16, TP>(c, MAT_HEAD, nc_head, &best);
   for (int b = 0; b < p.B; ++b) {
     float v = best.v[b];
     int i = best.i[b];
@@ -1243,6 +1556,13 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
   grid_sync(c);
   if (blockIdx.x == 0 && warp == 0 && !sh->abort) {
     // merge the per-SM candidates, then the loop carry (step_containers / step_loop_cond)
+    if (p.done_flag && p.stop_mask && lane == 0) {
+      // keep_going = sum(stop_mask) < batch, taken on the mask as it was BEFORE this iteration's update (base_model.py:348-352)
+      int stopped = 0;
+      for (int b = 0; b < p.B; ++b) stopped += p.stop_mask[b] ? 1 : 0;
+      if (stopped == p.B) *p.done_flag = 1;
+    }
+    __syncwarp();
     for (int b = 0; b < p.B; ++b) {
       float v = -INFINITY;
       int i = 0x7fffffff;
@@ -1278,7 +1598,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
           }
           if (!got) {
             sh->abort = 1;
-            if (p.error_flag) atomicExch(p.error_flag, 11);
+            if (p.error_flag) atomicCAS(p.error_flag, 0, 11);
           }
         }
         v = rv;
@@ -1335,23 +1655,11 @@ __global__ void stream_permute_kernel(const uint4 *__restrict__ src, uint4 *__re
 
 using namespace pt;
 
-static int mk_sm_count(int *out) {
-  static int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    PT_CUDA(cudaGetDevice(&dev));
-    PT_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  }
-  *out = n_sm;
-  return PT_OK;
-}
-
 extern "C" int pt_llama_stream_permute(int wfmt, const void *packed, void *out, int n_out, int k_in, void *stream) {
   PT_REQUIRE(packed && out && packed != out, "pt_llama_stream_permute: needs distinct source and destination buffers");
   PT_REQUIRE(wfmt == PT_W_INT4 || wfmt == PT_W_FP16, "pt_llama_stream_permute: weight format %d not used by the persistent kernel", wfmt);
   PT_REQUIRE(n_out > 0 && k_in > 0 && k_in % chunk_k(wfmt) == 0, "pt_llama_stream_permute: bad shape [%d, %d]", n_out, k_in);
-  int n_sm = 0;
-  if (int rc = mk_sm_count(&n_sm)) return rc;
+  const int n_sm = pt::sm_count();
   mk::stream_permute_kernel<<<dim3(32, n_sm), 256, 0, as_stream(stream)>>>((const uint4 *)packed, (uint4 *)out, ceil_div(n_out, 16), k_in / chunk_k(wfmt),
                                                                             tile_bytes(wfmt) / 16, n_sm);
   PT_LAUNCH_CHECK("pt_llama_stream_permute");
@@ -1361,8 +1669,8 @@ extern "C" int pt_llama_stream_permute(int wfmt, const void *packed, void *out, 
 extern "C" size_t pt_llama_step_workspace_bytes(int batch, int n_head, int head_dim, int max_pages) {
   const size_t heads = (size_t)batch * n_head;
   auto al = [](size_t v) { return (v + 255) / 256 * 256; };
-  // barrier words | per-SM progress words | per-head progress words | page (max, sum) | partial outputs (both as 8-byte tagged words) | arg-max candidates (value, index) for up to 256 SMs
-  return 256 + 1024 + al(heads * sizeof(uint32_t)) + al(heads * max_pages * 2 * sizeof(uint2)) + al(heads * max_pages * head_dim * sizeof(uint2)) + 2 * al((size_t)batch * 256 * sizeof(float));
+  // barrier words | per-SM progress words | per-SM x statistics | per-head progress words | page (max, sum) | partial outputs (both as 8-byte tagged words) | arg-max candidates (value, index) for up to 256 SMs
+  return 256 + 1024 + (size_t)mk::BMAX * 256 * sizeof(uint2) + al(heads * sizeof(uint32_t)) + al(heads * max_pages * 2 * sizeof(uint2)) + al(heads * max_pages * head_dim * sizeof(uint2)) + 2 * al((size_t)batch * 256 * sizeof(float));
 }
 
 extern "C" size_t pt_llama_tp_buffer_bytes(int batch, int d_model, int tp_size) {
@@ -1391,8 +1699,7 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   const size_t need = pt_llama_step_workspace_bytes(a->batch, a->n_head, a->head_dim, a->max_pages);
   PT_REQUIRE(a->workspace_bytes >= need, "pt_llama_decode_step: workspace needs %zu bytes, got %zu", need, a->workspace_bytes);
 
-  int n_sm = 0;
-  if (int rc = mk_sm_count(&n_sm)) return rc;
+  const int n_sm = pt::sm_count();
   static size_t smem_max = 0;
   if (smem_max == 0) {
     int dev = 0, v = 0;
@@ -1424,6 +1731,8 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   p.layers = a->layers; p.norm = (const __half *)a->norm; p.emb = (const __half *)a->emb;
   p.sin_t = (const __half *)a->rope_sin; p.cos_t = (const __half *)a->rope_cos; p.head = (const unsigned char *)a->head;
   p.ids = a->ids; p.step = a->step_dev; p.stop_mask = a->stop_mask; p.next_ids = a->next_ids; p.page_table = a->page_table;
+  p.done_flag = a->done_flag;
+  PT_REQUIRE(!a->done_flag || a->stop_mask, "pt_llama_decode_step: done_flag needs stop_mask");
   p.xw = (uint32_t *)a->x; p.qkvw = (uint32_t *)a->qkv; p.attnw = (uint32_t *)a->attn; p.actw = (uint32_t *)a->act; p.logits = (__half *)a->logits;
   p.error_flag = a->error_flag;
   p.trace = (unsigned long long *)a->trace;
@@ -1433,6 +1742,7 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   char *ws = (char *)a->workspace;
   p.barrier = (unsigned *)ws; ws += 256;
   p.flag_sm = (uint32_t *)ws; ws += 1024;
+  p.flag_ssq = (uint2 *)ws; ws += (size_t)mk::BMAX * 256 * sizeof(uint2);
   p.flag_head = (uint32_t *)ws; ws += al(heads * sizeof(uint32_t));
   p.ws_ml = (uint2 *)ws; ws += al(heads * a->max_pages * 2 * sizeof(uint2));
   p.ws_o = (uint2 *)ws; ws += al(heads * a->max_pages * a->head_dim * sizeof(uint2));
@@ -1447,11 +1757,23 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   const size_t smem = (size_t)p.ns * mk::STAGE_BYTES + fixed;
 
   {
-    static uint32_t hint_set = 2000u;
+    // per device: what the constants currently hold (stream-ordered updates; launches on other streams of the same device
+    // that overlap a change may see either value)
+    static uint32_t hint_set[64];
+    static int limit_set[64];
+    int dev = 0;
+    PT_CUDA(cudaGetDevice(&dev));
+    PT_REQUIRE(dev >= 0 && dev < 64, "pt_llama_decode_step: device ordinal %d outside 0..63", dev);
     const uint32_t want = ((uint32_t)a->debug >> 16) ? ((uint32_t)a->debug >> 16) : 2000u;
-    if (want != hint_set) {
+    if (want != (hint_set[dev] ? hint_set[dev] : 2000u)) {
       PT_CUDA(cudaMemcpyToSymbolAsync(mk::c_wait_hint, &want, sizeof(want), 0, cudaMemcpyHostToDevice, as_stream(stream)));
-      hint_set = want;
+      hint_set[dev] = want;
+    }
+    PT_REQUIRE(a->wait_limit >= 0, "pt_llama_decode_step: wait_limit=%d", a->wait_limit);
+    const int limit = a->wait_limit > 0 ? std::max(a->wait_limit, 256) : mk::kDefaultPollLimit;
+    if (limit != (limit_set[dev] ? limit_set[dev] : mk::kDefaultPollLimit)) {
+      PT_CUDA(cudaMemcpyToSymbolAsync(mk::c_poll_limit, &limit, sizeof(limit), 0, cudaMemcpyHostToDevice, as_stream(stream)));
+      limit_set[dev] = limit;
     }
   }
   void *kargs[] = {(void *)&p};

@@ -462,12 +462,53 @@ extern "C" size_t pt_linear_packed_bytes(int wfmt, int n_out, int k_in) {
   return (size_t)n_rt * (k_in / chunk_k(wfmt)) * tile_bytes(wfmt);
 }
 
+// Split-k workspace layout: [arrival counters, kCounterBytes][partial sums].  The counter region has ONE size for every shape,
+// so that linears of different widths can share a workspace: a narrow linear's partial sums never land where a wide one
+// expects zeroed counters.  One counter per group of 8 row tiles: 2048 counters cover n_out up to 262144.
+constexpr size_t kCounterBytes = 8192;
+constexpr int kMaxCounters = (int)(kCounterBytes / sizeof(int));
+
 extern "C" size_t pt_linear_workspace_bytes(int batch, int n_out, int max_ksplit) {
   const size_t npad = (size_t)ceil_div(n_out, 16) * 16;
-  // counters (one int per group of 8 row tiles, rounded up to 256 B) followed by the split-k partials
-  const size_t counters = ((size_t)ceil_div((int)(npad / 16), kWarps) * sizeof(int) + 255) / 256 * 256;
-  return counters + (size_t)max_ksplit * batch * npad * sizeof(float);
+  return kCounterBytes + (size_t)max_ksplit * batch * npad * sizeof(float);
 }
+
+namespace {
+// The k-split of a linear launch and the shared memory it needs; one rule for pt_linear and pt_linear_static_scratch.
+// About 24 warps per SM in total (one warp per (row tile, k-slice)); at least 8 chunks (8 KB of weights) per warp for
+// FP16 / FP8 so that the fixed cost of a warp (prologue, split-k reduction) stays small, 4 chunks for INT4, whose tiles carry
+// four times the math (both measured on B200 over the decode shapes of the supported models); and an activation slice that
+// fits shared memory next to the rings.
+struct SplitPlan { int ksplit, chunks_per_split; size_t smem; bool fits; };
+SplitPlan plan_split(int wfmt, int batch, int n_out, int k_in, int ksplit_req) {
+  const int ck = chunk_k(wfmt), n_rt = ceil_div(n_out, 16), nchunks = k_in / ck;
+  const int nb = batch <= 8 ? 1 : (batch <= 16 ? 2 : 4);
+  int ksplit = ksplit_req;
+  if (ksplit <= 0) {
+    const int want_warps = sm_count() * 24;
+    ksplit = std::max(1, want_warps / n_rt);
+    ksplit = std::max(1, std::min(ksplit, nchunks / (wfmt == PT_W_INT4 ? 4 : 8)));
+  }
+  ksplit = std::max(1, std::min(ksplit, nchunks));
+  const size_t ring_bytes = (size_t)kWarps * kRingStages * tile_bytes(wfmt);
+  const size_t smem_budget = 200 * 1024;
+  auto smem_bytes = [&](int ksp) {
+    const int cps = ceil_div(nchunks, ksp);
+    const size_t slice = (size_t)cps * ck * 2;
+    // row stride = 64 (mod 128) keeps the 8 batch rows of a quad on distinct banks
+    const size_t xs = ((size_t)batch * (slice | 64) + 127) / 128 * 128;
+    const size_t corr = wfmt == PT_W_INT4 ? ((size_t)cps * 8 * nb * sizeof(float) + 127) / 128 * 128 : 0;
+    return xs + corr + ring_bytes;
+  };
+  while (smem_bytes(ksplit) > smem_budget && ksplit < nchunks) ++ksplit;
+  SplitPlan pl;
+  pl.fits = smem_bytes(ksplit) <= smem_budget;
+  pl.chunks_per_split = ceil_div(nchunks, ksplit);
+  pl.ksplit = ceil_div(nchunks, pl.chunks_per_split);  // no empty splits
+  pl.smem = smem_bytes(pl.ksplit);
+  return pl;
+}
+}  // namespace
 
 extern "C" int pt_linear_repack(int wfmt, const void *w, const void *scale, int n_out, int k_in, int group, int interleave_rows,
                                 void *packed_w, void *stream) {
@@ -487,7 +528,7 @@ extern "C" int pt_linear_repack(int wfmt, const void *w, const void *scale, int 
   const int n_rt = ceil_div(n_out, 16);
   const int units_per_row = row_bytes(wfmt, k_in) / 16;
   const int nchunks = units_per_row / 4;
-  repack_kernel<<<148 * 8, 256, 0, as_stream(stream)>>>((const uint4 *)w, (const __half *)scale, (uint4 *)packed_w, wfmt, n_out, units_per_row,
+  repack_kernel<<<sm_count() * 8, 256, 0, as_stream(stream)>>>((const uint4 *)w, (const __half *)scale, (uint4 *)packed_w, wfmt, n_out, units_per_row,
                                                        nchunks, n_rt, interleave_rows, ngroups, group_chunks);
   PT_LAUNCH_CHECK("pt_linear_repack");
   return PT_OK;
@@ -532,42 +573,21 @@ extern "C" int pt_linear(const pt_linear_args *a, void *stream) {
   p.out_scale = 1.0f;
   if (a->wfmt == PT_W_FP8) p.out_scale = (a->w_scale > 0.f ? a->w_scale : 1.0f) * (cast ? a->act_scale : 1.0f);
 
-  // k-split: about 24 warps per SM in total (one warp per (row tile, k-slice)); at least 8 chunks (8 KB of weights) per warp
-  // for FP16 / FP8 so that the fixed cost of a warp (prologue, split-k reduction) stays small, 4 chunks for INT4, whose
-  // tiles carry four times the math (both measured on B200 over the decode shapes of the supported models); and an
-  // activation slice that fits shared memory next to the rings.
-  const int nb = a->batch <= 8 ? 1 : (a->batch <= 16 ? 2 : 4);
-  int ksplit = a->ksplit;
-  if (ksplit <= 0) {
-    const int want_warps = 148 * 24;
-    ksplit = std::max(1, want_warps / p.n_rt);
-    ksplit = std::max(1, std::min(ksplit, p.nchunks / (a->wfmt == PT_W_INT4 ? 4 : 8)));
-  }
-  ksplit = std::max(1, std::min(ksplit, p.nchunks));
-  const size_t ring_bytes = (size_t)kWarps * kRingStages * tile_bytes(a->wfmt);
-  const size_t smem_budget = 200 * 1024;
-  auto smem_bytes = [&](int ksp) {
-    const int cps = ceil_div(p.nchunks, ksp);
-    const size_t slice = (size_t)cps * ck * 2;
-    // row stride = 64 (mod 128) keeps the 8 batch rows of a quad on distinct banks
-    const size_t xs = ((size_t)a->batch * (slice | 64) + 127) / 128 * 128;
-    const size_t corr = a->wfmt == PT_W_INT4 ? ((size_t)cps * 8 * nb * sizeof(float) + 127) / 128 * 128 : 0;
-    return xs + corr + ring_bytes;
-  };
-  while (smem_bytes(ksplit) > smem_budget && ksplit < p.nchunks) ++ksplit;
-  PT_REQUIRE(smem_bytes(ksplit) <= smem_budget, "pt_linear: activation slice does not fit shared memory (batch=%d k=%d)", a->batch, a->k_in);
-  p.chunks_per_split = ceil_div(p.nchunks, ksplit);
-  p.ksplit = ceil_div(p.nchunks, p.chunks_per_split);  // no empty splits
+  const SplitPlan plan = plan_split(a->wfmt, a->batch, a->n_out, a->k_in, a->ksplit);
+  PT_REQUIRE(plan.fits, "pt_linear: activation slice does not fit shared memory (batch=%d k=%d)", a->batch, a->k_in);
+  p.chunks_per_split = plan.chunks_per_split;
+  p.ksplit = plan.ksplit;
   p.xs_stride = (int)(((size_t)p.chunks_per_split * ck * 2) | 64);
   if (p.ksplit > 1) {
     const size_t need = pt_linear_workspace_bytes(a->batch, a->n_out, p.ksplit);
     PT_REQUIRE(a->workspace && a->workspace_bytes >= need, "pt_linear: split-k=%d needs %zu workspace bytes, got %zu", p.ksplit, need,
                a->workspace_bytes);
-    const size_t counters = ((size_t)ceil_div(p.n_rt, kWarps) * sizeof(int) + 255) / 256 * 256;
+    PT_REQUIRE(ceil_div(p.n_rt, kWarps) <= kMaxCounters, "pt_linear: n_out=%d exceeds the %d arrival counters of a split-k workspace", a->n_out,
+               kMaxCounters);
     p.counters = (int *)a->workspace;
-    p.partial = (float *)((char *)a->workspace + counters);
+    p.partial = (float *)((char *)a->workspace + kCounterBytes);
   }
-  const size_t smem = smem_bytes(p.ksplit);
+  const size_t smem = plan.smem;
   cudaStream_t st = as_stream(stream);
   switch (a->wfmt) {
     case PT_W_INT4: return dispatch_nb<PT_W_INT4>(p, smem, st);
@@ -601,27 +621,22 @@ extern "C" int pt_linear_static_scratch(const pt_linear_args *a, void *stream) {
   const int ck = chunk_k(a->wfmt == PT_W_INT4 || a->wfmt == PT_W_FP16 || a->wfmt == PT_W_FP8 ? a->wfmt : PT_W_FP16);
   PT_REQUIRE(a->batch >= 1 && a->n_out > 0 && a->k_in > 0 && a->k_in % ck == 0, "pt_linear_static_scratch: bad shape batch=%d n_out=%d k_in=%d",
              a->batch, a->n_out, a->k_in);
-  // Fix the k-split here (same rule as pt_linear's default) so that the scratch need is known before the launch.
-  const int n_rt = ceil_div(a->n_out, 16), nchunks = a->k_in / ck;
-  int ksplit = a->ksplit;
-  if (ksplit <= 0) {
-    ksplit = std::max(1, (148 * 24) / n_rt);
-    ksplit = std::max(1, std::min(ksplit, nchunks / 4));
-  }
-  ksplit = std::max(1, std::min(ksplit, nchunks));
-  const size_t need = ksplit > 1 ? pt_linear_workspace_bytes(a->batch, a->n_out, ksplit) : 0;
+  PT_REQUIRE(a->batch <= 32, "pt_linear_static_scratch: batch=%d outside 1..32", a->batch);
+  // The split pt_linear will settle on (one rule, shared with it), so that the scratch need is known before the launch.
+  const SplitPlan plan = plan_split(a->wfmt, a->batch, a->n_out, a->k_in, a->ksplit);
+  PT_REQUIRE(plan.fits, "pt_linear_static_scratch: activation slice does not fit shared memory (batch=%d k=%d)", a->batch, a->k_in);
+  const size_t need = plan.ksplit > 1 ? pt_linear_workspace_bytes(a->batch, a->n_out, plan.ksplit) : 0;
   PT_REQUIRE(need <= kStaticWsBytes,
              "pt_linear_static_scratch: batch=%d n_out=%d k-split=%d needs %zu bytes of scratch, the built-in scratch holds %zu; use pt_linear "
              "with a caller-provided workspace",
-             a->batch, a->n_out, ksplit, need, (size_t)kStaticWsBytes);
+             a->batch, a->n_out, plan.ksplit, need, (size_t)kStaticWsBytes);
   pt_linear_args b = *a;
-  b.ksplit = ksplit;
+  b.ksplit = plan.ksplit;
   b.workspace = ws_of_device[dev];
   b.workspace_bytes = kStaticWsBytes;
-  if (ksplit > 1) {
+  if (plan.ksplit > 1) {
     // The array keeps whatever the previous call left; the arrival counters at its start must be zero.
-    const size_t counters = ((size_t)ceil_div(n_rt, kWarps) * sizeof(int) + 255) / 256 * 256;
-    PT_CUDA(cudaMemsetAsync(ws_of_device[dev], 0, counters, as_stream(stream)));
+    PT_CUDA(cudaMemsetAsync(ws_of_device[dev], 0, kCounterBytes, as_stream(stream)));
   }
   return pt_linear(&b, stream);
 }

@@ -403,12 +403,23 @@ __global__ void rwkv_act_kernel(int mode, const __half *__restrict__ a, const __
 __global__ void embedding_kernel(const uint4 *__restrict__ table, const int *__restrict__ ids, int ids_stride, const int *step_dev,
                                  int dim8, int vocab, uint4 *__restrict__ out) {
   const int b = blockIdx.x;
-  int id = ids[(size_t)b * ids_stride + (step_dev ? *step_dev : 0)];
+  const int step = step_dev ? min(max(*step_dev, 0), ids_stride - 1) : 0;  // a step past the container reads its last column
+  int id = ids[(size_t)b * ids_stride + step];
   id = min(max(id, 0), vocab - 1);
   for (int i = threadIdx.x; i < dim8; i += blockDim.x) out[(size_t)b * dim8 + i] = table[(size_t)id * dim8 + i];
 }
 __global__ void step_containers_kernel(int *ids, int batch, int max_len, int *step_dev, const int *next_ids, int pad_id, int eos_id,
-                                       int *stop_mask) {
+                                       int *stop_mask, int *done_flag) {
+  __shared__ int s_running;
+  if (done_flag) {
+    if (*done_flag) return;   // uniform: every thread reads the same word
+    if (threadIdx.x == 0) s_running = 0;
+    __syncthreads();
+    // keep_going = sum(stop_mask) < batch on the mask BEFORE this iteration's update (models/base_model.py:348-352)
+    for (int b = threadIdx.x; b < batch; b += blockDim.x)
+      if (!stop_mask[b]) atomicAdd(&s_running, 1);
+    __syncthreads();
+  }
   const int nxt = *step_dev + 1;
   for (int b = threadIdx.x; b < batch; b += blockDim.x) {
     if (nxt < max_len) {
@@ -419,7 +430,10 @@ __global__ void step_containers_kernel(int *ids, int batch, int max_len, int *st
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) *step_dev = nxt;
+  if (threadIdx.x == 0) {
+    *step_dev = nxt;
+    if (done_flag && s_running == 0) *done_flag = 1;
+  }
 }
 __global__ void add_f16_kernel(const __half *__restrict__ a, const __half *__restrict__ b, size_t n, __half *__restrict__ out) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = h_add(a[i], b[i]);
@@ -427,7 +441,7 @@ __global__ void add_f16_kernel(const __half *__restrict__ a, const __half *__res
 
 static inline int grid_for(size_t n, int block = 256) {
   size_t g = (n + block - 1) / block;
-  const size_t cap = 148 * 8;
+  const size_t cap = (size_t)sm_count() * 8;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
@@ -632,8 +646,17 @@ extern "C" int pt_step_containers(int32_t *ids, int batch, int max_len, int32_t 
                                   int32_t *stop_mask, void *stream) {
   PT_REQUIRE(ids && step_dev && next_ids, "pt_step_containers: null pointer argument");
   PT_REQUIRE(batch > 0 && max_len > 0, "pt_step_containers: bad shape");
-  step_containers_kernel<<<1, 128, 0, as_stream(stream)>>>(ids, batch, max_len, step_dev, next_ids, pad_id, eos_id, stop_mask);
+  step_containers_kernel<<<1, 128, 0, as_stream(stream)>>>(ids, batch, max_len, step_dev, next_ids, pad_id, eos_id, stop_mask, nullptr);
   PT_LAUNCH_CHECK("pt_step_containers");
+  return PT_OK;
+}
+
+extern "C" int pt_step_containers_early_stop(int32_t *ids, int batch, int max_len, int32_t *step_dev, const int32_t *next_ids, int pad_id,
+                                             int eos_id, int32_t *stop_mask, int32_t *done_flag, void *stream) {
+  PT_REQUIRE(ids && step_dev && next_ids && stop_mask && done_flag, "pt_step_containers_early_stop: null pointer argument");
+  PT_REQUIRE(batch > 0 && max_len > 0, "pt_step_containers_early_stop: bad shape");
+  step_containers_kernel<<<1, 128, 0, as_stream(stream)>>>(ids, batch, max_len, step_dev, next_ids, pad_id, eos_id, stop_mask, done_flag);
+  PT_LAUNCH_CHECK("pt_step_containers_early_stop");
   return PT_OK;
 }
 

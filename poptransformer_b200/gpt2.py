@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from . import ops
+from .loop import DecodeLoop
 from .tp import fused_qkv_rows, rows, vocab_rows
 
 
@@ -35,9 +36,9 @@ class GPT2Config:
         self.head_dim = d_model // n_head
 
 
-class GPT2Decoder:
+class GPT2Decoder(DecodeLoop):
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None,
-                 spare_pages=0, pdl_linear=None, pdl_attn=None):
+                 spare_pages=0, pdl_linear=None, pdl_attn=None, early_stop=False):
         c = cfg
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         self.pdl_linear = pdl_default(batch)[0] if pdl_linear is None else int(pdl_linear)
@@ -52,6 +53,7 @@ class GPT2Decoder:
         self.cfg, self.batch, self.device = cfg, batch, device
         self.pad_id = c.vocab - 1 if pad_id is None else pad_id
         self.eos_id = eos_id
+        self._init_loop(device, early_stop)
         dev = device
         t = lambda k: state_dict[k].to(dev).to(torch.float16).contiguous()
         self.wte, self.wpe = t("transformer.wte.weight"), t("transformer.wpe.weight")
@@ -153,7 +155,7 @@ class GPT2Decoder:
                                  ops._stream()), "topk")
         else:
             ops.lm_head_tp_merge(self)
-        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
+        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask, done_flag=self._loop_done_flag())
 
     def capture(self):
         saved = (self.ids.clone(), self.step_t.clone())
@@ -184,15 +186,6 @@ class GPT2Decoder:
         else:
             self.enqueue_step()
 
-    def run(self, input_ids, max_loop=None):
-        """Session.run analogue (poptransformer/sessions.py:47-49): returns the anchors {'Loop:0': ids, 'Loop:1': step}."""
-        self.reset(input_ids)
-        for _ in range(self.cfg.max_len if max_loop is None else max_loop):
-            self.step()
-        torch.cuda.synchronize()
-        if int(self.error_flag.item()) != 0:
-            raise ops.PtError("a bounded device-side wait gave up")
-        return {"Loop:0": self.ids.cpu().numpy(), "Loop:1": self.step_t.cpu().numpy()}
 
 
 class GPT2BeamDecoder(GPT2Decoder):

@@ -25,6 +25,7 @@ import numpy as np
 import torch
 
 from . import ops
+from .loop import DecodeLoop
 
 
 class LlamaConfig:
@@ -48,10 +49,16 @@ def rope_tables(max_len, head_dim, device):
 from .tp import KSlice as _KSlice, rows as _rows, row_parallel_int4, row_parallel_fp16  # noqa: E402
 
 
-class LlamaDecoder:
+class LlamaDecoder(DecodeLoop):
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, fuse_norm=None, pad_id=None, eos_id=-1,
-                 tp_rank=0, tp_size=1, group=None, pdl=True, persistent=None, keep_logits=True):
+                 tp_rank=0, tp_size=1, group=None, pdl=True, persistent=None, keep_logits=True, early_stop=False, tp_buffers=None,
+                 wait_limit=0):
+        """tp_buffers: for tp_size > 1, the exchange buffers of all ranks as this process sees them (a list of tp_size int32 CUDA
+        tensors of pt_llama_tp_buffer_bytes each, entry tp_rank being local memory, the others peer mappings the caller set up).
+        Default: the buffers are allocated as symmetric memory over `group` (torch.distributed).
+        wait_limit: trip limit of the persistent kernel's polling loops (0 = the library default, about two seconds)."""
         self.cfg, self.batch, self.device = cfg, batch, device
+        self._init_loop(device, early_stop)
         self.tp, self.rank, self.group = tp_size, tp_rank, group
         self.pdl = 1 if pdl else 0
         c = cfg
@@ -180,23 +187,32 @@ class LlamaDecoder:
                            for n in ((2 if tp > 1 else 1) * d, 3 * self.d_loc, self.d_loc, self.down_ks.width)]
             a.x, a.qkv, a.attn, a.act = (t.data_ptr() for t in self.mk_act)
             if tp > 1:
-                # exchange buffer for the fused all-reduces: symmetric memory, every rank maps every rank's buffer; plain peer
-                # loads / stores only (no multicast object is requested)
-                import torch.distributed._symmetric_memory as symm_mem
                 nbytes = L.pt_llama_tp_buffer_bytes(B, d, tp)
-                grp = group if group is not None else torch.distributed.group.WORLD
-                self.tp_buf = symm_mem.empty((nbytes + 3) // 4, dtype=torch.int32, device=dev)
-                self.tp_buf.zero_()
-                self.tp_hdl = symm_mem.rendezvous(self.tp_buf, grp)
                 a.tp_size, a.tp_rank = tp, r
                 a.ffn_offset, a.ffn_valid, a.vocab_offset, a.emb_rows = self.down_ks.offset, self.f_loc, r * self.vocab_loc, c.vocab
-                for i in range(tp):
-                    a.tp_buffers[i] = int(self.tp_hdl.buffer_ptrs[i])
-                torch.cuda.synchronize()
-                torch.distributed.barrier(group=grp)
+                if tp_buffers is not None:
+                    if len(tp_buffers) != tp or any(b.numel() * b.element_size() < nbytes for b in tp_buffers):
+                        raise ops.PtError(f"tp_buffers: need {tp} buffers of at least {nbytes} bytes")
+                    self.tp_bufs = list(tp_buffers)
+                    for i in range(tp):
+                        a.tp_buffers[i] = self.tp_bufs[i].data_ptr()
+                else:
+                    # exchange buffer for the fused all-reduces: symmetric memory, every rank maps every rank's buffer; plain peer
+                    # loads / stores only (no multicast object is requested)
+                    import torch.distributed._symmetric_memory as symm_mem
+                    grp = group if group is not None else torch.distributed.group.WORLD
+                    self.tp_buf = symm_mem.empty((nbytes + 3) // 4, dtype=torch.int32, device=dev)
+                    self.tp_buf.zero_()
+                    self.tp_hdl = symm_mem.rendezvous(self.tp_buf, grp)
+                    for i in range(tp):
+                        a.tp_buffers[i] = int(self.tp_hdl.buffer_ptrs[i])
+                    torch.cuda.synchronize()
+                    torch.distributed.barrier(group=grp)
             a.logits = self.logits.data_ptr() if keep_logits else None
             a.workspace, a.workspace_bytes = self.mk_ws.data_ptr(), self.mk_ws.numel()
             a.error_flag = self.error_flag.data_ptr()
+            a.done_flag = self.done_flag.data_ptr() if self.early_stop else None
+            a.wait_limit = int(wait_limit)
             self.mk_args = a
         torch.cuda.synchronize()
 
@@ -269,7 +285,7 @@ class LlamaDecoder:
                                  ops._stream()), "topk")
         else:
             ops.lm_head_tp_merge(self)
-        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
+        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask, done_flag=self._loop_done_flag())
 
     def _norm_linear_raw(self, x, gamma, pl, out_ptr, out_ld):
         """gate|up linear with the SwiGLU epilogue writing at a column offset of the (zero-padded) activation buffer."""
@@ -324,17 +340,3 @@ class LlamaDecoder:
             self.graph.replay()
         else:
             self.enqueue_step()
-
-    def run(self, input_ids, max_loop=None):
-        """Session.run equivalent (poptransformer/sessions.py:47-49): feeds the id container, runs `max_loop`
-        loop iterations on the device and returns the reference's anchors {'Loop:0': ids, 'Loop:1': step}."""
-        n = self.cfg.max_len if max_loop is None else max_loop
-        if n > self.cfg.max_len:
-            raise ops.PtError(f"max_loop={n} exceeds max_length={self.cfg.max_len}")
-        self.reset(input_ids)
-        for _ in range(n):
-            self.step()
-        out = {"Loop:0": self.ids.cpu().numpy(), "Loop:1": self.step_t.cpu().numpy()}
-        if int(self.error_flag.item()) != 0:
-            raise ops.PtError("a bounded device-side wait gave up during decode (error flag set)")
-        return out

@@ -12,7 +12,6 @@ Reference op            -> function here
   FP8MatMul...          -> fp8_matmul
   BeamSearch            -> beam_search
   Remap                 -> remap_tensor        (layout hint on IPU; identity here)
-  ReplicatedAllGather   -> replicated_allgather (NCCL all-gather over the TP group)
 plus the fused decode stages that replace chains of reference ops: PackedLinear / linear,
 rms_norm, kv_append_attn, topk, embedding, step_containers, wkv.
 """
@@ -224,6 +223,7 @@ class PagedKVCache:
 
     def __init__(self, rows, n_kv, head_dim, max_len, page_size=64, device="cuda", page_table=None, extra_pages=0):
         self.rows, self.n_kv, self.head_dim, self.page_size = rows, n_kv, head_dim, page_size
+        self.max_len = max_len
         self.max_pages = (max_len + page_size - 1) // page_size
         n_pages = rows * self.max_pages + extra_pages
         self.pool = torch.zeros((n_pages, 2, n_kv, page_size, head_dim), dtype=torch.float16, device=device)
@@ -254,6 +254,7 @@ def attn_args(qkv, step, cache, out, n_head, rope_mode, softmax_mode, score_scal
     a.workspace, a.workspace_bytes = _ptr(workspace), workspace.numel()
     a.error_flag = _ptr(error_flag)
     a.pdl = pdl
+    a.max_len = cache.max_len
     return a
 
 
@@ -302,17 +303,28 @@ def beam_search(logits, hyp_container, prob_container, step, beam_size, parent=N
 
 
 # ------------------------------------------------------------------------------------------ FP8
+def _require_e4m3(op, fp8_format):
+    """The reference's formats are Graphcore's F143 / F152 (exponent bias and range differ from OCP E4M3, the arithmetic is
+    closed): bytes in those formats would decode to other values here, so they are refused instead of silently misread."""
+    if fp8_format in ("F143", "F152"):
+        raise PtError(f"{op}: Graphcore {fp8_format} bytes are not OCP E4M3 and are not supported; re-quantise the fp16/fp32 tensor "
+                      "with poptransformer_b200.quant.quantize_fp8 (E4M3, per-tensor scale amax/448)")
+    if fp8_format != "E4M3":
+        raise PtError(f"{op}: unsupported format {fp8_format}")
+
+
 def half_to_uint8(x, fp8_scale, fp8_format="E4M3"):
     """ops.half_to_uint8 (customized.py:127-135) with OCP E4M3 and a float per-tensor scale."""
-    if fp8_format not in ("E4M3", "F143"):
-        raise PtError(f"CastToUint8: unsupported format {fp8_format}")
+    _require_e4m3("CastToUint8", fp8_format)
     out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
     check(_lib.lib().pt_cast_fp8(_ptr(x), float(fp8_scale), x.numel(), _ptr(out), _stream()), "CastToUint8")
     return out
 
 
-def fp8_matmul(input_l, input_r, fp8_scale_lhs, fp8_scale_rhs):
+def fp8_matmul(input_l, input_r, fp8_scale_lhs, fp8_scale_rhs, fp8_format_lhs="E4M3", fp8_format_rhs="E4M3"):
     """ops.fp8_matmul (customized.py:137-148): input_l e4m3 [m, k], input_r e4m3 [n, k] (k contiguous) -> fp16 [m, n]."""
+    _require_e4m3("FP8MatMul", fp8_format_lhs)
+    _require_e4m3("FP8MatMul", fp8_format_rhs)
     m, k = input_l.shape
     n = input_r.shape[0]
     out = torch.empty((m, n), dtype=torch.float16, device=input_l.device)
@@ -340,10 +352,17 @@ def embedding(table, ids, step=None, out=None):
     return out
 
 
-def step_containers(ids, step, next_ids, pad_id, eos_id=-1, stop_mask=None):
+def step_containers(ids, step, next_ids, pad_id, eos_id=-1, stop_mask=None, done_flag=None):
+    """step_containers + step_loop_cond (models/base_model.py:313-355).  With `done_flag` (device int32, zeroed per generation)
+    the reference's early stop applies: the flag is set by the iteration that found every sequence already stopped, and the
+    calls after it change nothing."""
     batch, max_len = ids.shape
-    check(_lib.lib().pt_step_containers(_ptr(ids), batch, max_len, _ptr(step), _ptr(next_ids), int(pad_id), int(eos_id), _ptr(stop_mask),
-                                        _stream()), "pt_step_containers")
+    if done_flag is None:
+        check(_lib.lib().pt_step_containers(_ptr(ids), batch, max_len, _ptr(step), _ptr(next_ids), int(pad_id), int(eos_id), _ptr(stop_mask),
+                                            _stream()), "pt_step_containers")
+    else:
+        check(_lib.lib().pt_step_containers_early_stop(_ptr(ids), batch, max_len, _ptr(step), _ptr(next_ids), int(pad_id), int(eos_id),
+                                                       _ptr(stop_mask), _ptr(done_flag), _stream()), "pt_step_containers_early_stop")
 
 
 def lm_head_tp_merge(dec):

@@ -16,6 +16,7 @@ import ctypes
 import torch
 
 from . import ops
+from .loop import DecodeLoop
 from .tp import rows, vocab_rows
 
 
@@ -29,8 +30,8 @@ class RWKVConfig:
             n_layer, d_model, ffn, vocab, max_len, rescale_every, eps)
 
 
-class RWKVDecoder:
-    def __init__(self, cfg, state_dict, batch, device="cuda", pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None, pdl_linear=None):
+class RWKVDecoder(DecodeLoop):
+    def __init__(self, cfg, state_dict, batch, device="cuda", pad_id=None, eos_id=-1, tp_rank=0, tp_size=1, group=None, pdl_linear=None, early_stop=False):
         c = cfg
         self.pdl_linear = PDL_DEFAULT if pdl_linear is None else int(pdl_linear)
         self.tp, self.rank, self.group = tp_size, tp_rank, group
@@ -42,6 +43,7 @@ class RWKVDecoder:
         self.cfg, self.batch, self.device = cfg, batch, device
         self.pad_id = c.vocab - 1 if pad_id is None else pad_id
         self.eos_id = eos_id
+        self._init_loop(device, early_stop)
         dev = device
         h = lambda k: state_dict[k].to(dev).to(torch.float16).reshape(-1).contiguous()
         f = lambda k: state_dict[k].to(dev).to(torch.float32).reshape(-1)[r * dl:(r + 1) * dl].contiguous()   # sharded with the channels
@@ -180,7 +182,7 @@ class RWKVDecoder:
             ops.check(L_.pt_topk(P(self.logits), B, c.vocab, 1, 0, P(self.next_val), P(self.next_ids), S()), "topk")
         else:
             ops.lm_head_tp_merge(self)
-        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask)
+        ops.step_containers(self.ids, self.step_t, self.next_ids, self.pad_id, self.eos_id, self.stop_mask, done_flag=self._loop_done_flag())
 
     def reset(self, input_ids):
         self.ids.copy_(torch.as_tensor(input_ids, dtype=torch.int32).to(self.device))
@@ -192,12 +194,3 @@ class RWKVDecoder:
     def step(self):
         self.enqueue_step()
 
-    def run(self, input_ids, max_loop=None):
-        """Session.run analogue (poptransformer/sessions.py:47-49): returns the anchors {'Loop:0': ids, 'Loop:1': step}."""
-        self.reset(input_ids)
-        for _ in range(self.cfg.max_len if max_loop is None else max_loop):
-            self.step()
-        torch.cuda.synchronize()
-        if int(self.error_flag.item()) != 0:
-            raise ops.PtError("a bounded device-side wait gave up")
-        return {"Loop:0": self.ids.cpu().numpy(), "Loop:1": self.step_t.cpu().numpy()}

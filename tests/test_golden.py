@@ -49,12 +49,21 @@ def test_cuda_reproduces_reference_token_stream(path, cuda):
     got, exp = out["Loop:0"], z["output_ids"]
     assert int(out["Loop:1"][0]) == max_len - 1
     assert np.array_equal(got[:, :prompt], exp[:, :prompt])
-    # fp32 accumulation order differs from numpy's, so a stream may leave the reference's at a numerical tie and never
-    # return; require most of every row to agree and the first generated tokens to be identical
+    # fp32 accumulation order differs from numpy's, so a row may leave the reference's stream, but only at a position where
+    # the oracle's two best logits (given the reference's history) are closer than the logit tolerance; and most positions agree
+    cfg = llama_np.LlamaConfig(**dims, max_len=max_len, group=0)
+    sd_np = {k: (v.numpy().reshape(-1) if k.endswith("_scale") else v.numpy()) for k, v in sd.items()}
+    orc = llama_np.LlamaOracle(cfg, sd_np, batch)
+    orc.reset()
+    logits = [orc.logits(exp[:, t], t)[0].astype(np.float32) for t in range(max_len - 1)]
     for b in range(batch):
         diff = np.nonzero(got[b] != exp[b])[0]
-        first = int(diff[0]) if diff.size else max_len
-        assert first >= prompt + 4, f"row {b} diverges from the reference stream already at position {first}"
+        if diff.size:
+            t = int(diff[0])
+            assert t >= prompt, f"row {b}: prompt position {t} changed"
+            top2 = np.sort(logits[t - 1][b])[-2:]
+            assert top2[1] - top2[0] <= 2e-2, f"row {b}: leaves the reference stream at {t} with margin {top2[1] - top2[0]}"
+    assert (got == exp).mean() >= 0.9
 
 
 # ------------------------------------------------------------------ GPT-2 / ChatGLM2 / RWKV: the reference's model classes, fp16

@@ -81,3 +81,72 @@ def test_run_twice_is_deterministic(cuda):
     a = dec.run(ids)["Loop:0"].copy()
     b = dec.run(ids)["Loop:0"].copy()
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("persistent", [True, False])
+def test_early_stop_ends_where_the_reference_loop_ends(cuda, persistent):
+    """early_stop (models/base_model.py:348-352): keep_going is evaluated on the stop mask as it was before an iteration's own
+    update, so the loop body runs once more after the iteration that produced the last eos id.  With the eos id first
+    generated for position p the final state is step = p + 1, position p + 1 written, everything after it still padding."""
+    from poptransformer_b200 import llama, synth
+    batch, max_len, prompt = 1, 48, 6
+    sd = synth.llama_state_dict(**TINY, seed=7, device="cpu", int4_group=128)
+    cfg = llama.LlamaConfig(**TINY, max_len=max_len, int4_group=128)
+    ids = synth.prompt_ids(batch, prompt, max_len, TINY["vocab"], TINY["vocab"] - 1, seed=8)
+    free = llama.LlamaDecoder(cfg, sd, batch, device=cuda, persistent=persistent)
+    full = free.run(ids, max_loop=max_len)["Loop:0"]
+    p = prompt + 9
+    eos = int(full[0, p])
+    first = int(np.nonzero(full[0, prompt:] == eos)[0][0]) + prompt      # the id may occur earlier in the stream
+    dec = llama.LlamaDecoder(cfg, sd, batch, device=cuda, persistent=persistent, eos_id=eos, early_stop=True)
+    out = dec.run(ids, max_loop=max_len, poll_every=4)
+    got = out["Loop:0"]
+    assert int(out["Loop:1"][0]) == first + 1
+    assert np.array_equal(got[0, :first + 2], full[0, :first + 2])
+    assert (got[0, first + 2:] == dec.pad_id).all()
+    assert int(dec.stop_mask.item()) == 1 and int(dec.done_flag.item()) == 1
+    # without early_stop the same eos id only sets the stop mask: the loop runs to the end, like the reference's
+    plain = llama.LlamaDecoder(cfg, sd, batch, device=cuda, persistent=persistent, eos_id=eos)
+    out = plain.run(ids, max_loop=max_len)
+    assert int(out["Loop:1"][0]) == max_len and np.array_equal(out["Loop:0"], full) and int(plain.stop_mask.item()) == 1
+
+
+def test_bounded_wait_runs_out_and_is_reported(cuda):
+    """A tensor-parallel step whose second rank never shows up: rank 0 of a tp_size = 2 configuration is launched alone, with
+    a local buffer standing in for the absent rank's exchange buffer, so nothing ever writes rank 1's arrival counter.  The
+    kernel's wait for it must run out (short limit), set the error flag to the staging wait's code, and return; the host call
+    must raise; and the device must stay usable."""
+    from poptransformer_b200 import _lib, llama, ops, synth
+    batch, max_len = 1, 32
+    sd = synth.llama_state_dict(**TINY, seed=9, device="cpu", int4_group=128)
+    cfg = llama.LlamaConfig(**TINY, max_len=max_len, int4_group=128)
+    nbytes = _lib.lib().pt_llama_tp_buffer_bytes(batch, TINY["d_model"], 2)
+    bufs = [torch.zeros((nbytes + 3) // 4, dtype=torch.int32, device=cuda) for _ in range(2)]
+    dec = llama.LlamaDecoder(cfg, sd, batch, device=cuda, tp_rank=0, tp_size=2, tp_buffers=bufs, persistent=True, wait_limit=4096)
+    assert dec.persistent
+    ids = synth.prompt_ids(batch, 4, max_len, TINY["vocab"], dec.pad_id, seed=1)
+    with pytest.raises(ops.PtError, match="error flag 10"):
+        dec.run(ids, max_loop=1)
+    assert int(dec.error_flag.item()) == 10
+    assert int(dec.step_t.item()) == 0                    # the failed iteration did not advance the loop
+    # the context is intact: an ordinary decoder still runs, and the default limit is back in force for it
+    ok = llama.LlamaDecoder(cfg, sd, batch, device=cuda, persistent=True)
+    assert int(ok.run(ids, max_loop=8)["Loop:1"][0]) == 8
+
+
+def test_step_past_the_container_is_refused_on_the_device(cuda):
+    """A launch with step >= max_len has no position left (id container, RoPE tables, page table): both paths set error flag 12
+    instead of reading past their tables, and change nothing."""
+    from poptransformer_b200 import ops, synth
+    for persistent in (True, False):
+        dec, _ = _setup(cuda, 1, 24, 128, persistent=persistent)
+        ids = synth.prompt_ids(1, 4, 24, TINY["vocab"], dec.pad_id, seed=1)
+        dec.run(ids, max_loop=24)
+        with pytest.raises(ops.PtError):
+            dec.run(ids, max_loop=25)
+        dec.step_t.fill_(24)
+        before = dec.ids.clone()
+        dec.step()
+        torch.cuda.synchronize()
+        assert int(dec.error_flag.item()) == 12
+        assert torch.equal(dec.ids, before)

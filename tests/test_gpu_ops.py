@@ -76,7 +76,36 @@ def test_linear_int4(cuda, batch, n, k, group):
         got = ops.linear(dev(x, cuda), pl, workspace=ws, ksplit=ksplit).cpu().numpy().astype(np.float32)
         # exact fp16 products, fp32 accumulation in a different order than numpy: tiny relative error + fp16 output rounding
         np.testing.assert_allclose(got, exp.astype(np.float16).astype(np.float32), rtol=2e-3, atol=2e-3 * np.abs(exp).max())
-    assert torch.count_nonzero(ws[:256]).item() == 0, "split-k counters must return to zero"
+    assert torch.count_nonzero(ws[:8192]).item() == 0, "split-k counters must return to zero"
+
+
+def test_linear_shared_workspace_across_widths(cuda):
+    """One split-k workspace serves linears of different widths, as the decoders use it: a narrow linear (its partial sums start
+    right behind the counter region) followed by wide ones whose row groups need more counters than a 256-byte region held,
+    twice in a row.  Shapes: o_proj-like 4096 x 4096, then 16384 and 22016 (Llama-7B gate|up) and 27392 (ChatGLM2-6B gate|up)
+    output rows.  Every output row must be written (none stale) and match the oracle's dequantised-weight matmul."""
+    from poptransformer_b200 import ops
+    r = rng(31)
+    k, batch = 4096, 4
+    x = r.standard_normal((batch, k)).astype(np.float16)
+    widths = (4096, 16384, 22016, 27392)
+    ws = ops.linear_workspace(batch, max(widths), 16, cuda)
+    layers = []
+    for n in widths:
+        packed = r.integers(-128, 128, size=(n, k // 2), dtype=np.int8)
+        scale = (r.random((n, k // 128), dtype=np.float32) * 0.004 + 0.004).astype(np.float16)
+        wt = O.int4_to_half(packed, scale, axis=1, group=128)
+        layers.append((ops.PackedLinear(ops.W_INT4, dev(packed, cuda), dev(scale, cuda), group=128), _lin_ref(x, wt)))
+    xd = dev(x, cuda)
+    for rep in range(2):
+        for (pl, exp), n in zip(layers, widths):
+            out = torch.full((batch, n), float("nan"), dtype=torch.float16, device=cuda)
+            ops.linear(xd, pl, out, workspace=ws, ksplit=4)
+            got = out.cpu().numpy().astype(np.float32)
+            assert np.isfinite(got).all(), f"rep {rep} n_out {n}: rows left unwritten"
+            np.testing.assert_allclose(got, exp.astype(np.float16).astype(np.float32), rtol=2e-3, atol=2e-3 * np.abs(exp).max(),
+                                       err_msg=f"rep {rep} n_out {n}")
+    assert torch.count_nonzero(ws[:8192]).item() == 0
 
 
 @pytest.mark.parametrize("batch,n,k", [(1, 32000, 512), (4, 50257, 768), (2, 100, 1600), (16, 300, 64)])
