@@ -264,9 +264,9 @@ typedef struct pt_llama_step_args {
    * the reference's keep_going condition) sets it after finishing, and every later launch returns at once without touching
    * ids, step or the caches, so the host may poll it every few steps and still read the reference's final state. */
   int32_t *done_flag;
-  /* Trip limit of the kernel's polling loops on global memory (one trip = one L2 / NVLink round trip); 0 = default (about two
-   * seconds).  A wait that runs out sets error_flag, and the launch still terminates.  Applies to the device it is set on until
-   * changed. */
+  /* 0: the kernel's polling loops on global memory give up after about two seconds (2^21 trips of one L2 / NVLink round trip);
+   * non-zero: the short-wait build of the kernel is launched, which gives up after 2^12 trips (a few milliseconds).  A wait
+   * that runs out sets error_flag, and the launch still terminates. */
   int wait_limit;
 } pt_llama_step_args;
 

@@ -26,8 +26,17 @@
 
 #include "tile_math.cuh"
 
+// This file is compiled twice: as itself, and included by decode_llama_short.cu with PT_MK_SHORT_VARIANT defined, which builds
+// the same kernel in namespace mk_short with the short poll limit and only a launcher around it.
+#ifdef PT_MK_SHORT_VARIANT
+#define PT_MK_NS mk_short
+#define PT_MK_POLL_LIMIT kShortPollLimit
+#else
+#define PT_MK_NS mk
+#endif
+
 namespace pt {
-namespace mk {
+namespace PT_MK_NS {
 
 #ifndef PT_MK_WARPS
 #define PT_MK_WARPS 16
@@ -96,8 +105,13 @@ __constant__ uint32_t c_wait_hint = 2000u;  // suspend-time hint (ns) of the mba
 // Trip limit of every polling loop on global memory (progress words, tagged words, arrival counters); one trip is one L2 or
 // NVLink round trip, so the default gives a waiter about two seconds before it gives up and raises the error flag.
 constexpr int kDefaultPollLimit = 1 << 21;
-__constant__ int c_poll_limit = kDefaultPollLimit;
-#define POLL_LIMIT c_poll_limit
+constexpr int kShortPollLimit = 1 << 12;   // the short-wait build of the kernel (pt_llama_step_args.wait_limit != 0): a few milliseconds
+// The limit is a compile-time constant of each kernel instantiation: a run-time bound costs the polling loops a register, and
+// this kernel has none to spare (measured: 2 % of the step).
+#ifndef PT_MK_POLL_LIMIT
+#define PT_MK_POLL_LIMIT kDefaultPollLimit
+#endif
+constexpr int POLL_LIMIT = PT_MK_POLL_LIMIT;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int *abort_flag) {
   const uint32_t hint = c_wait_hint;
   for (int it = 0; it < (1 << 18); ++it) {
@@ -691,7 +705,7 @@ struct TileRegs { uint4 a, b; uint32_t s; };
 // needs: two AND per packed word and one integer mma per 512 weights (INT4), operands and accumulator initialisers that
 // arrive from shared memory in fragment order, ring positions advanced without divisions.
 #ifdef PT_MK_TRACE_WAITS
-constexpr bool NOMATH = true;   // diagnostics build: bit 0 of `debug` skips the tile math (bit 1 the tile loads too), waits are timed
+constexpr bool NOMATH = true;   // diagnostics build: bit 0 of `debug` skips the tile math, waits are timed
 constexpr int TRS = 64;         // trace slots per (SM, layer)
 #else
 constexpr bool NOMATH = false;
@@ -722,24 +736,26 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int mat, int nchunks, Best 
   float ssq = 0.f;   // sum of squares of the x values this lane's epilogues write (residual phases)
   const uint32_t ring_s = smem_addr(c.ring) + warp * TILE + lane * 16;
   const uint32_t full_s = smem_addr(&c.sh->full[0]), empty_s = smem_addr(&c.sh->empty[0]);
-  // Per-lane operand addresses.  Column n of the mma's B operand (the activations) only feeds column n of the result, and only
-  // the columns of real batch rows are ever read back, so lanes that hold other columns load nothing: their operand
-  // registers and the sums derived from them are never used.
-  uint32_t x_s, corr_s, xsc_s;
-  bool has_x, has_c;
-  if (I4) {
-    has_x = g < 2 * p.B;                // B-operand columns 2b (t1) and 2b + 1 (t2) of batch row b
-    has_c = tig < p.B;                  // accumulator columns 2 tig, 2 tig + 1 belong to batch row tig
-    x_s = smem_addr(c.xs) + g * 128 + tig * 32;
-    corr_s = smem_addr(&c.sh->corr[0][has_c ? tig : 0]);
-    xsc_s = smem_addr(&c.sh->xscale[0][has_c ? tig : 0]);
-  } else {
-    has_x = !(g & 1) && (g >> 1) < p.B;  // batch b sits in column 2b, so that lane tig = b ends up with its sums
-    has_c = false;
-    x_s = smem_addr(c.xs) + (g >> 1) * p.xs_stride + tig * 16;
-    corr_s = xsc_s = 0;
+  // Per-lane operand addresses: base + chunk * stride, with stride 0 and the zero block for lanes that carry no batch column
+  // (every lane loads unconditionally: a conditional load would turn the operand registers into values that live across
+  // the loop iterations, and this loop has no registers to spare).
+  uint32_t x_s, x_cs, corr_s, corr_cs, xsc_s;
+  {
+    const uint32_t zero_s = smem_addr(&c.sh->zeros[0]);
+    if (I4) {
+      const bool has = g < 2 * p.B;
+      x_s = has ? smem_addr(c.xs) + g * 128 + tig * 32 : zero_s;
+      x_cs = has ? p.B * 256 : 0;
+      corr_s = tig < p.B ? smem_addr(&c.sh->corr[0][tig]) : zero_s;
+      corr_cs = tig < p.B ? (uint32_t)sizeof(int4) * BMAX : 0;
+      xsc_s = smem_addr(&c.sh->xscale[0][tig < p.B ? tig : 0]);
+    } else {
+      const bool has = !(g & 1) && (g >> 1) < p.B;   // batch b sits in column 2b, so that lane tig = b ends up with its sums
+      x_s = has ? smem_addr(c.xs) + (g >> 1) * p.xs_stride + tig * 16 : zero_s;
+      x_cs = has ? 64 : 0;
+      corr_s = corr_cs = xsc_s = 0;
+    }
   }
-  const uint32_t x_cs = I4 ? (uint32_t)p.B * 256u : 64u;
 
   // Residual words of the row tile whose sum this warp will finish after the loop (row tiles shared by several warps, the usual
   // case of the residual phases): requested now, so that their round trip is not at the end of the phase.
@@ -783,12 +799,10 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int mat, int nchunks, Best 
   struct XOps { uint4 x0, x1; int c0, c1; float xs; };
   auto load_xops = [&](int chunk, XOps &o) {
     const uint32_t xaddr = x_s + chunk * x_cs;
-    if (has_x) {
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(o.x0.x), "=r"(o.x0.y), "=r"(o.x0.z), "=r"(o.x0.w) : "r"(xaddr));
-      if (I4) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(o.x1.x), "=r"(o.x1.y), "=r"(o.x1.z), "=r"(o.x1.w) : "r"(xaddr + 16));
-    }
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(o.x0.x), "=r"(o.x0.y), "=r"(o.x0.z), "=r"(o.x0.w) : "r"(xaddr));
     if (I4) {
-      if (has_c) asm volatile("ld.shared.v2.s32 {%0,%1}, [%2];" : "=r"(o.c0), "=r"(o.c1) : "r"(corr_s + chunk * (uint32_t)(sizeof(int4) * BMAX)));
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(o.x1.x), "=r"(o.x1.y), "=r"(o.x1.z), "=r"(o.x1.w) : "r"(xaddr + 16));
+      asm volatile("ld.shared.v2.s32 {%0,%1}, [%2];" : "=r"(o.c0), "=r"(o.c1) : "r"(corr_s + chunk * corr_cs));
       asm volatile("ld.shared.f32 %0, [%1];" : "=f"(o.xs) : "r"(xsc_s + chunk * (uint32_t)(sizeof(float) * BMAX)));
     }
   };
@@ -811,31 +825,6 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int mat, int nchunks, Best 
     }
     next_chunk();
   };
-  // Two consecutive tiles of the warp's range, interleaved by hand (every shared-memory load and mma here is an ordered asm
-  // statement, so the source order is the issue order): four independent chains of two dependent integer mma each, then the
-  // two folds.  With four warps per scheduler this independence is what keeps the issue slots busy.
-  auto compute2 = [&](const TileRegs &ta, const TileRegs &tb, const XOps &oa, const XOps &ob) {
-    if (NOMATH && (p.debug & 1)) return;
-    if (I4) {
-      int lo_a[4], hi_a[4], lo_b[4], hi_b[4];
-      imma0(hi_a, ta.a.x & HI, ta.b.x & HI, ta.a.y & HI, ta.b.y & HI, oa.x0.z, oa.x0.w);
-      imma_c(lo_a, ta.a.x & LO, ta.b.x & LO, ta.a.y & LO, ta.b.y & LO, oa.x0.x, oa.x0.y, oa.c0, oa.c1);
-      imma0(hi_b, tb.a.x & HI, tb.b.x & HI, tb.a.y & HI, tb.b.y & HI, ob.x0.z, ob.x0.w);
-      imma_c(lo_b, tb.a.x & LO, tb.b.x & LO, tb.a.y & LO, tb.b.y & LO, ob.x0.x, ob.x0.y, ob.c0, ob.c1);
-      imma(hi_a, ta.a.z & HI, ta.b.z & HI, ta.a.w & HI, ta.b.w & HI, oa.x1.z, oa.x1.w);
-      imma(lo_a, ta.a.z & LO, ta.b.z & LO, ta.a.w & LO, ta.b.w & LO, oa.x1.x, oa.x1.y);
-      imma(hi_b, tb.a.z & HI, tb.b.z & HI, tb.a.w & HI, tb.b.w & HI, ob.x1.z, ob.x1.w);
-      imma(lo_b, tb.a.z & LO, tb.b.z & LO, tb.a.w & LO, tb.b.w & LO, ob.x1.x, ob.x1.y);
-      fold(lo_a, hi_a, ta.s, oa.xs);
-      next_chunk();
-      fold(lo_b, hi_b, tb.s, ob.xs);
-      next_chunk();
-    } else {
-      compute(ta, oa);
-      compute(tb, ob);
-    }
-  };
-
 #ifdef PT_MK_TRACE_WAITS
   pq[1] = pclk();
   // diagnostics build: SM-cycle accounting of the loop for three sample warps (wait for the stage / operand loads / math)
@@ -843,17 +832,13 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int mat, int nchunks, Best 
   unsigned long long *dslot = (c.tr && dw >= 0 && lane == 0) ? c.tr + 32 + 4 * dw : nullptr;
   auto clk = []() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)); return t; };
 #endif
-  // Stage j / 2 of this phase holds tiles j and j + 1 of this warp's range.  The activation-side operands are requested first,
-  // then the stage is awaited, both tiles go to registers, the stage is handed back to the producer as soon as those loads
-  // are issued, and the pair is multiplied.
-  XOps oa, ob;
-  oa.x0 = oa.x1 = ob.x0 = ob.x1 = make_uint4(0, 0, 0, 0);
-  oa.c0 = oa.c1 = ob.c0 = ob.c1 = 0;
-  oa.xs = ob.xs = 0.f;
+  // Stage j / 2 of this phase holds tiles j and j + 1 of this warp's range.  The first tile is multiplied while the second is on
+  // its way to the registers; the stage is handed back to the producer as soon as the second tile's loads are issued.
+  // (Measured on B200: multiplying the two tiles as interleaved mma chains, or requesting the activation operands before the
+  // wait, is 7-10 % slower per step than this plain order, with or without register spills.)
   for (int j = 0; j < nstages; j += 2) {
     const bool first = j < len, second = j + 1 < len;
-    if (first) load_xops(ch, oa);
-    if (second) load_xops(ch + 1 == nchunks ? 0 : ch + 1, ob);
+    XOps oa, ob;
 #ifdef PT_MK_TRACE_WAITS
     const unsigned long long t_w = (c.tr && tid == 0) ? gtime() : 0ull;
     const long long c0 = clk();
@@ -869,34 +854,25 @@ __device__ __forceinline__ void linear_phase(Ctx &c, int mat, int nchunks, Best 
     }
     const uint32_t t_s = ring_s + c.slot * STAGE_BYTES;
     TileRegs ta, tb;
-#ifdef PT_MK_TRACE_WAITS
-    ta.a = ta.b = tb.a = tb.b = make_uint4(0, 0, 0, 0);
-    ta.s = tb.s = 0;
-    const bool skip_loads = (p.debug & 2) != 0;
-    if (first && got && !skip_loads) load_tile(t_s, ta);
-    if (second && got && !skip_loads) load_tile(t_s + NCW * TILE, tb);
-#else
-    if (first && got) load_tile(t_s, ta);
+    if (first && got) {
+      load_tile(t_s, ta);
+      load_xops(ch, oa);
+      compute(ta, oa);
+    }
     if (second && got) load_tile(t_s + NCW * TILE, tb);
-#endif
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_s + c.slot * 8);
     c.advance();
-#ifdef PT_MK_TRACE_WAITS
-    long long c2;
-    asm volatile("{\n\t.reg .u32 z;\n\tadd.u32 z, %1, %2;\n\tand.b32 z, z, 0;\n\tmov.u64 %0, %%clock64;\n\t}" : "=l"(c2) : "r"(ta.a.x), "r"(tb.b.w));
-#endif
-    if (got) {
-      if (second) compute2(ta, tb, oa, ob);
-      else if (first) compute(ta, oa);
+    if (second && got) {
+      load_xops(ch, ob);
+      compute(tb, ob);
     }
 #ifdef PT_MK_TRACE_WAITS
     long long c3;
     asm volatile("{\n\t.reg .u32 z;\n\tadd.u32 z, %1, %2;\n\tand.b32 z, z, 0;\n\tmov.u64 %0, %%clock64;\n\t}" : "=l"(c3) : "r"(__float_as_uint(acc0)), "r"(__float_as_uint(acc1)));
     if (dslot) {
       atomicAdd(dslot + 0, (unsigned long long)(c1 - c0));
-      atomicAdd(dslot + 1, (unsigned long long)(c2 - c1));
-      atomicAdd(dslot + 2, (unsigned long long)(c3 - c2));
+      atomicAdd(dslot + 2, (unsigned long long)(c3 - c1));
       atomicAdd(dslot + 3, 1ull);
     }
 #endif
@@ -1650,9 +1626,33 @@ __global__ void stream_permute_kernel(const uint4 *__restrict__ src, uint4 *__re
   }
 }
 
-}  // namespace mk
+}  // namespace PT_MK_NS
 }  // namespace pt
 
+#ifdef PT_MK_SHORT_VARIANT
+namespace pt {
+// Launches the short-wait build of the kernel.  `params` points to a Params of the default build (same layout).
+int mk_short_launch(bool tp, const void *params, int n_sm, size_t smem, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    int dev = 0, v = 0;
+    PT_CUDA(cudaGetDevice(&dev));
+    PT_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    PT_CUDA(cudaFuncSetAttribute(mk_short::llama_step_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
+    PT_CUDA(cudaFuncSetAttribute(mk_short::llama_step_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
+    attr_set = true;
+  }
+  void *kargs[] = {const_cast<void *>(params)};
+  const void *kernel = tp ? (const void *)mk_short::llama_step_kernel<true> : (const void *)mk_short::llama_step_kernel<false>;
+  cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(n_sm), dim3(mk_short::THREADS), kargs, smem, stream);
+  if (e != cudaSuccess) return pt::set_error(PT_ERR_CUDA, "pt_llama_decode_step: %s", cudaGetErrorString(e));
+  return PT_OK;
+}
+}  // namespace pt
+#else
+namespace pt {
+int mk_short_launch(bool tp, const void *params, int n_sm, size_t smem, cudaStream_t stream);
+}
 using namespace pt;
 
 extern "C" int pt_llama_stream_permute(int wfmt, const void *packed, void *out, int n_out, int k_in, void *stream) {
@@ -1760,7 +1760,6 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
     // per device: what the constants currently hold (stream-ordered updates; launches on other streams of the same device
     // that overlap a change may see either value)
     static uint32_t hint_set[64];
-    static int limit_set[64];
     int dev = 0;
     PT_CUDA(cudaGetDevice(&dev));
     PT_REQUIRE(dev >= 0 && dev < 64, "pt_llama_decode_step: device ordinal %d outside 0..63", dev);
@@ -1769,12 +1768,12 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
       PT_CUDA(cudaMemcpyToSymbolAsync(mk::c_wait_hint, &want, sizeof(want), 0, cudaMemcpyHostToDevice, as_stream(stream)));
       hint_set[dev] = want;
     }
-    PT_REQUIRE(a->wait_limit >= 0, "pt_llama_decode_step: wait_limit=%d", a->wait_limit);
-    const int limit = a->wait_limit > 0 ? std::max(a->wait_limit, 256) : mk::kDefaultPollLimit;
-    if (limit != (limit_set[dev] ? limit_set[dev] : mk::kDefaultPollLimit)) {
-      PT_CUDA(cudaMemcpyToSymbolAsync(mk::c_poll_limit, &limit, sizeof(limit), 0, cudaMemcpyHostToDevice, as_stream(stream)));
-      limit_set[dev] = limit;
-    }
+  }
+  PT_REQUIRE(a->wait_limit >= 0, "pt_llama_decode_step: wait_limit=%d", a->wait_limit);
+  if (a->wait_limit > 0) {  // the short-wait build (its limit is a compile-time constant, like the default build's)
+    if (int rc = mk_short_launch(tp > 1, &p, n_sm, smem, as_stream(stream))) return rc;
+    pt::count_launch();
+    return PT_OK;
   }
   void *kargs[] = {(void *)&p};
   const void *kernel = tp > 1 ? (const void *)mk::llama_step_kernel<true> : (const void *)mk::llama_step_kernel<false>;
@@ -1783,3 +1782,4 @@ extern "C" int pt_llama_decode_step(const pt_llama_step_args *a, void *stream) {
   PT_LAUNCH_CHECK("pt_llama_decode_step");
   return PT_OK;
 }
+#endif  // PT_MK_SHORT_VARIANT
