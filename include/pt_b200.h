@@ -128,6 +128,41 @@ int pt_linear(const pt_linear_args *args, void *stream);
  *   - Nothing is allocated or freed, by this call or on its behalf. */
 int pt_linear_static_scratch(const pt_linear_args *args, void *stream);
 
+/* ---- tensor-core GEMMs for 16 or more activation rows (batched decode, prefill) ---------------------------------
+ * The same layers as pt_linear (Linear.__call__ -> ParamHandler.matmul, poptransformer/layers/linear.py:42-46,
+ * utils/param_handler/precision_strategy.py:56-81) when the batch no longer fits a matrix-vector kernel: the reference issues
+ * one PopLibs matmul per layer whatever the batch (ops/popart.py:55-67); here 16 or more rows go to tcgen05 / tensor-memory
+ * GEMMs fed by TMA.
+ *   PT_W_FP8 : x = E4M3 bytes [m, k_in] (pt_cast_fp8 with x_scale), w = E4M3 bytes [n_out, k_in] as stored by the checkpoint
+ *              (k contiguous), out = fp16((x . w^T) * x_scale * w_scale) - the FP8MatMul op (custom_ops/matmul_fp8.cpp:885-1091).
+ *   PT_W_INT4: x = fp16 [m, k_in], w = pt_gemm_int4_repack of the reference's int8 [n_out, k_in/2] rows, scales fp16
+ *              [n_out, k_in/group]; every weight becomes fp16(q) * scale with one rounding (Int4ToHalf,
+ *              custom_ops/int4_to_half_codelets.cpp:18-38) on its way to the tensor core.
+ * k_in must be a multiple of 128.  Accumulation is fp32.  k-slices (ksplit, 0 = chosen by the library) are summed in a fixed
+ * order; with more than one slice a workspace is needed (zeroed once by the caller; every launch leaves its counters at zero). */
+typedef struct pt_gemm_args {
+  int wfmt;               /* PT_W_FP8 or PT_W_INT4                                  */
+  int m, n_out, k_in;
+  int group;              /* INT4: scale group along k (a multiple of 128)          */
+  int epilogue;           /* PT_EPI_STORE or PT_EPI_RESIDUAL                         */
+  int ksplit;             /* 0 = let the library choose                             */
+  const void *x, *w;
+  const void *scales;     /* INT4: fp16 [n_out, k_in / group]                        */
+  float x_scale, w_scale; /* FP8 per-tensor scales                                   */
+  const void *residual;   /* fp16 [m, n_out]; may alias `out`                        */
+  void *out;              /* fp16 [m, n_out]                                         */
+  int out_ld;             /* row stride of `out` in elements; 0 = dense              */
+  void *workspace;        /* pt_gemm_workspace_bytes                                 */
+  size_t workspace_bytes;
+  int32_t *error_flag;    /* optional device int, set non-zero (21..24) if a bounded wait gave up */
+} pt_gemm_args;
+size_t pt_gemm_workspace_bytes(int m, int n_out, int max_ksplit);
+int pt_gemm(const pt_gemm_args *args, void *stream);
+/* Re-orders the nibbles of the reference's int4 rows (int8 [n_out, k_in/2], high nibble = even k, two's complement) into the
+ * word layout pt_gemm's transform step splits with two masks; same size (pt_gemm_int4_packed_bytes), still row-major. */
+size_t pt_gemm_int4_packed_bytes(int n_out, int k_in);
+int pt_gemm_int4_repack(const void *w, int n_out, int k_in, void *packed, void *stream);
+
 /* ---- norms ------------------------------------------------------------------------
  * pt_norm_ce replaces the `NormCE` custom op (customized.py:69-102; custom_ops/NormCE.cpp:534-610):
  * fp16 rows, LayerNorm over `dim`; rows == 1 takes the GetInPlaceNorm arithmetic

@@ -599,6 +599,14 @@ extern "C" int pt_cast_fp8(const void *x, float scale, int64_t n, void *out, voi
 extern "C" int pt_fp8_matmul(const void *a, const void *b, float scale_a, float scale_b, int m, int n, int k, void *out, void *stream) {
   PT_REQUIRE(a && b && out, "pt_fp8_matmul: null pointer argument");
   PT_REQUIRE(m > 0 && n > 0 && k > 0, "pt_fp8_matmul: bad shape m=%d n=%d k=%d", m, n, k);
+  if (k % 128 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0) {
+    // the tcgen05 GEMM (one k-slice: this entry point has no workspace argument)
+    pt_gemm_args g{};
+    g.wfmt = PT_W_FP8; g.m = m; g.n_out = n; g.k_in = k; g.epilogue = PT_EPI_STORE; g.ksplit = 1;
+    g.x = a; g.w = b; g.x_scale = scale_a; g.w_scale = scale_b; g.out = out;
+    return pt_gemm(&g, stream);
+  }
+  // shapes the tensor-core kernel does not take (k not a multiple of 128): scalar tiles
   dim3 grid(ceil_div(n, 32), ceil_div(m, 32));
   fp8_matmul_kernel<<<grid, 256, 0, as_stream(stream)>>>((const uint8_t *)a, (const uint8_t *)b, scale_a * scale_b, m, n, k, (__half *)out);
   PT_LAUNCH_CHECK("pt_fp8_matmul");

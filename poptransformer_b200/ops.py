@@ -20,7 +20,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import AttnArgs, LinearArgs, PtError, check
+from ._lib import AttnArgs, GemmArgs, LinearArgs, PtError, check
 
 W_INT4, W_FP16, W_FP8 = 0, 1, 2
 PRO_NONE, PRO_RMSNORM, PRO_CAST_FP8, PRO_RMSNORM_CAST_FP8 = 0, 1, 2, 3
@@ -122,6 +122,53 @@ def linear(x, pl, out=None, **kw):
         out = torch.empty((x.shape[0], n), dtype=torch.float16, device=x.device)
     a = linear_args(x, pl, out, **kw)
     check(_lib.lib().pt_linear(ctypes.byref(a), _stream()), "pt_linear")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ tensor-core GEMMs (16+ rows)
+class GemmWeight:
+    """A weight matrix for pt_gemm: FP8 bytes [n_out, k] as the checkpoint stores them, or INT4 rows in the reference's int8
+    [n_out, k/2] format re-ordered once (pt_gemm_int4_repack) plus fp16 scales [n_out, k/group]."""
+
+    def __init__(self, wfmt, w, scale=None, group=0, w_scale=1.0):
+        L = _lib.lib()
+        self.wfmt, self.n_out, self.w_scale = wfmt, w.shape[0], float(w_scale)
+        if wfmt == W_INT4:
+            self.k_in = w.shape[1] * 2
+            self.group = int(group) if group else self.k_in
+            self.scales = scale.reshape(self.n_out, self.k_in // self.group).to(torch.float16).contiguous()
+            self.w = torch.empty(L.pt_gemm_int4_packed_bytes(self.n_out, self.k_in), dtype=torch.uint8, device=w.device)
+            check(L.pt_gemm_int4_repack(_ptr(w.contiguous()), self.n_out, self.k_in, _ptr(self.w), _stream()), "pt_gemm_int4_repack")
+        elif wfmt == W_FP8:
+            self.k_in, self.group, self.scales = w.shape[1], 0, None
+            self.w = w.contiguous()
+        else:
+            raise PtError("GemmWeight: INT4 or FP8")
+
+    @property
+    def nbytes(self):
+        return self.w.numel() + (self.scales.numel() * 2 if self.scales is not None else 0)
+
+
+def gemm_workspace(m, n_out_max, max_ksplit=8, device="cuda"):
+    return torch.zeros(_lib.lib().pt_gemm_workspace_bytes(m, n_out_max, max_ksplit), dtype=torch.uint8, device=device)
+
+
+def gemm(x, gw, out=None, x_scale=1.0, epilogue=EPI_STORE, residual=None, workspace=None, ksplit=0, error_flag=None):
+    """y = x @ W^T on the tcgen05 GEMM.  INT4: x fp16 [m, k]; FP8: x E4M3 bytes [m, k] quantised with `x_scale`."""
+    m = x.shape[0]
+    if x.shape[1] != gw.k_in:
+        raise PtError(f"gemm: x has k={x.shape[1]}, weight has k={gw.k_in}")
+    if out is None:
+        out = torch.empty((m, gw.n_out), dtype=torch.float16, device=x.device)
+    a = GemmArgs()
+    a.wfmt, a.m, a.n_out, a.k_in, a.group, a.epilogue, a.ksplit = gw.wfmt, m, gw.n_out, gw.k_in, gw.group, epilogue, ksplit
+    a.x, a.w, a.scales = _ptr(x), _ptr(gw.w), _ptr(gw.scales)
+    a.x_scale, a.w_scale = float(x_scale), gw.w_scale
+    a.residual, a.out, a.out_ld = _ptr(residual), _ptr(out), 0
+    a.workspace, a.workspace_bytes = _ptr(workspace), (workspace.numel() if workspace is not None else 0)
+    a.error_flag = _ptr(error_flag)
+    check(_lib.lib().pt_gemm(ctypes.byref(a), _stream()), "pt_gemm")
     return out
 
 
