@@ -310,7 +310,7 @@ def run_b200(args):
         torch.cuda.synchronize()
         lin_ms = e0.elapsed_time(e1) / (reps * n_lin)
         roof = {"bound": "hbm", "achieved": (lin_bytes / n_lin) / (lin_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "traffic": None,
-                "kernel": "linear_kernel<INT4>", "peak_source": peak_src, "launch_us": lin_ms * 1e3, "bytes_per_launch": lin_bytes / n_lin}
+                "kernel": "gemm_tc_kernel<INT4> (tcgen05)" if getattr(dec, "use_gemm", False) else "linear_kernel<INT4>", "peak_source": peak_src, "launch_us": lin_ms * 1e3, "bytes_per_launch": lin_bytes / n_lin}
     roof["frac"] = roof["achieved"] / peak
 
     def shutdown():

@@ -133,9 +133,11 @@ int pt_linear_static_scratch(const pt_linear_args *args, void *stream);
  * utils/param_handler/precision_strategy.py:56-81) when the batch no longer fits a matrix-vector kernel: the reference issues
  * one PopLibs matmul per layer whatever the batch (ops/popart.py:55-67); here 16 or more rows go to tcgen05 / tensor-memory
  * GEMMs fed by TMA.
- *   PT_W_FP8 : x = E4M3 bytes [m, k_in] (pt_cast_fp8 with x_scale), w = E4M3 bytes [n_out, k_in] as stored by the checkpoint
- *              (k contiguous), out = fp16((x . w^T) * x_scale * w_scale) - the FP8MatMul op (custom_ops/matmul_fp8.cpp:885-1091).
- *   PT_W_INT4: x = fp16 [m, k_in], w = pt_gemm_int4_repack of the reference's int8 [n_out, k_in/2] rows, scales fp16
+ *   PT_W_FP8 : x = E4M3 bytes [m, k_in] (pt_cast_fp8 with x_scale), w = E4M3 bytes [n_out, k_in], out = fp16((x . w^T) * x_scale
+ *              * w_scale) - the FP8MatMul op (custom_ops/matmul_fp8.cpp:885-1091).  w is either row-major as the checkpoint
+ *              stores it (w_tiled = 0: what FP8MatMul passes; fetched with strided TMA boxes) or tiled once by pt_gemm_repack
+ *              (w_tiled = 1: one contiguous bulk copy per stage, the layout for a model's weights).
+ *   PT_W_INT4: x = fp16 [m, k_in], w = pt_gemm_repack of the reference's int8 [n_out, k_in/2] rows (w_tiled = 1), scales fp16
  *              [n_out, k_in/group]; every weight becomes fp16(q) * scale with one rounding (Int4ToHalf,
  *              custom_ops/int4_to_half_codelets.cpp:18-38) on its way to the tensor core.
  * k_in must be a multiple of 128.  Accumulation is fp32.  k-slices (ksplit, 0 = chosen by the library) are summed in a fixed
@@ -146,6 +148,7 @@ typedef struct pt_gemm_args {
   int group;              /* INT4: scale group along k (a multiple of 128)          */
   int epilogue;           /* PT_EPI_STORE or PT_EPI_RESIDUAL                         */
   int ksplit;             /* 0 = let the library choose                             */
+  int w_tiled;            /* 1: w was tiled by pt_gemm_repack; 0: row-major (FP8 only) */
   const void *x, *w;
   const void *scales;     /* INT4: fp16 [n_out, k_in / group]                        */
   float x_scale, w_scale; /* FP8 per-tensor scales                                   */
@@ -158,10 +161,12 @@ typedef struct pt_gemm_args {
 } pt_gemm_args;
 size_t pt_gemm_workspace_bytes(int m, int n_out, int max_ksplit);
 int pt_gemm(const pt_gemm_args *args, void *stream);
-/* Re-orders the nibbles of the reference's int4 rows (int8 [n_out, k_in/2], high nibble = even k, two's complement) into the
- * word layout pt_gemm's transform step splits with two masks; same size (pt_gemm_int4_packed_bytes), still row-major. */
-size_t pt_gemm_int4_packed_bytes(int n_out, int k_in);
-int pt_gemm_int4_repack(const void *w, int n_out, int k_in, void *packed, void *stream);
+/* One-time tiling of a weight matrix for pt_gemm: [128-row tile][k block] with every tile contiguous.  FP8: E4M3 bytes
+ * [n_out, k_in] -> 16 KB tiles in the 128-byte-swizzled image the tensor core reads.  INT4: the reference's int8
+ * [n_out, k_in/2] rows (high nibble = even k, two's complement) -> 4 KB tiles of offset-binary nibbles in the word order
+ * the transform step splits with two masks.  Rows are padded to a multiple of 128 (pt_gemm_packed_bytes). */
+size_t pt_gemm_packed_bytes(int wfmt, int n_out, int k_in);
+int pt_gemm_repack(int wfmt, const void *w, int n_out, int k_in, void *packed, void *stream);
 
 /* ---- norms ------------------------------------------------------------------------
  * pt_norm_ce replaces the `NormCE` custom op (customized.py:69-102; custom_ops/NormCE.cpp:534-610):
@@ -366,6 +371,9 @@ int pt_step_containers(int32_t *ids, int batch, int max_len, int32_t *step_dev, 
  * done_flag: device int, zeroed by the caller before a generation. */
 int pt_step_containers_early_stop(int32_t *ids, int batch, int max_len, int32_t *step_dev, const int32_t *next_ids,
                                   int pad_id, int eos_id, int32_t *stop_mask, int32_t *done_flag, void *stream);
+/* SwiGLU behind a fused gate|up linear (llama2/mlp.py:20-28, chatglm2/mlp.py:51-59): gate_up fp16 [rows, 2 f] with the gate
+ * features first; out[r, j] = fp16(up[r, j] * swish(gate[r, j])), swish in float32 rounded once.  out_ld: row stride (0 = f). */
+int pt_swiglu(const void *gate_up, int rows, int f, void *out, int out_ld, void *stream);
 /* Elementwise fp16: out = fp16(a + b) (ops.add). */
 int pt_add_f16(const void *a, const void *b, int64_t n, void *out, void *stream);
 

@@ -41,7 +41,7 @@ class AttnArgs(ctypes.Structure):
 class GemmArgs(ctypes.Structure):
     _fields_ = [
         ("wfmt", c_int), ("m", c_int), ("n_out", c_int), ("k_in", c_int), ("group", c_int), ("epilogue", c_int), ("ksplit", c_int),
-        ("x", c_void_p), ("w", c_void_p), ("scales", c_void_p), ("x_scale", c_float), ("w_scale", c_float),
+        ("w_tiled", c_int), ("x", c_void_p), ("w", c_void_p), ("scales", c_void_p), ("x_scale", c_float), ("w_scale", c_float),
         ("residual", c_void_p), ("out", c_void_p), ("out_ld", c_int), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
         ("error_flag", c_void_p),
     ]
@@ -74,8 +74,8 @@ SIGNATURES = {
     "pt_linear_static_scratch": (c_int, [ctypes.POINTER(LinearArgs), c_void_p]),
     "pt_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "pt_gemm": (c_int, [ctypes.POINTER(GemmArgs), c_void_p]),
-    "pt_gemm_int4_packed_bytes": (c_size_t, [c_int, c_int]),
-    "pt_gemm_int4_repack": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "pt_gemm_packed_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "pt_gemm_repack": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "pt_norm_ce": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
     "pt_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "pt_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -104,6 +104,7 @@ SIGNATURES = {
     "pt_embedding": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_step_containers": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "pt_step_containers_early_stop": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "pt_swiglu": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "pt_add_f16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
 }
 

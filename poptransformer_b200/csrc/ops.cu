@@ -439,6 +439,15 @@ __global__ void add_f16_kernel(const __half *__restrict__ a, const __half *__res
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = h_add(a[i], b[i]);
 }
 
+// SwiGLU on the output of a fused gate|up linear whose rows are [gate features | up features]: out = fp16(up * swish(gate)).
+__global__ void swiglu_kernel(const __half *__restrict__ gu, int rows, int f, __half *__restrict__ out, int out_ld) {
+  const size_t total = (size_t)rows * f;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t b = i / f, j = i - b * f;
+    out[b * out_ld + j] = h_mul(gu[b * 2 * f + f + j], swish_h(gu[b * 2 * f + j]));
+  }
+}
+
 static inline int grid_for(size_t n, int block = 256) {
   size_t g = (n + block - 1) / block;
   const size_t cap = (size_t)sm_count() * 8;
@@ -665,6 +674,13 @@ extern "C" int pt_step_containers_early_stop(int32_t *ids, int batch, int max_le
   PT_REQUIRE(batch > 0 && max_len > 0, "pt_step_containers_early_stop: bad shape");
   step_containers_kernel<<<1, 128, 0, as_stream(stream)>>>(ids, batch, max_len, step_dev, next_ids, pad_id, eos_id, stop_mask, done_flag);
   PT_LAUNCH_CHECK("pt_step_containers_early_stop");
+  return PT_OK;
+}
+
+extern "C" int pt_swiglu(const void *gate_up, int rows, int f, void *out, int out_ld, void *stream) {
+  PT_REQUIRE(gate_up && out && rows > 0 && f > 0, "pt_swiglu: bad arguments");
+  swiglu_kernel<<<grid_for((size_t)rows * f), 256, 0, as_stream(stream)>>>((const __half *)gate_up, rows, f, (__half *)out, out_ld > 0 ? out_ld : f);
+  PT_LAUNCH_CHECK("pt_swiglu");
   return PT_OK;
 }
 

@@ -52,7 +52,7 @@ from .tp import KSlice as _KSlice, rows as _rows, row_parallel_int4, row_paralle
 class LlamaDecoder(DecodeLoop):
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, fuse_norm=None, pad_id=None, eos_id=-1,
                  tp_rank=0, tp_size=1, group=None, pdl=True, persistent=None, keep_logits=True, early_stop=False, tp_buffers=None,
-                 wait_limit=0):
+                 wait_limit=0, use_gemm=None):
         """tp_buffers: for tp_size > 1, the exchange buffers of all ranks as this process sees them (a list of tp_size int32 CUDA
         tensors of pt_llama_tp_buffer_bytes each, entry tp_rank being local memory, the others peer mappings the caller set up).
         Default: the buffers are allocated as symmetric memory over `group` (torch.distributed).
@@ -75,16 +75,29 @@ class LlamaDecoder(DecodeLoop):
         def t(key):
             return state_dict[key].to(dev)
 
+        # More than 32 rows on one GPU with INT4 weights (beyond the skinny-matmul kernels' range): the transformer linears run on
+        # the tcgen05 GEMM, weights tiled once.  (Measured on B200 at 16 and 32 rows the skinny-matmul kernel is as fast or faster.)
+        first_w = state_dict["model.layers.0.self_attn.q_proj.weight"]
+        grp0 = (first_w.shape[1] * 2) // max(1, state_dict["model.layers.0.self_attn.q_proj.weight_scale"].numel() // first_w.shape[0]) \
+            if first_w.dtype == torch.int8 else 0
+        self.use_gemm = ((batch > 32 or use_gemm is True) and use_gemm is not False and tp_size == 1 and first_w.dtype == torch.int8 and grp0 % 128 == 0 and persistent is not True
+                         and c.d_model % 128 == 0 and c.ffn % 128 == 0)
+
         def col_parallel(keys, interleave=False):
             ws = [_rows(t(k), r, tp) for k in keys]
             if ws[0].dtype == torch.int8:
                 sc = [_rows(t(k + "_scale").reshape(t(k).shape[0], -1), r, tp) for k in keys]
                 grp = (ws[0].shape[1] * 2) // sc[0].shape[1]
+                if self.use_gemm:
+                    return ops.GemmWeight(ops.W_INT4, torch.cat(ws, 0), torch.cat(sc, 0), group=grp)
                 return ops.PackedLinear(ops.W_INT4, torch.cat(ws, 0), torch.cat(sc, 0), group=grp, interleave_gate_up=interleave)
             return ops.PackedLinear(ops.W_FP16, torch.cat(ws, 0).to(torch.float16), interleave_gate_up=interleave)
 
         def row_parallel(key, k_total):
             w = t(key)
+            if w.dtype == torch.int8 and self.use_gemm:
+                sc = t(key + "_scale").reshape(w.shape[0], -1)
+                return ops.GemmWeight(ops.W_INT4, w, sc, group=(w.shape[1] * 2) // sc.shape[1]), _KSlice(k_total, 0, 1, 128)
             if w.dtype == torch.int8:
                 loc, loc_s, grp_loc, ks = row_parallel_int4(w, t(key + "_scale").reshape(w.shape[0], -1), k_total, r, tp)
                 return ops.PackedLinear(ops.W_INT4, loc, loc_s, group=grp_loc), ks
@@ -142,10 +155,13 @@ class LlamaDecoder(DecodeLoop):
             self.caches.append(kc)
         self.attn_ws = ops.attn_workspace(B, self.h_loc, c.head_dim, self.caches[0].max_pages, dev)
         self.lin_ws = ops.linear_workspace(B, max(3 * self.d_loc, 2 * self.f_loc, d, self.logits.shape[1]), 16, dev)
+        if self.use_gemm:
+            self.gemm_ws = ops.gemm_workspace(B, max(3 * d, 2 * f), 8, dev)
+            self.gu_out = torch.empty((B, 2 * f), **f16)
         self.graph = None
         # The persistent whole-step kernel covers INT4, batch <= 2, on one GPU or tensor-parallel over up to 8 (the all-reduces are
         # then fused into the kernel as peer stores); everything else takes the per-op kernels and NCCL.
-        can_persist = (batch <= 2 and c.head_dim == 128 and page_size == 64 and self.layers[0]["qkv"].wfmt == ops.W_INT4
+        can_persist = (not self.use_gemm and batch <= 2 and c.head_dim == 128 and page_size == 64 and self.layers[0]["qkv"].wfmt == ops.W_INT4
                        and d % 128 == 0 and f % 128 == 0)
         if tp > 1:
             can_persist = (can_persist and tp <= 8 and self.d_loc % 128 == 0 and self.f_loc % 8 == 0 and self.o_ks.offset == 0
@@ -267,6 +283,10 @@ class LlamaDecoder(DecodeLoop):
             ops.check(L_.pt_llama_decode_step(ctypes.byref(self.mk_args), ops._stream()), "pt_llama_decode_step")
             return
         ops.embedding(self.emb, self.ids, self.step_t, out=self.x)
+        if self.use_gemm:
+            self._enqueue_layers_gemm()
+            self._enqueue_head()
+            return
         attn_out = self.attn.data_ptr() + 2 * self.o_ks.offset      # column offset inside the zero-padded k-window
         act_out = self.act.data_ptr() + 2 * self.down_ks.offset
         for li, L in enumerate(self.layers):
@@ -279,6 +299,32 @@ class LlamaDecoder(DecodeLoop):
             self._row_parallel(self.attn, L["o"])
             self._norm_linear_raw(self.x, L["ln2"], L["gu"], act_out, self.act.shape[1])
             self._row_parallel(self.act, L["down"])
+        self._enqueue_head()
+
+    def _enqueue_layers_gemm(self):
+        """The transformer blocks at 16 or more rows: RMSNorm kernel, tcgen05 GEMMs (residual adds in their epilogues), SwiGLU kernel."""
+        c = self.cfg
+        L_ = ops._lib.lib()
+
+        def norm(gamma):
+            ops.check(L_.pt_rms_norm(ops._ptr(self.x), None, ops._ptr(gamma), self.batch, c.d_model, c.eps, ops._ptr(self.h), None, ops._stream()),
+                      "pt_rms_norm")
+
+        for li, L in enumerate(self.layers):
+            norm(L["ln1"])
+            ops.gemm(self.h, L["qkv"], out=self.qkv, workspace=self.gemm_ws, error_flag=self.error_flag)
+            a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_LLAMA, ops.SOFTMAX_F32, self.score_scale,
+                              self.sin, self.cos, self.attn_ws, self.error_flag)
+            ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
+            ops.gemm(self.attn, L["o"], out=self.x, epilogue=ops.EPI_RESIDUAL, residual=self.x, workspace=self.gemm_ws, error_flag=self.error_flag)
+            norm(L["ln2"])
+            ops.gemm(self.h, L["gu"], out=self.gu_out, workspace=self.gemm_ws, error_flag=self.error_flag)
+            ops.check(L_.pt_swiglu(ops._ptr(self.gu_out), self.batch, c.ffn, ops._ptr(self.act), self.act.shape[1], ops._stream()), "pt_swiglu")
+            ops.gemm(self.act, L["down"], out=self.x, epilogue=ops.EPI_RESIDUAL, residual=self.x, workspace=self.gemm_ws, error_flag=self.error_flag)
+
+    def _enqueue_head(self):
+        c = self.cfg
+        L_ = ops._lib.lib()
         self._norm_linear(self.x, self.norm, self.head, self.logits)
         if self.tp == 1:
             ops.check(L_.pt_topk(ops._ptr(self.logits), self.batch, c.vocab, 1, 0, ops._ptr(self.next_val), ops._ptr(self.next_ids),
@@ -303,6 +349,13 @@ class LlamaDecoder(DecodeLoop):
 
     def enqueue_linears_only(self):
         """Every INT4/FP16 transformer linear of one step, back to back (used to time the dominant kernel alone)."""
+        if self.use_gemm:
+            for L in self.layers:
+                ops.gemm(self.h, L["qkv"], out=self.qkv, workspace=self.gemm_ws)
+                ops.gemm(self.attn, L["o"], out=self.part, workspace=self.gemm_ws)
+                ops.gemm(self.h, L["gu"], out=self.gu_out, workspace=self.gemm_ws)
+                ops.gemm(self.act, L["down"], out=self.part, workspace=self.gemm_ws)
+            return
         for L in self.layers:
             self._norm_linear(self.x, L["ln1"], L["qkv"], self.qkv)
             ops.linear(self.attn, L["o"], self.part, workspace=self.lin_ws)

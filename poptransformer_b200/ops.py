@@ -127,8 +127,8 @@ def linear(x, pl, out=None, **kw):
 
 # ------------------------------------------------------------------------------------------ tensor-core GEMMs (16+ rows)
 class GemmWeight:
-    """A weight matrix for pt_gemm: FP8 bytes [n_out, k] as the checkpoint stores them, or INT4 rows in the reference's int8
-    [n_out, k/2] format re-ordered once (pt_gemm_int4_repack) plus fp16 scales [n_out, k/group]."""
+    """A weight matrix tiled once for pt_gemm (pt_gemm_repack): FP8 bytes [n_out, k], or INT4 rows in the reference's int8
+    [n_out, k/2] format plus fp16 scales [n_out, k/group]."""
 
     def __init__(self, wfmt, w, scale=None, group=0, w_scale=1.0):
         L = _lib.lib()
@@ -137,17 +137,18 @@ class GemmWeight:
             self.k_in = w.shape[1] * 2
             self.group = int(group) if group else self.k_in
             self.scales = scale.reshape(self.n_out, self.k_in // self.group).to(torch.float16).contiguous()
-            self.w = torch.empty(L.pt_gemm_int4_packed_bytes(self.n_out, self.k_in), dtype=torch.uint8, device=w.device)
-            check(L.pt_gemm_int4_repack(_ptr(w.contiguous()), self.n_out, self.k_in, _ptr(self.w), _stream()), "pt_gemm_int4_repack")
         elif wfmt == W_FP8:
             self.k_in, self.group, self.scales = w.shape[1], 0, None
-            self.w = w.contiguous()
         else:
             raise PtError("GemmWeight: INT4 or FP8")
+        self.w = torch.empty(L.pt_gemm_packed_bytes(wfmt, self.n_out, self.k_in), dtype=torch.uint8, device=w.device)
+        check(L.pt_gemm_repack(wfmt, _ptr(w.contiguous()), self.n_out, self.k_in, _ptr(self.w), _stream()), "pt_gemm_repack")
 
     @property
     def nbytes(self):
-        return self.w.numel() + (self.scales.numel() * 2 if self.scales is not None else 0)
+        """Algorithmic bytes one launch streams from HBM."""
+        wb = self.n_out * self.k_in // 2 if self.wfmt == W_INT4 else self.n_out * self.k_in
+        return wb + (self.scales.numel() * 2 if self.scales is not None else 0)
 
 
 def gemm_workspace(m, n_out_max, max_ksplit=8, device="cuda"):
@@ -163,6 +164,7 @@ def gemm(x, gw, out=None, x_scale=1.0, epilogue=EPI_STORE, residual=None, worksp
         out = torch.empty((m, gw.n_out), dtype=torch.float16, device=x.device)
     a = GemmArgs()
     a.wfmt, a.m, a.n_out, a.k_in, a.group, a.epilogue, a.ksplit = gw.wfmt, m, gw.n_out, gw.k_in, gw.group, epilogue, ksplit
+    a.w_tiled = 1
     a.x, a.w, a.scales = _ptr(x), _ptr(gw.w), _ptr(gw.scales)
     a.x_scale, a.w_scale = float(x_scale), gw.w_scale
     a.residual, a.out, a.out_ld = _ptr(residual), _ptr(out), 0

@@ -14,23 +14,27 @@ pytestmark = pytest.mark.gpu
 TINY = dict(n_layer=2, d_model=256, n_head=2, ffn=512, vocab=1000)
 
 
-def _setup(cuda, batch, max_len, int4_group, seed=0, persistent=None):
+def _setup(cuda, batch, max_len, int4_group, seed=0, persistent=None, use_gemm=None):
     from poptransformer_b200 import llama, synth
     sd = synth.llama_state_dict(**TINY, seed=seed, device="cpu", int4_group=int4_group)
     cfg = llama.LlamaConfig(**TINY, max_len=max_len, int4_group=int4_group)
-    dec = llama.LlamaDecoder(cfg, sd, batch, device=cuda, persistent=persistent)
+    dec = llama.LlamaDecoder(cfg, sd, batch, device=cuda, persistent=persistent, use_gemm=use_gemm)
     ocfg = llama_np.LlamaConfig(**TINY, max_len=max_len, group=int4_group)
     orc = llama_np.LlamaOracle(ocfg, {k: v.numpy() for k, v in sd.items()}, batch)
     return dec, orc
 
 
 @pytest.mark.parametrize("batch,int4_group,persistent", [(1, 128, True), (2, 128, True), (1, 128, False), (2, 0, False), (1, 256, False),
-                                                        (16, 128, False)])
+                                                        (16, 128, False), (16, 128, "gemm")])
 def test_logits_teacher_forced(cuda, batch, int4_group, persistent):
-    """persistent=True: the whole-step kernel; False: the per-op kernels.  Both against the oracle."""
+    """persistent=True: the whole-step kernel; False: the per-op kernels; "gemm": the per-op path with the transformer linears on the
+    tcgen05 GEMM (the path of more than 32 rows, forced here at 16).  All against the oracle."""
     from poptransformer_b200 import synth
-    max_len = 72 if persistent else 40          # more than one KV page for the persistent kernel
-    dec, orc = _setup(cuda, batch, max_len, int4_group, persistent=persistent)
+    max_len = 72 if persistent is True else 40          # more than one KV page for the persistent kernel
+    gemm = persistent == "gemm"
+    persistent = False if gemm else persistent
+    dec, orc = _setup(cuda, batch, max_len, int4_group, persistent=persistent, use_gemm=True if gemm else None)
+    assert dec.use_gemm == gemm
     assert dec.persistent == persistent
     ids = synth.prompt_ids(batch, max_len, max_len, TINY["vocab"], dec.pad_id, seed=1)     # all prompt: every step is forced
     dec.reset(ids)

@@ -33,12 +33,17 @@ def checkpoint(cuda):
     return sd, {k: v.cpu().numpy() for k, v in sd.items()}
 
 
-@pytest.mark.parametrize("batch,persistent", [(1, True), (2, True), (1, False), (16, False)])
+@pytest.mark.parametrize("batch,persistent", [(1, True), (2, True), (1, False), (16, False), (16, "gemm")])
 def test_full_width_teacher_forced(cuda, checkpoint, batch, persistent):
+    """persistent True: the whole-step kernel; False: the per-op kernels; "gemm": per-op with the transformer linears on the tcgen05
+    GEMM (the path of more than 32 rows, forced here at 16)."""
     from poptransformer_b200 import llama, synth
     sd, sd_np = checkpoint
-    dec = llama.LlamaDecoder(llama.LlamaConfig(**DIMS, max_len=MAX_LEN, int4_group=GROUP), sd, batch, device=cuda, persistent=persistent)
-    assert dec.persistent == persistent
+    gemm = persistent == "gemm"
+    persistent = False if gemm else persistent
+    dec = llama.LlamaDecoder(llama.LlamaConfig(**DIMS, max_len=MAX_LEN, int4_group=GROUP), sd, batch, device=cuda, persistent=persistent,
+                             use_gemm=True if gemm else None)
+    assert dec.persistent == persistent and dec.use_gemm == gemm
     orc = c_ref.LlamaOracleC(llama_np.LlamaConfig(**DIMS, max_len=MAX_LEN, group=GROUP), sd_np, batch)
 
     # a cache that is already CTX tokens deep: the same random K/V rows on both sides
