@@ -93,6 +93,53 @@ def run_other(name):
     print(name, "ok: step", out_step, "ids[0, :12]", np.asarray(out_ids)[0, :12])
 
 
+def run_graph_case(name, out_path):
+    """Records the graph the reference's unmodified LLAMA2DecModel emits for case `name` with the PRODUCT's recorder
+    (poptransformer_b200/frontend/popart.py) and stores it without weights: the fixture the GPU front-end test lowers on a machine
+    that has no reference checkout.  Same checkpoint seeds as the golden id streams of the same case."""
+    dims, precision, group, batch, max_len, prompt, seed = CASES[name]
+    sys.path[:0] = [os.path.join(ROOT, "poptransformer_b200", "frontend")]      # popart / poprt = the front end; hydra = the test stub
+    import popart
+    assert "frontend" in popart.__file__
+    from poptransformer_b200 import synth
+    from poptransformer_b200 import build as _b
+    tmp = tempfile.mkdtemp()
+    os.makedirs(os.path.join(tmp, "examples", "llama2"))
+    os.symlink(_b.build(), os.path.join(tmp, "custom_ops.so"))      # the reference loads '../../custom_ops.so' at import (ops/customized.py:17-18)
+    os.chdir(os.path.join(tmp, "examples", "llama2"))
+    from poptransformer.utils.registry import REGISTRY
+    from poptransformer.utils.tensor_type import TensorType
+    for k, v in dict(num_replicas=1, batch_size=batch, batch_per_step=1, model_type="shard", enable_pipeline=False, precision=precision).items():
+        REGISTRY.register(k, v)
+    REGISTRY.register("tensor_type", TensorType(precision))
+    REGISTRY.register("logger", logging.getLogger("poptransformer"))
+    from poptransformer.models.llama2.model import LLAMA2DecModel
+    pad_id = dims["vocab"] - 1
+    sd = synth.llama_state_dict(**dims, seed=seed, device="cpu", int4_group=group)
+    if group:
+        sd = {k: (v.reshape(-1) if k.endswith("_scale") else v) for k, v in sd.items()}
+
+    class GoldenLlama(LLAMA2DecModel):
+        def prepare_state_dict(self):
+            self.hf_tokenizer = types.SimpleNamespace(pad_token_id=pad_id, eos_token_id=pad_id - 1)
+            self.hf_config = types.SimpleNamespace(vocab_size=dims["vocab"], hidden_size=dims["d_model"], rms_norm_eps=1e-5,
+                                                   num_attention_heads=dims["n_head"], intermediate_size=dims["ffn"],
+                                                   num_hidden_layers=dims["n_layer"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+            self.state_dict = sd
+            self.register_state_dict()
+
+    model = GoldenLlama(max_length=max_len, max_loop=max_len - 1, layer_per_ipu=[dims["n_layer"]], early_stop=False)
+    model.build_graph()
+    os.chdir(ROOT)
+    model.graph.save(out_path)
+    # the recorded initializers are the checkpoint in the reference's storage layout: the lowering must recover the synthetic one
+    from poptransformer_b200.frontend import lower
+    plan = lower.analyze(model.graph)
+    back = lower.state_dict_from_initializers(model.graph, plan)
+    assert set(back) == set(sd) and all(np.array_equal(back[k].numpy().reshape(-1), sd[k].numpy().reshape(-1)) for k in sd)
+    print(name, "graph recorded:", len(model.graph.nodes), "main nodes,", plan)
+
+
 def run_case(name):
     """Each case runs in a fresh interpreter: the reference keeps its graph and settings in a process-global registry."""
     dims, precision, group, batch, max_len, prompt, seed = CASES[name]
@@ -185,8 +232,11 @@ def run_tp_strategies(name="tp_strategies"):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) > 2:
+    if len(sys.argv) > 2 and sys.argv[2].endswith(":graph"):       # e.g. llama_tiny_int4:graph [output path]
+        case = sys.argv[2].split(":")[0]
+        run_graph_case(case, sys.argv[3] if len(sys.argv) > 3 else os.path.join(ROOT, "tests", "golden", case + "_graph.json"))
+    elif len(sys.argv) > 2:
         (run_tp_strategies if sys.argv[2] == "tp_strategies" else run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
     else:
-        for case in list(CASES) + list(OTHER) + ["tp_strategies"]:
+        for case in list(CASES) + list(OTHER) + ["tp_strategies", "llama_tiny_int4:graph", "llama_tiny_fp16:graph"]:
             subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)
