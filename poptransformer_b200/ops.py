@@ -241,25 +241,38 @@ def kv_cache(state, step, updater):
 
 
 class KVCachePipelineOp:
-    def __init__(self, max_len, max_bps, sequence_axis, step_len=1):
-        self.max_len, self.max_bps, self.axis, self.step_len = max_len, max_bps, sequence_axis, step_len
+    """One `KVCachePipeline` call site (custom_ops/kv_cache_pipeline.cpp:374-451): `max_bps` caches, cache step % max_bps receives the
+    shifted insert and is returned.  transpose=1 is the op's second storage layout (kv_cache_pipeline.hpp:107-113, vertex
+    GetBpsKvCacheLastDim, kv_cache_codelet.cpp:170-212): the caches are kept as [..., H, max_len] and shifted along their LAST
+    dimension; the op returns the tensor transposed back (kv_cache_pipeline.cpp:441-446), so callers see the same values."""
+
+    def __init__(self, max_len, max_bps, sequence_axis, step_len=1, transpose=0):
+        self.max_len, self.max_bps, self.axis, self.step_len, self.transpose = max_len, max_bps, sequence_axis, step_len, int(transpose)
         self.caches = None
 
     def __call__(self, step, updater):
         shape = list(updater.shape)
         if self.axis != len(shape) - 2:
             raise PtError("KVCachePipeline: sequence_axis must be rank - 2 (kv_cache_pipeline.hpp:83-88)")
-        outer = 1
-        for d in shape[: self.axis]:
-            outer *= d
-        inner = shape[-1]
-        shape[self.axis] = self.max_len
+        if shape[self.axis] != self.step_len:
+            raise PtError(f"KVCachePipeline: updater has {shape[self.axis]} positions on axis {self.axis}, step_len is {self.step_len}")
+        if self.transpose:
+            upd = updater.transpose(-1, -2).contiguous()           # [..., H, step_len]: the sequence is the last dimension
+            outer, inner = upd.numel() // self.step_len, 1
+            store = list(upd.shape[:-1]) + [self.max_len]
+        else:
+            upd = updater
+            outer = 1
+            for d in shape[: self.axis]:
+                outer *= d
+            inner = shape[-1]
+            store = shape[: self.axis] + [self.max_len, shape[-1]]
         if self.caches is None:
-            self.caches = torch.zeros([self.max_bps] + shape, dtype=updater.dtype, device=updater.device)
-        out = torch.empty(shape, dtype=updater.dtype, device=updater.device)
-        check(_lib.lib().pt_kv_cache_pipeline(_ptr(step), _ptr(updater), _ptr(self.caches), _ptr(out), self.max_bps, outer, self.max_len,
+            self.caches = torch.zeros([self.max_bps] + store, dtype=updater.dtype, device=updater.device)
+        out = torch.empty(store, dtype=updater.dtype, device=updater.device)
+        check(_lib.lib().pt_kv_cache_pipeline(_ptr(step), _ptr(upd), _ptr(self.caches), _ptr(out), self.max_bps, outer, self.max_len,
                                               self.step_len, inner, _stream()), "KVCachePipeline")
-        return out
+        return out.transpose(-1, -2).contiguous() if self.transpose else out
 
 
 def kv_cache_pipeline(state, step, updater):
@@ -425,6 +438,16 @@ def lm_head_tp_merge(dec):
     torch.distributed.all_gather_into_tensor(dec.gather_ids, dec.next_ids.view(1, -1), group=dec.group)
     check(L.pt_lm_head_tp_pick(_ptr(dec.gather_val), _ptr(dec.gather_ids), dec.tp, dec.batch, _ptr(dec.next_ids), _stream()),
           "pt_lm_head_tp_pick")
+
+
+def random_sample(logits, k, generator=None):
+    """ops.random_sample (popart.py:25-29): top-k of the logits on their last axis, then one of the k candidates picked by the arg-max
+    of k standard-normal draws (one draw vector shared by all rows, shape [1, k] as in the reference).  The draws come from torch's
+    generator (the reference's come from PopART's RNG: the choice is not reproducible across the two, the candidate set is)."""
+    vals, ids = topk(logits, k)
+    noise = torch.randn((1, k), generator=generator, device=logits.device, dtype=torch.float32)
+    pick = torch.argmax(noise, dim=1)                               # [1]
+    return ids[..., pick.item()].unsqueeze(-1).contiguous()
 
 
 def add(a, b):

@@ -186,6 +186,94 @@ def run_case(name):
     print(name, "ok: step", out_step, "ids[0, :12]", np.asarray(out_ids)[0, :12])
 
 
+def run_checkpoint_preprocess(name="checkpoint_preprocess"):
+    """The reference's own checkpoint pre-processing on tiny seeded checkpoints: GPT2DecModel.process_hf_model_state_dict
+    (models/gpt2/model.py:154-166) and RWKVDecodeModel.process_hf_model_state_dict (models/rwkv/model.py:150-155) are called
+    unbound on stand-in `hf_model` objects that hold the tensors where the HF modules hold them; the ChatGLM2 splits
+    (models/chatglm2/model.py:256-276) are inline in a method that downloads the model, so their few lines are replayed here
+    on the same kind of tensors."""
+    import popart                                       # the numpy stand-in
+    import torch
+    from oracle import c_ref
+    tmp = tempfile.mkdtemp()
+    os.makedirs(os.path.join(tmp, "examples", "ckpt"))
+    os.symlink(c_ref.build(), os.path.join(tmp, "custom_ops.so"))
+    os.chdir(os.path.join(tmp, "examples", "ckpt"))
+    from poptransformer.utils.registry import REGISTRY
+    from poptransformer.utils.tensor_type import TensorType
+    for k, v in dict(num_replicas=1, batch_size=1, batch_per_step=1, model_type="shard", enable_pipeline=False, precision="fp16").items():
+        REGISTRY.register(k, v)
+    REGISTRY.register("tensor_type", TensorType("fp16"))
+    REGISTRY.register("logger", logging.getLogger("poptransformer"))
+    from poptransformer.models.gpt2.model import GPT2DecModel
+    from poptransformer.models.rwkv.model import RWKVDecodeModel
+    g = torch.Generator().manual_seed(41)
+    rnd = lambda *shape: torch.randn(shape, generator=g)
+    out = {}
+    # ---- GPT-2: 2 blocks, n_embd 8, 2 heads; HF Conv1D layout [in, out]
+    n_embd, n_head, n_blocks = 8, 2, 2
+    blocks, hf = [], {}
+    for i in range(n_blocks):
+        t = {"attn.c_attn.weight": rnd(n_embd, 3 * n_embd), "attn.c_attn.bias": rnd(3 * n_embd), "attn.c_proj.weight": rnd(n_embd, n_embd),
+             "mlp.c_fc.weight": rnd(n_embd, 4 * n_embd), "mlp.c_proj.weight": rnd(4 * n_embd, n_embd)}
+        for k, v in t.items():
+            hf[f"transformer.h.{i}.{k}"] = v.clone()
+        blocks.append(types.SimpleNamespace(attn=types.SimpleNamespace(c_attn=types.SimpleNamespace(weight=t["attn.c_attn.weight"], bias=t["attn.c_attn.bias"]),
+                                                                       c_proj=types.SimpleNamespace(weight=t["attn.c_proj.weight"])),
+                                            mlp=types.SimpleNamespace(c_fc=types.SimpleNamespace(weight=t["mlp.c_fc.weight"]),
+                                                                      c_proj=types.SimpleNamespace(weight=t["mlp.c_proj.weight"]))))
+    fake = types.SimpleNamespace(hf_config=types.SimpleNamespace(n_embd=n_embd, n_head=n_head), logger=logging.getLogger("x"),
+                                 hf_model=types.SimpleNamespace(transformer=types.SimpleNamespace(h=blocks)))
+    GPT2DecModel.process_hf_model_state_dict(fake)
+    for k, v in hf.items():
+        out["gpt2_in/" + k] = v.numpy()
+    for i, b in enumerate(blocks):
+        out[f"gpt2_out/transformer.h.{i}.attn.c_attn.weight"] = b.attn.c_attn.weight.numpy().copy()
+        out[f"gpt2_out/transformer.h.{i}.attn.c_attn.bias"] = b.attn.c_attn.bias.numpy().copy()
+        out[f"gpt2_out/transformer.h.{i}.attn.c_proj.weight"] = b.attn.c_proj.weight.numpy().copy()
+        out[f"gpt2_out/transformer.h.{i}.mlp.c_fc.weight"] = b.mlp.c_fc.weight.numpy().copy()
+        out[f"gpt2_out/transformer.h.{i}.mlp.c_proj.weight"] = b.mlp.c_proj.weight.numpy().copy()
+    # ---- RWKV: 5 blocks, rescale_every 2
+    rblocks, rin = [], {}
+    for i in range(5):
+        a, f = rnd(6, 6), rnd(6, 12)
+        rin[f"rwkv.blocks.{i}.attention.output.weight"], rin[f"rwkv.blocks.{i}.feed_forward.value.weight"] = a.clone(), f.clone()
+        rblocks.append(types.SimpleNamespace(attention=types.SimpleNamespace(output=types.SimpleNamespace(weight=a)),
+                                             feed_forward=types.SimpleNamespace(value=types.SimpleNamespace(weight=f))))
+    fake = types.SimpleNamespace(hf_config=types.SimpleNamespace(rescale_every=2), hf_model=types.SimpleNamespace(rwkv=types.SimpleNamespace(blocks=rblocks)))
+    RWKVDecodeModel.process_hf_model_state_dict(fake)
+    for k, v in rin.items():
+        out["rwkv_in/" + k] = v.numpy()
+    for i, b in enumerate(rblocks):
+        out[f"rwkv_out/rwkv.blocks.{i}.attention.output.weight"] = b.attention.output.weight.numpy().copy()
+        out[f"rwkv_out/rwkv.blocks.{i}.feed_forward.value.weight"] = b.feed_forward.value.weight.numpy().copy()
+    # ---- ChatGLM2: hidden 8, 2 kv groups x 2 channels -> qkv rows 8 + 8; MLP 2 x 6 rows (chatglm2/model.py:260-276 replayed)
+    hidden = 8
+    cin = {"transformer.encoder.layers.0.self_attention.query_key_value.weight": rnd(16, hidden),
+           "transformer.encoder.layers.0.self_attention.query_key_value.bias": rnd(16),
+           "transformer.encoder.layers.0.mlp.dense_h_to_4h.weight": rnd(12, hidden),
+           "transformer.encoder.layers.0.mlp.dense_4h_to_h.weight": rnd(hidden, 6)}
+    sd = {k: v.clone() for k, v in cin.items()}
+    for k in list(sd.keys()):
+        if "query_key_value" in k:
+            weight_np = sd.pop(k)
+            weight_1, weight_2 = np.split(weight_np, [hidden], axis=0)
+            sd[k.replace("query_key_value", "query")] = weight_1
+            sd[k.replace("query_key_value", "key_value")] = weight_2
+        if "dense_h_to_4h" in k:
+            weight_np = sd.pop(k)
+            weight_1, weight_2 = weight_np.chunk(2, dim=0)
+            sd[k.replace("dense_h_to_4h", "dense_h_to_4h_1")] = weight_1
+            sd[k.replace("dense_h_to_4h", "dense_h_to_4h_2")] = weight_2
+    for k, v in cin.items():
+        out["chatglm2_in/" + k] = v.numpy()
+    for k, v in sd.items():
+        out["chatglm2_out/" + k] = np.asarray(v)
+    os.chdir(ROOT)
+    np.savez(os.path.join(ROOT, "tests", "golden", name + ".npz"), **out)
+    print(name, "ok:", len(out), "arrays")
+
+
 def run_tp_strategies(name="tp_strategies"):
     """The reference's load-time weight slicing (utils/param_handler/tensor_parallel_strategy.py:21-70, the sharded embedding
     weight of :38-45 and ChatGLM2's rearrange_tp_weights, models/chatglm2/model.py:29-49) on small seeded integer-valued arrays.
@@ -236,7 +324,8 @@ if __name__ == "__main__":
         case = sys.argv[2].split(":")[0]
         run_graph_case(case, sys.argv[3] if len(sys.argv) > 3 else os.path.join(ROOT, "tests", "golden", case + "_graph.json"))
     elif len(sys.argv) > 2:
-        (run_tp_strategies if sys.argv[2] == "tp_strategies" else run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
+        (run_tp_strategies if sys.argv[2] == "tp_strategies" else run_checkpoint_preprocess if sys.argv[2] == "checkpoint_preprocess"
+         else run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
     else:
-        for case in list(CASES) + list(OTHER) + ["tp_strategies", "llama_tiny_int4:graph", "llama_tiny_fp16:graph"]:
+        for case in list(CASES) + list(OTHER) + ["tp_strategies", "checkpoint_preprocess", "llama_tiny_int4:graph", "llama_tiny_fp16:graph"]:
             subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)

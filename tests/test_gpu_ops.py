@@ -297,6 +297,42 @@ def test_kv_cache_pipeline(cuda):
         assert np.array_equal(got.view(np.uint16), exp.view(np.uint16)), f"step {step}"
 
 
+def test_kv_cache_pipeline_last_dim_layout(cuda):
+    """transpose=1: the caches are stored [..., H, L] and shifted along the last dimension (GetBpsKvCacheLastDim); the op hands the
+    result back transposed, so the values equal the plain layout's."""
+    from poptransformer_b200 import ops
+    r = rng(12)
+    B, N, L, H, bps = 2, 3, 9, 8, 2
+    st_o = O.KVCachePipelineState()
+    op = ops.KVCachePipelineOp(max_len=L, max_bps=bps, sequence_axis=2, transpose=1)
+    step_t = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for step in list(range(12)) + [0, 1]:
+        kv = r.standard_normal((B, N, 1, H)).astype(np.float16)
+        step_t.fill_(step)
+        got = ops.kv_cache_pipeline(op, step_t, dev(kv, cuda)).cpu().numpy()
+        exp = O.kv_cache_pipeline(st_o, step, kv, L, bps, 2, 1)
+        assert np.array_equal(got.view(np.uint16), exp.view(np.uint16)), f"step {step}"
+    assert tuple(op.caches.shape) == (bps, B, N, H, L)
+    # the stored layout really is the shifted last dimension: newest token in column 0 of the cache that took the last insert
+    assert np.array_equal(op.caches[1 % bps].cpu().numpy()[..., 0].view(np.uint16), kv[:, :, 0, :].view(np.uint16))
+
+
+def test_random_sample_picks_one_of_the_top_k(cuda):
+    from poptransformer_b200 import ops
+    r = rng(13)
+    x = r.standard_normal((3, 1, 500)).astype(np.float16)
+    g = torch.Generator(device=cuda).manual_seed(0)
+    seen = set()
+    for _ in range(8):
+        ids = ops.random_sample(dev(x, cuda), 4, generator=g).cpu().numpy()
+        assert ids.shape == (3, 1, 1)
+        top4 = O.topk(x, 4)[1]
+        for b in range(3):
+            assert ids[b, 0, 0] in top4[b, 0]
+        seen.add(int(np.nonzero(top4[0, 0] == ids[0, 0, 0])[0][0]))
+    assert len(seen) > 1            # the pick varies with the draws
+
+
 # ------------------------------------------------------------------ fused RoPE + paged append + attention
 @pytest.mark.parametrize("B,N,G,H,L,page,mode", [(1, 4, 4, 128, 40, 16, "llama"), (2, 8, 8, 128, 150, 64, "llama"),
                                                 (2, 4, 4, 64, 70, 32, "gpt2"), (2, 8, 2, 128, 70, 64, "none_gqa"),
