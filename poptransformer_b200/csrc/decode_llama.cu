@@ -1386,7 +1386,8 @@ __global__ void __launch_bounds__(THREADS, 1) llama_step_kernel(const Params p) 
       for (int bb = 0; bb < BMAX; ++bb)
         if (bb == b) esq[bb] += q;
     }
-    if (!TP) {  // this SM's share of sum(x^2) per batch row, published with the progress word (see Params::flag_ssq)
+    {  // this SM's share of sum(x^2) per batch row, published with the progress word (see Params::flag_ssq); the first staging
+       // of the launch uses it on every rank (layer 0 has no partial sums to add)
 #pragma unroll
       for (int b = 0; b < BMAX; ++b) {
         const float t = (b < p.B) ? consumer_sum(c, esq[b]) : 0.f;
