@@ -251,6 +251,29 @@ int pt_kv_reorder_pages(void *pool, const int32_t *page_table, const int32_t *sp
 int pt_kv_reorder_table(int32_t *page_table, int32_t *table_tmp, int32_t *spare_pages, const int32_t *parent,
                         const int32_t *step_dev, int rows, int page_size, int max_pages, void *stream);
 
+/* ---- prompt ingestion ("prefill") attention, Llama architecture ------------------------------------------------------
+ * All tokens of a prompt in one pass: the attention of the reference's first stage, sequence_length = prompt length
+ * (models/base_model.py:358-494; llama2/attention.py:64-114 with the causal mask and stable_mode = True).  qkv is fp16
+ * [batch * n_tokens, 3 * n_head * head_dim] (row b * n_tokens + t holds q | k | v of token t of sequence b, position start + t);
+ * q is rotated in place, rotated k and v are written to the paged cache (layout of pt_kv_append_attn), and out
+ * [batch * n_tokens, n_head * head_dim] receives softmax(q K^T * score_scale + causal mask) V over positions 0 .. start + t.
+ * head_dim 128, page_size 64, no grouped KV heads. */
+typedef struct pt_prefill_attn_args {
+  int batch, n_tokens, start, n_head, head_dim, page_size, max_pages, max_len;
+  float score_scale;
+  void *qkv;
+  const void *rope_sin, *rope_cos;   /* fp16 [max_len, head_dim / 2] */
+  void *pool;
+  const int32_t *page_table;
+  void *out;
+} pt_prefill_attn_args;
+int pt_prefill_attn(const pt_prefill_attn_args *args, void *stream);
+/* Embedding rows of prompt tokens start .. start + n_tokens - 1 of every sequence (out row b * n_tokens + t), and the stop mask of
+ * the reference's loop carry over them: sequence b is marked when ids[b, start + t + 1] == eos_id (models/base_model.py:313-346).
+ * stop_mask may be NULL. */
+int pt_prefill_embed(const void *table, const int32_t *ids, int ids_stride, int batch, int n_tokens, int start, int dim, int vocab,
+                     int eos_id, int32_t *stop_mask, void *out, void *stream);
+
 /* ---- persistent decode step (Llama architecture) ------------------------------------------------
  * One cooperative launch executes a whole iteration of the reference's decode loop body
  * (poptransformer/models/llama2/model.py:162-197, models/base_model.py:313-355) for batch <= 2: embedding, every

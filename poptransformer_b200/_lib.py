@@ -47,6 +47,12 @@ class GemmArgs(ctypes.Structure):
     ]
 
 
+class PrefillAttnArgs(ctypes.Structure):
+    _fields_ = [(n, c_int) for n in ("batch", "n_tokens", "start", "n_head", "head_dim", "page_size", "max_pages", "max_len")] + \
+               [("score_scale", c_float), ("qkv", c_void_p), ("rope_sin", c_void_p), ("rope_cos", c_void_p), ("pool", c_void_p),
+                ("page_table", c_void_p), ("out", c_void_p)]
+
+
 class LlamaLayer(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in ("qkv", "o", "gu", "down", "ln1", "ln2", "pool")]
 
@@ -83,6 +89,8 @@ SIGNATURES = {
     "pt_kv_cache_pipeline": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_void_p]),
     "pt_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "pt_kv_append_attn": (c_int, [ctypes.POINTER(AttnArgs), c_void_p]),
+    "pt_prefill_attn": (c_int, [ctypes.POINTER(PrefillAttnArgs), c_void_p]),
+    "pt_prefill_embed": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_kv_export": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_kv_reorder_pages": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pt_kv_reorder_table": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.environ.get("PT_B200_LIB", os.path.join(HERE, "libpt_b200.so"))   # same override as _lib.LIB_PATH
-SOURCES = ["api.cu", "linear.cu", "attention.cu", "ops.cu", "decode_llama.cu", "decode_llama_short.cu", "gemm_tc.cu"]
+SOURCES = ["api.cu", "linear.cu", "attention.cu", "ops.cu", "decode_llama.cu", "decode_llama_short.cu", "gemm_tc.cu", "prefill.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--threads", "0",
     "-Xcompiler", "-fPIC", "-shared",

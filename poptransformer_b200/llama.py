@@ -4,7 +4,7 @@ Host-side mirror of the reference's LLAMA2DecModel loop body
 (poptransformer/models/llama2/model.py:162-197, llama2/attention.py:64-122, llama2/mlp.py:20-28,
 layers/lm_head.py:47-116, models/base_model.py:313-355): one `step()` is one iteration of the
 reference's on-device Loop, i.e. one token per sequence (prompt tokens are consumed one per step, like
-the reference).  The step is five kernels per layer,
+the reference's one-stage models; `prefill()` ingests them in one pass like its two-stage models).  The step is five kernels per layer,
 
     [RMSNorm ->] fused QKV linear -> RoPE + KV append + attention -> o_proj (+ residual)
     [RMSNorm ->] gate|up linear with SwiGLU epilogue -> down_proj (+ residual)
@@ -20,6 +20,7 @@ One process per GPU; rank r keeps slice r.
 """
 import ctypes
 import math
+from types import SimpleNamespace
 
 import numpy as np
 import torch
@@ -52,10 +53,11 @@ from .tp import KSlice as _KSlice, rows as _rows, row_parallel_int4, row_paralle
 class LlamaDecoder(DecodeLoop):
     def __init__(self, cfg, state_dict, batch, device="cuda", page_size=64, fuse_norm=None, pad_id=None, eos_id=-1,
                  tp_rank=0, tp_size=1, group=None, pdl=True, persistent=None, keep_logits=True, early_stop=False, tp_buffers=None,
-                 wait_limit=0, use_gemm=None):
+                 wait_limit=0, use_gemm=None, prefill=False):
         """tp_buffers: for tp_size > 1, the exchange buffers of all ranks as this process sees them (a list of tp_size int32 CUDA
         tensors of pt_llama_tp_buffer_bytes each, entry tp_rank being local memory, the others peer mappings the caller set up).
         Default: the buffers are allocated as symmetric memory over `group` (torch.distributed).
+        prefill: also keep the weights in the tcgen05 GEMM's tiling so that `prefill()` can ingest a prompt in one pass.
         wait_limit: trip limit of the persistent kernel's polling loops (0 = the library default, about two seconds)."""
         self.cfg, self.batch, self.device = cfg, batch, device
         self._init_loop(device, early_stop)
@@ -104,6 +106,11 @@ class LlamaDecoder(DecodeLoop):
             loc, ks = row_parallel_fp16(w, k_total, r, tp)
             return ops.PackedLinear(ops.W_FP16, loc), ks
 
+        def gemm_weight(keys):
+            ws = [t(k) for k in keys]
+            sc = [t(k + "_scale").reshape(w.shape[0], -1) for k, w in zip(keys, ws)]
+            return ops.GemmWeight(ops.W_INT4, torch.cat(ws, 0), torch.cat(sc, 0), group=(ws[0].shape[1] * 2) // sc[0].shape[1])
+
         self.emb = t("model.embed_tokens.weight").to(torch.float16).contiguous()   # replicated: one row is read per token
         self.layers = []
         for i in range(c.n_layer):
@@ -117,6 +124,26 @@ class LlamaDecoder(DecodeLoop):
                 "o": o, "gu": col_parallel([p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], interleave=True), "down": down,
             })
         self.o_ks, self.down_ks = o_ks, down_ks
+        # Prompt ingestion runs hundreds of rows through every linear: those go to the tcgen05 GEMM, which wants its own tiling of
+        # the weights (a second copy beside the decode kernels' packing when the decode path is not the GEMM itself).
+        self.pf_layers = None
+        if prefill:
+            if not (tp_size == 1 and first_w.dtype == torch.int8 and grp0 % 128 == 0 and c.d_model % 128 == 0 and c.ffn % 128 == 0
+                    and c.head_dim == 128 and page_size == 64):
+                raise ops.PtError("prefill=True needs INT4 weights (group a multiple of 128), one GPU, head_dim 128 and 64-token pages")
+            if self.use_gemm:
+                self.pf_layers = self.layers
+            else:
+                self.pf_layers = []
+                for i in range(c.n_layer):
+                    p = f"model.layers.{i}."
+                    self.pf_layers.append({
+                        "ln1": self.layers[i]["ln1"], "ln2": self.layers[i]["ln2"],
+                        "qkv": gemm_weight([p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"]),
+                        "o": gemm_weight([p + "self_attn.o_proj.weight"]),
+                        "gu": gemm_weight([p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"]),
+                        "down": gemm_weight([p + "mlp.down_proj.weight"])})
+            self._pf_bufs = {}
         self.norm = t("model.norm.weight").contiguous()
         self.vocab_loc = math.ceil(c.vocab / tp)
         head = t("lm_head.weight").to(torch.float16)
@@ -321,6 +348,54 @@ class LlamaDecoder(DecodeLoop):
             ops.gemm(self.h, L["gu"], out=self.gu_out, workspace=self.gemm_ws, error_flag=self.error_flag)
             ops.check(L_.pt_swiglu(ops._ptr(self.gu_out), self.batch, c.ffn, ops._ptr(self.act), self.act.shape[1], ops._stream()), "pt_swiglu")
             ops.gemm(self.act, L["down"], out=self.x, epilogue=ops.EPI_RESIDUAL, residual=self.x, workspace=self.gemm_ws, error_flag=self.error_flag)
+
+    def prefill(self, n_tokens=None, chunk=1024):
+        """Ingests the first `n_tokens` positions of every sequence in one pass (the work of the reference's first stage,
+        models/base_model.py:358-494) instead of one loop iteration per token: their keys and values go to the caches and the step
+        counter moves to `n_tokens`, so the next `step()` is loop iteration `n_tokens` of the token-by-token loop.  Default: one less
+        than the shortest prompt (leading ids that are not the pad id), so that the first decode step processes the last prompt
+        token every sequence has and ragged prompts keep the loop's rule (a pad position takes the generated id).  Call right
+        after `reset()`.  Returns the number of positions ingested.  With `early_stop`, the loop condition is not evaluated over the
+        ingested positions (a batch whose prompts all contain the eos id stops on the first decode step, not inside the prompt)."""
+        if self.pf_layers is None:
+            raise ops.PtError("this decoder was built without prefill=True")
+        c, B = self.cfg, self.batch
+        if n_tokens is None:
+            lead = (self.ids != self.pad_id).to(torch.int32).cumprod(1).sum(1).min()
+            n_tokens = int(lead.item()) - 1
+        n = int(n_tokens)
+        if n <= 0:
+            return 0
+        if n >= c.max_len:
+            raise ops.PtError(f"prefill: n_tokens={n} leaves no decode position (max_len={c.max_len})")
+        L_ = ops._lib.lib()
+        d, f = c.d_model, c.ffn
+        for s0 in range(0, n, chunk):
+            P = min(chunk, n - s0)
+            rows = B * P
+            if rows not in self._pf_bufs:
+                f16 = dict(dtype=torch.float16, device=self.device)
+                self._pf_bufs = {rows: SimpleNamespace(x=torch.empty((rows, d), **f16), h=torch.empty((rows, d), **f16), qkv=torch.empty((rows, 3 * d), **f16),
+                                                       attn=torch.empty((rows, d), **f16), gu=torch.empty((rows, 2 * f), **f16),
+                                                       act=torch.empty((rows, f), **f16), ws=ops.gemm_workspace(rows, max(3 * d, 2 * f), 8, self.device))}
+            w = self._pf_bufs[rows]
+            ops.check(L_.pt_prefill_embed(ops._ptr(self.emb), ops._ptr(self.ids), c.max_len, B, P, s0, d, c.vocab, self.eos_id, ops._ptr(self.stop_mask),
+                                          ops._ptr(w.x), ops._stream()), "pt_prefill_embed")
+
+            def norm(gamma):
+                ops.check(L_.pt_rms_norm(ops._ptr(w.x), None, ops._ptr(gamma), rows, d, c.eps, ops._ptr(w.h), None, ops._stream()), "pt_rms_norm")
+
+            for li, L in enumerate(self.pf_layers):
+                norm(L["ln1"])
+                ops.gemm(w.h, L["qkv"], out=w.qkv, workspace=w.ws, error_flag=self.error_flag)
+                ops.prefill_attn(w.qkv, self.caches[li], B, P, s0, c.n_head, self.score_scale, self.sin, self.cos, out=w.attn)
+                ops.gemm(w.attn, L["o"], out=w.x, epilogue=ops.EPI_RESIDUAL, residual=w.x, workspace=w.ws, error_flag=self.error_flag)
+                norm(L["ln2"])
+                ops.gemm(w.h, L["gu"], out=w.gu, workspace=w.ws, error_flag=self.error_flag)
+                ops.check(L_.pt_swiglu(ops._ptr(w.gu), rows, f, ops._ptr(w.act), f, ops._stream()), "pt_swiglu")
+                ops.gemm(w.act, L["down"], out=w.x, epilogue=ops.EPI_RESIDUAL, residual=w.x, workspace=w.ws, error_flag=self.error_flag)
+        self.step_t.fill_(n)
+        return n
 
     def _enqueue_head(self):
         c = self.cfg

@@ -29,9 +29,10 @@ class DecodeLoop:
         """The device flag handed to the loop-carry kernel (None when the loop always runs max_loop iterations)."""
         return self.done_flag if self.early_stop else None
 
-    def run(self, input_ids, max_loop=None, poll_every=16):
+    def run(self, input_ids, max_loop=None, poll_every=16, prefill=False):
         """Session.run equivalent (poptransformer/sessions.py:47-49): feeds the id container, runs at most `max_loop` loop
-        iterations on the device and returns the reference's anchors {'Loop:0': ids, 'Loop:1': step}."""
+        iterations on the device and returns the reference's anchors {'Loop:0': ids, 'Loop:1': step}.  `prefill=True` (decoders that
+        have `prefill()`): the iterations that only consume prompt tokens are replaced by one pass over the prompt."""
         max_len = self.cfg.max_len
         n = max_len if max_loop is None else int(max_loop)
         if n < 0 or n > max_len:
@@ -39,7 +40,8 @@ class DecodeLoop:
         self.reset(input_ids)
         if self.done_flag is not None:
             self.done_flag.zero_()
-        for i in range(n):
+        first = min(n, self.prefill()) if prefill else 0     # loop iterations the one-pass prompt ingestion stands for
+        for i in range(first, n):
             self.step()
             if self.early_stop and (i + 1) % poll_every == 0 and int(self.done_flag.item()):
                 break

@@ -332,6 +332,22 @@ def kv_append_attn(qkv, step, cache, n_head, rope_mode=ROPE_NONE, softmax_mode=S
     return out
 
 
+def prefill_attn(qkv, cache, batch, n_tokens, start, n_head, score_scale, rope_sin, rope_cos, out=None):
+    """Causal attention over a whole prompt chunk (the reference's sequence_length != 1 attention, llama2/attention.py:64-114):
+    qkv fp16 [batch * n_tokens, 3 * n_head * H], row b * n_tokens + t = position start + t of sequence b.  Rotates q in place,
+    appends rotated k and v to the paged cache and returns softmax(q K^T * scale + causal mask) V, [batch * n_tokens, n_head * H]."""
+    if qkv.shape != (batch * n_tokens, 3 * n_head * cache.head_dim) or cache.n_kv != n_head:
+        raise PtError(f"prefill_attn: qkv {tuple(qkv.shape)} does not match batch={batch} n_tokens={n_tokens} n_head={n_head} (no grouped KV heads)")
+    if out is None:
+        out = torch.empty((batch * n_tokens, n_head * cache.head_dim), dtype=torch.float16, device=qkv.device)
+    a = _lib.PrefillAttnArgs()
+    a.batch, a.n_tokens, a.start, a.n_head, a.head_dim = batch, n_tokens, start, n_head, cache.head_dim
+    a.page_size, a.max_pages, a.max_len, a.score_scale = cache.page_size, cache.max_pages, cache.max_len, score_scale
+    a.qkv, a.rope_sin, a.rope_cos, a.pool, a.page_table, a.out = _ptr(qkv), _ptr(rope_sin), _ptr(rope_cos), _ptr(cache.pool), _ptr(cache.page_table), _ptr(out)
+    check(_lib.lib().pt_prefill_attn(ctypes.byref(a), _stream()), "pt_prefill_attn")
+    return out
+
+
 # ------------------------------------------------------------------------------------------ top-k / beam search
 def topk(x, k, axis=-1):
     """ops.topk (popart.py:135-137) on the last axis: (values, int32 indices), ties -> lowest index."""
