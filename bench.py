@@ -366,6 +366,60 @@ SECONDARY = {
 }
 
 
+def check_secondary(fam, dims, rows, dev, steps=3):
+    """Parity of a secondary workload at the benchmarked WIDTH: the same architecture with every matrix at full size (hidden,
+    FFN, vocabulary, heads) but two blocks, `rows` rows, teacher-forced from step 0 for `steps` steps against the numpy
+    restatement of the reference model (the checker; nothing here is timed).  Returns the share of logits inside the tolerance
+    (fp16: rtol/atol 2e-2; FP8 linears: 5e-2), the worst difference and the share of greedy ids equal or tied within it."""
+    import numpy as np
+    import torch
+    from poptransformer_b200 import chatglm2, gpt2, rwkv, synth
+    d2 = dict(dims, n_layer=2)
+    max_len = 16
+    if fam.startswith("gpt2"):
+        from oracle import gpt2_np
+        sd = synth.gpt2_state_dict(**d2, seed=0, device="cpu")
+        dec = gpt2.GPT2Decoder(gpt2.GPT2Config(**d2, max_len=max_len), sd, rows, device=dev)
+        orc = gpt2_np.GPT2Oracle(gpt2_np.GPT2Config(**d2, max_len=max_len), {k: v.numpy() for k, v in sd.items()}, rows)
+        tol = 2e-2
+    elif fam == "chatglm2":
+        from oracle import chatglm2_np
+        sd = synth.chatglm2_state_dict(**d2, seed=0, device="cpu", precision="fp8")
+        dec = chatglm2.ChatGLM2Decoder(chatglm2.ChatGLM2Config(**d2, max_len=max_len, precision="fp8"), sd, rows, device=dev)
+        np_sd = {k: (v.numpy() if hasattr(v, "numpy") else v) for k, v in sd.items()}
+        orc = chatglm2_np.ChatGLM2Oracle(chatglm2_np.ChatGLM2Config(**d2, max_len=max_len, precision="fp8"), np_sd, rows)
+        tol = 5e-2
+    else:
+        from oracle import rwkv_np
+        sd = synth.rwkv_state_dict(**d2, seed=0, device="cpu")
+        dec = rwkv.RWKVDecoder(rwkv.RWKVConfig(**d2, max_len=max_len), sd, rows, device=dev)
+        orc = rwkv_np.RWKVOracle(rwkv_np.RWKVConfig(**d2, max_len=max_len), {k: v.numpy() for k, v in sd.items()}, rows)
+        tol = 2e-2
+    ids = synth.prompt_ids(rows, max_len, max_len, d2["vocab"], dec.pad_id, seed=3)
+    dec.reset(ids)
+    orc.reset()
+    inside, worst, rms_rel, id_ok, n_ids = [], 0.0, 0.0, 0, 0
+    for step in range(steps):
+        dec.step()
+        got = dec.logits.float().cpu().numpy().reshape(rows, -1)
+        exp = (orc.logits(ids[:, step].numpy()) if fam == "rwkv" else orc.logits(ids[:, step].numpy(), step))[0]
+        exp = np.asarray(exp, dtype=np.float32).reshape(rows, -1)
+        err = np.abs(got - exp)
+        inside.append(float(np.mean(err <= tol + tol * np.abs(exp))))
+        worst = max(worst, float(err.max()))
+        rms_rel = max(rms_rel, float(np.sqrt((err ** 2).mean()) / np.sqrt((exp ** 2).mean())))
+        gid = got.argmax(1)
+        for b in range(rows):
+            n_ids += 1
+            id_ok += int(exp[b].max() - exp[b][gid[b]] <= (4 * tol if fam == "chatglm2" else tol))
+    if int(dec.error_flag.item()) != 0:
+        raise SystemExit("device-side bounded wait gave up during the parity check")
+    del dec
+    torch.cuda.empty_cache()
+    return {"layers": 2, "rows": rows, "steps": steps, "tol": tol, "logits_within_tol": min(inside), "max_abs_diff": worst, "rms_diff_over_rms_logit": rms_rel,
+            "ids_equal_or_tied": id_ok / n_ids, "against": "numpy restatement of the reference model, full-width matrices, from step 0"}
+
+
 def run_secondary(args):
     """One of SECONDARY on cuda:0: state as after the prompt (seeded ids, random KV pages / WKV states), one CUDA-graph replay
     per decode step, CUDA events around K steps.  The JSON line is marked `secondary` and carries a step-level roofline: the
@@ -404,6 +458,15 @@ def run_secondary(args):
         dtype = "fp16 (float32 WKV states)"
     del sd
     torch.cuda.empty_cache()
+    check = None
+    if args.check_ids > 0:
+        check = check_secondary(fam, dims, rows, dev)
+        # fp16 families: the element-wise band.  FP8 (E4M3 casts amplify one-ulp differences to a few per cent within two blocks,
+        # and the band's absolute part does not grow with the logits of a 4096-wide model): the rms difference relative to the
+        # logits' rms, and greedy ids inside four times the band.
+        bad = (check["rms_diff_over_rms_logit"] > 0.08) if fam == "chatglm2" else (check["logits_within_tol"] < 0.999 or check["max_abs_diff"] > 4 * check["tol"])
+        if bad or check["ids_equal_or_tied"] < 1.0:
+            raise SystemExit(f"{args.workload}: parity check at the benchmarked width failed, no number is reported: {json.dumps(check)}")
     ids_host = synth.prompt_ids(rows, prompt, max_len, cfg.vocab, dec.pad_id, seed=0).pin_memory()
     gen = torch.Generator(device=dev).manual_seed(1)
     for kc in getattr(dec, "caches", []):
@@ -492,6 +555,7 @@ def run_secondary(args):
         "e2e": {"value": batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": ids_host.numel() * 4 / K,
                 "d2h_bytes_per_step": ids_host.numel() * 4 / K},
         "gpu_launches": int(launches_per_step * K),
+        "parity_check": check,
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                      "kernel": f"all {launches_per_step} launches of one step (per-op kernels, one CUDA graph)", "peak_source": peak_src,
                      "launch_us": ms_step * 1e3, "bytes_per_launch": step_bytes},

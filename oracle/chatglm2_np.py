@@ -65,7 +65,8 @@ class ChatGLM2Oracle:
         if cols is not None:
             w = w[:, cols]
         if self.cfg.precision == "fp8":
-            y = O.fp8_matmul(O.cast_fp8(x, self.cfg.act_scales[site]), np.ascontiguousarray(w.T), self.cfg.act_scales[site], float(self.sd[key + "_scale"]))
+            a = float(self.sd[key + "_act_scale"]) if (key + "_act_scale") in self.sd else self.cfg.act_scales[site]   # per tensor, else per site
+            y = O.fp8_matmul(O.cast_fp8(x, a), np.ascontiguousarray(w.T), a, float(self.sd[key + "_scale"]))
         else:
             y = O.matmul_f16(x, np.asarray(w, dtype=F16).T)
         if not bias:

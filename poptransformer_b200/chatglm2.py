@@ -62,13 +62,18 @@ class ChatGLM2Decoder(DecodeLoop):
         dev, fp8 = device, c.precision == "fp8"
         t = lambda k: state_dict[k].to(dev)
 
-        def packed(keys, interleave=False, pick=None):
+        def packed(keys, site, interleave=False, pick=None):
             ws = [t(k) if pick is None or pick[j] is None else pick[j](t(k)) for j, k in enumerate(keys)]
             if fp8:
                 scales = {float(state_dict[k + "_scale"]) for k in keys}
-                if len(scales) != 1:
-                    raise ops.PtError("fused FP8 linears need one common weight scale")
-                return ops.PackedLinear(ops.W_FP8, torch.cat(ws, 0).contiguous(), w_scale=scales.pop(), interleave_gate_up=interleave)
+                # activation scale of the tensor (the reference casts the input with the scale stored beside the weight,
+                # precision_strategy.py:62-66); `<key>_act_scale` in the checkpoint, else the configuration's value for the site
+                acts = {float(state_dict[k + "_act_scale"]) if (k + "_act_scale") in state_dict else float(c.act_scales[site]) for k in keys}
+                if len(scales) != 1 or len(acts) != 1:
+                    raise ops.PtError("fused FP8 linears need one common weight scale and one common activation scale")
+                pl = ops.PackedLinear(ops.W_FP8, torch.cat(ws, 0).contiguous(), w_scale=scales.pop(), interleave_gate_up=interleave)
+                pl.act_scale = acts.pop()
+                return pl
             return ops.PackedLinear(ops.W_FP16, torch.cat(ws, 0).to(torch.float16).contiguous(), interleave_gate_up=interleave)
 
         self.emb = t("transformer.embedding.word_embeddings.weight").to(torch.float16).contiguous()
@@ -80,15 +85,15 @@ class ChatGLM2Decoder(DecodeLoop):
             p = f"transformer.encoder.layers.{i}."
             self.layers.append({
                 "ln1": t(p + "input_layernorm.weight").contiguous(), "ln2": t(p + "post_attention_layernorm.weight").contiguous(),
-                "qkv": packed([p + "self_attention.query.weight", p + "self_attention.key_value.weight"], pick=[q_rows, None]),
+                "qkv": packed([p + "self_attention.query.weight", p + "self_attention.key_value.weight"], "norm", pick=[q_rows, None]),
                 "b_qkv": torch.cat([t(p + "self_attention.query.bias")[mine], t(p + "self_attention.key_value.bias")]).to(torch.float16).contiguous(),
-                "dense": packed([p + "self_attention.dense.weight"], pick=[lambda w: w[:, mine]]),
-                "gu": packed([p + "mlp.dense_h_to_4h_1.weight", p + "mlp.dense_h_to_4h_2.weight"], interleave=True, pick=[start, start]),
-                "down": packed([p + "mlp.dense_4h_to_h.weight"], pick=[lambda w: w[:, r * self.f_loc:(r + 1) * self.f_loc]]),
+                "dense": packed([p + "self_attention.dense.weight"], "attn", pick=[lambda w: w[:, mine]]),
+                "gu": packed([p + "mlp.dense_h_to_4h_1.weight", p + "mlp.dense_h_to_4h_2.weight"], "norm", interleave=True, pick=[start, start]),
+                "down": packed([p + "mlp.dense_4h_to_h.weight"], "mlp", pick=[lambda w: w[:, r * self.f_loc:(r + 1) * self.f_loc]]),
             })
         self.norm = t("transformer.encoder.final_layernorm.weight").contiguous()
         self.vocab_loc = -(-c.vocab // tp) if tp > 1 else c.vocab
-        self.head = packed(["transformer.output_layer.weight"], pick=[(lambda w: vocab_rows(w, r, tp)[0]) if tp > 1 else None])
+        self.head = packed(["transformer.output_layer.weight"], "norm", pick=[(lambda w: vocab_rows(w, r, tp)[0]) if tp > 1 else None])
         self.sin, self.cos = chatglm2_rope_tables(c.max_len, c.head_dim, dev)
         self.score_scale = float(np.float16(1.0 / np.sqrt(c.head_dim)))
         B, d = batch, c.d_model
@@ -123,7 +128,7 @@ class ChatGLM2Decoder(DecodeLoop):
         fp8 = pl.wfmt == ops.W_FP8
         pro = (ops.PRO_RMSNORM_CAST_FP8 if fp8 else ops.PRO_RMSNORM) if gamma is not None else (ops.PRO_CAST_FP8 if fp8 else ops.PRO_NONE)
         a = ops.linear_args(x, pl, out, prologue=pro, epilogue=epilogue, gamma=gamma, eps=self.cfg.eps,
-                            act_scale=self.cfg.act_scales[site] if fp8 else 0.0, bias=bias, residual=residual, workspace=self.lin_ws,
+                            act_scale=pl.act_scale if fp8 else 0.0, bias=bias, residual=residual, workspace=self.lin_ws,
                             error_flag=self.error_flag, pdl=self.pdl_linear)
         ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
 

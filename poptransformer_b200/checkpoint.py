@@ -99,13 +99,17 @@ def quantize_linears_int4(sd, group=128, match=_LINEAR, skip=("embed", "lm_head"
     return out
 
 
-def quantize_linears_fp8(sd, match=_LINEAR, skip=("embed", "wte", "wpe", "word_embeddings")):
-    """Linear weights -> E4M3 bytes + a float32 per-tensor scale amax / 448 under `<key>_scale`."""
+def quantize_linears_fp8(sd, match=_LINEAR, skip=("embed", "wte", "wpe", "word_embeddings"), act_amax=None):
+    """Linear weights -> E4M3 bytes + a float32 per-tensor scale amax / 448 under `<key>_scale`.  act_amax: optional
+    {weight key: largest input magnitude seen in calibration}; stored as the tensor's activation scale `<key>_act_scale`
+    = amax / 448 (linears that share their input must be given the same value)."""
     out = {}
     for k, v in sd.items():
         if v.ndim == 2 and match.search(k) and not any(s in k for s in skip) and v.dtype in (torch.float16, torch.float32, torch.bfloat16):
             q, s = quantize_fp8(v)
             out[k], out[k + "_scale"] = q, torch.tensor(s, dtype=torch.float32)
+            if act_amax and k in act_amax:
+                out[k + "_act_scale"] = torch.tensor(float(act_amax[k]) / 448.0, dtype=torch.float32)
         else:
             out[k] = v
     return out

@@ -72,21 +72,28 @@ def gpt2_state_dict(n_layer, d_model, n_head, vocab, n_positions, seed=0, device
 def chatglm2_state_dict(n_layer, d_model, n_head, n_group, ffn, vocab, seed=0, device="cpu", precision="fp16"):
     """ChatGLM2 architecture with the reference's key names after its checkpoint pre-processing (chatglm2/model.py:256-289:
     query / key_value and the two halves of dense_h_to_4h split).  precision "fp8" stores every transformer linear and the output
-    layer as E4M3 bytes plus a float `<key>_scale`; linears that the decoder fuses (query | key_value, the two MLP halves) are
+    layer as E4M3 bytes plus a float `<key>_scale` and a per-tensor activation scale `<key>_act_scale`; linears that the decoder fuses (query | key_value, the two MLP halves) are
     quantised with one common scale."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     hs = d_model // n_head
     sd = {"transformer.embedding.word_embeddings.weight": _normal((vocab, d_model), gen, device)}
 
-    def lin(group):
+    n_lin = [0]
+
+    def lin(group, act_range):
         ws = {k: _normal(shape, gen, device) for k, shape in group}
         if precision == "fp8":
             amax = max(float(w.float().abs().max()) for w in ws.values())
             scale = amax / 448.0
+            # per-tensor activation scale `<key>_act_scale`: the largest input magnitude the linear is calibrated for / 448, a
+            # different value for every tensor (the same for linears that share their input)
+            act = act_range * (1.0, 1.25, 0.8)[n_lin[0] % 3] / 448.0
+            n_lin[0] += 1
             for k, w in ws.items():
                 sd[k] = torch.clamp(w.float() / scale, -448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
                 sd[k + "_scale"] = scale
+                sd[k + "_act_scale"] = act
         else:
             sd.update(ws)
 
@@ -94,14 +101,14 @@ def chatglm2_state_dict(n_layer, d_model, n_head, n_group, ffn, vocab, seed=0, d
         p = f"transformer.encoder.layers.{i}."
         sd[p + "input_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
         sd[p + "post_attention_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
-        lin([(p + "self_attention.query.weight", (d_model, d_model)), (p + "self_attention.key_value.weight", (2 * n_group * hs, d_model))])
+        lin([(p + "self_attention.query.weight", (d_model, d_model)), (p + "self_attention.key_value.weight", (2 * n_group * hs, d_model))], 8.0)
         sd[p + "self_attention.query.bias"] = _normal((d_model,), gen, device)
         sd[p + "self_attention.key_value.bias"] = _normal((2 * n_group * hs,), gen, device)
-        lin([(p + "self_attention.dense.weight", (d_model, d_model))])
-        lin([(p + "mlp.dense_h_to_4h_1.weight", (ffn, d_model)), (p + "mlp.dense_h_to_4h_2.weight", (ffn, d_model))])
-        lin([(p + "mlp.dense_4h_to_h.weight", (d_model, ffn))])
+        lin([(p + "self_attention.dense.weight", (d_model, d_model))], 2.0)
+        lin([(p + "mlp.dense_h_to_4h_1.weight", (ffn, d_model)), (p + "mlp.dense_h_to_4h_2.weight", (ffn, d_model))], 8.0)
+        lin([(p + "mlp.dense_4h_to_h.weight", (d_model, ffn))], 1.0)
     sd["transformer.encoder.final_layernorm.weight"] = (1.0 + _normal((d_model,), gen, device).float()).to(torch.float16)
-    lin([("transformer.output_layer.weight", (vocab, d_model))])
+    lin([("transformer.output_layer.weight", (vocab, d_model))], 8.0)
     return sd
 
 

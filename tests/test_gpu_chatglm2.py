@@ -1,6 +1,7 @@
 """GPU parity of the ChatGLM2 decode loop (multi-query attention, interleaved RoPE, fp16 softmax, fused RMSNorm prologues,
 fp16 and FP8-E4M3 linears) against the numpy restatement of the reference model (oracle/chatglm2_np.py).
-Tolerances: rtol / atol 2e-2 on fp16 logits, 5e-2 with FP8 linears."""
+Tolerances: rtol / atol 2e-2 on fp16 logits; with FP8 linears bit-exact where the arithmetic coincides and the 5e-2 band
+applied statistically elsewhere (see the comment in the test)."""
 import numpy as np
 import pytest
 
@@ -36,14 +37,37 @@ def test_chatglm2_logits_teacher_forced(cuda, batch, precision, tol):
         if step % 5 == 0 or step == max_len - 1:
             exp = exp.astype(np.float32)
             if precision == "fp8":
-                # An fp16 difference of one ulp in front of an E4M3 cast can move that activation to the neighbouring code (up to
-                # 12.5 % of its value), and such flips stay in the KV cache, so a few logits leave the band as the context grows;
-                # require 98 % inside it and bound the rest.
+                # E4M3 casts amplify differences: a relative difference delta between two implementations' fp16 activations moves
+                # a share delta / 6 % of them to the neighbouring E4M3 code (6-12 % of their value), so the next linear's outputs
+                # differ by about sqrt(delta / 0.06) * 0.09 -- larger than delta below a few per cent.  Measured on B200: when the
+                # arithmetic coincides the logits are bit-identical (test_chatglm2_fp8_bit_exact_where_the_arithmetic_coincides);
+                # one fp16 ulp in one head's attention output (the reference rounds each probability to fp16, the kernel
+                # normalises in fp32) becomes 2 % rms in the same block's MLP activations and the difference settles at 3-5 % of
+                # the logits' rms from then on.  So the 5e-2 band holds for all but about 1 % of the logits: require 98 % inside
+                # it, bound the worst by four times the band and the rms difference by 8 % of the logits' rms.
                 err = np.abs(got - exp)
                 assert np.mean(err <= tol + tol * np.abs(exp)) >= 0.98 and err.max() <= 4 * tol, f"step {step}: max {err.max()}"
+                assert np.sqrt((err ** 2).mean()) <= 0.08 * np.sqrt((exp ** 2).mean()), f"step {step}: rms difference {np.sqrt((err ** 2).mean())}"
             else:
                 np.testing.assert_allclose(got, exp, rtol=tol, atol=tol, err_msg=f"step {step}")
     assert dec.error_flag.item() == 0
+
+
+def test_chatglm2_fp8_bit_exact_where_the_arithmetic_coincides(cuda):
+    """First step of a fresh sequence (attention over one token) with a configuration in which the reference's fp16
+    probability exp(s) * fp16(1 / exp(s)) is exactly 1 for every head: every cast, FP8 product sum, bias, SwiGLU and residual of
+    two blocks and the head must then reproduce the restatement bit for bit, with per-tensor activation scales that differ from
+    tensor to tensor.  Any change of a rounding point in the FP8 path fails this."""
+    from poptransformer_b200 import synth
+    dec, orc = _setup(cuda, 2, 8, "fp8")
+    scales = {float(v) for k, v in orc.sd.items() if k.endswith("_act_scale")}
+    assert len(scales) >= 5, "the synthetic checkpoint carries per-tensor activation scales"
+    ids = synth.prompt_ids(2, 8, 8, SMALL["vocab"], dec.pad_id, seed=1)
+    dec.reset(ids)
+    orc.reset()
+    dec.step()
+    exp, _ = orc.logits(ids[:, 0].numpy(), 0)
+    np.testing.assert_array_equal(dec.logits.cpu().numpy(), np.asarray(exp, dtype=np.float16))
 
 
 def test_chatglm2_greedy_stream(cuda):
