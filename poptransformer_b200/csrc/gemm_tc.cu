@@ -616,8 +616,10 @@ extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
   // k-slices: fill the GPU when there are few tiles, but keep at least 8 k-blocks per CTA
   int ksplit = a->ksplit;
   if (ksplit <= 0) {
-    ksplit = std::max(1, sm_count() / (n_tiles * m_tiles));
+    ksplit = std::max(1, (p.mb <= 64 ? 2 : 1) * sm_count() / (n_tiles * m_tiles));   // two CTAs fit an SM up to 64 activation rows
     ksplit = std::max(1, std::min(ksplit, p.n_kb / 8));
+    ksplit = std::min(ksplit, 8);                                           // what pt_gemm_workspace_bytes is usually asked for ...
+    while (ksplit > 1 && pt_gemm_workspace_bytes(a->m, a->n_out, ksplit) > a->workspace_bytes) --ksplit;   // ... and never more than the caller's workspace holds
   }
   ksplit = std::max(1, std::min(ksplit, p.n_kb));
   p.kb_per_split = ceil_div(p.n_kb, ksplit);
@@ -639,7 +641,14 @@ extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
 
   const uint32_t b_bytes = (uint32_t)p.mb * tc::BKB;
   const uint32_t stage_bytes = tc::A_TILE + ((b_bytes + 1023u) & ~1023u);
-  const uint32_t budget = 200u * 1024u;
+  // Up to 64 activation rows a stage is small, and what limits the kernel is the one thread per CTA that issues the MMAs (about
+  // 75 cycles per tcgen05.mma whatever its N): two CTAs per SM (half the shared memory each) issue side by side.  Measured on
+  // B200, FP8 65024 x 4096 at 8 / 32 rows: 63 / 66 us with one CTA per SM, 45 / 47 us with two.
+#ifndef PT_TC_BUDGET_SMALL_KB
+#define PT_TC_BUDGET_SMALL_KB 100
+#endif
+  const bool small = p.mb <= 64;
+  const uint32_t budget = (small ? PT_TC_BUDGET_SMALL_KB : 200) * 1024u;
   size_t smem;
   if (int4) {
     p.stages = (int)std::min<uint32_t>(4, (budget - 8 * tc::RAW_TILE) / stage_bytes);
