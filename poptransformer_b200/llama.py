@@ -77,12 +77,13 @@ class LlamaDecoder(DecodeLoop):
         def t(key):
             return state_dict[key].to(dev)
 
-        # More than 32 rows on one GPU with INT4 weights (beyond the skinny-matmul kernels' range): the transformer linears run on
-        # the tcgen05 GEMM, weights tiled once.  (Measured on B200 at 16 and 32 rows the skinny-matmul kernel is as fast or faster.)
+        # More than 16 rows on one GPU with INT4 weights: the transformer linears run on the tcgen05 GEMM, weights tiled once (beyond
+        # 32 rows it is the only path).  Measured on B200, 7B width, 8 blocks: 16 rows 1.54 ms with the skinny-matmul kernels against
+        # 1.74 ms with the GEMM; 24 rows 2.44 against 2.02 ms; 32 rows 2.87 against 2.25 ms.
         first_w = state_dict["model.layers.0.self_attn.q_proj.weight"]
         grp0 = (first_w.shape[1] * 2) // max(1, state_dict["model.layers.0.self_attn.q_proj.weight_scale"].numel() // first_w.shape[0]) \
             if first_w.dtype == torch.int8 else 0
-        self.use_gemm = ((batch > 32 or use_gemm is True) and use_gemm is not False and tp_size == 1 and first_w.dtype == torch.int8 and grp0 % 128 == 0 and persistent is not True
+        self.use_gemm = ((batch > 16 or use_gemm is True) and use_gemm is not False and tp_size == 1 and first_w.dtype == torch.int8 and grp0 % 128 == 0 and persistent is not True
                          and c.d_model % 128 == 0 and c.ffn % 128 == 0)
 
         def col_parallel(keys, interleave=False):
@@ -284,6 +285,15 @@ class LlamaDecoder(DecodeLoop):
             torch.distributed.all_reduce(tns, group=self.group)
 
     def _norm_linear(self, x, gamma, pl, out, epilogue=ops.EPI_STORE, out_ld=0):
+        if x.shape[0] > 32:
+            # beyond the skinny-matmul kernels' 32 rows (the fp16 LM head of a large batch, whose transformer linears run on the
+            # GEMM): normalise once, then the linear in blocks of 32 rows
+            L = ops._lib.lib()
+            ops.check(L.pt_rms_norm(ops._ptr(x), None, ops._ptr(gamma), x.shape[0], x.shape[1], self.cfg.eps, ops._ptr(self.h), None,
+                                    ops._stream()), "pt_rms_norm")
+            for r0 in range(0, x.shape[0], 32):
+                ops.linear(self.h[r0:r0 + 32], pl, out[r0:r0 + 32], epilogue=epilogue, workspace=self.lin_ws, out_ld=out_ld, pdl=self.pdl)
+            return
         if self.fuse_norm:
             ops.linear(x, pl, out, prologue=ops.PRO_RMSNORM, gamma=gamma, eps=self.cfg.eps, epilogue=epilogue, workspace=self.lin_ws,
                        out_ld=out_ld, pdl=self.pdl)

@@ -25,10 +25,11 @@ def _setup(cuda, batch, max_len, int4_group, seed=0, persistent=None, use_gemm=N
 
 
 @pytest.mark.parametrize("batch,int4_group,persistent", [(1, 128, True), (2, 128, True), (1, 128, False), (2, 0, False), (1, 256, False),
-                                                        (16, 128, False), (16, 128, "gemm")])
+                                                        (16, 128, False), (16, 128, "gemm"), (40, 128, "gemm")])
 def test_logits_teacher_forced(cuda, batch, int4_group, persistent):
     """persistent=True: the whole-step kernel; False: the per-op kernels; "gemm": the per-op path with the transformer linears on the
-    tcgen05 GEMM (the path of more than 32 rows, forced here at 16).  All against the oracle."""
+    tcgen05 GEMM (the path of more than 16 rows, forced at 16; at 40 rows it is the only path and the fp16 LM head runs in blocks of
+    32 rows).  All against the oracle."""
     from poptransformer_b200 import synth
     max_len = 72 if persistent is True else 40          # more than one KV page for the persistent kernel
     gemm = persistent == "gemm"

@@ -36,7 +36,7 @@ def checkpoint(cuda):
 @pytest.mark.parametrize("batch,persistent", [(1, True), (2, True), (1, False), (16, False), (16, "gemm")])
 def test_full_width_teacher_forced(cuda, checkpoint, batch, persistent):
     """persistent True: the whole-step kernel; False: the per-op kernels; "gemm": per-op with the transformer linears on the tcgen05
-    GEMM (the path of more than 32 rows, forced here at 16)."""
+    GEMM (the path of more than 16 rows, forced here at 16)."""
     from poptransformer_b200 import llama, synth
     sd, sd_np = checkpoint
     gemm = persistent == "gemm"
