@@ -583,9 +583,15 @@ extern "C" int pt_gemm_repack(int wfmt, const void *w, int n_out, int k_in, void
   return PT_OK;
 }
 
+// k-slice workspace layout: [arrival counters, kGemmCounterBytes][partial sums].  The counter region has ONE size for every
+// shape, so that GEMMs of different widths can share a workspace: with a shape-dependent offset the partial sums of a narrow
+// GEMM (o_proj) would land where a wide one (q|k|v) expects zeroed counters.  16384 counters: one per (128-row weight tile,
+// block of activation rows); a shape with more tiles than that runs without k-slices when the split is automatic.
+constexpr size_t kGemmCounterBytes = 65536;
+constexpr size_t kGemmMaxCounters = kGemmCounterBytes / sizeof(int);
+
 extern "C" size_t pt_gemm_workspace_bytes(int m, int n_out, int max_ksplit) {
-  const size_t tiles = (size_t)ceil_div(n_out, tc::BM) * (size_t)ceil_div(m, 16);
-  return ((tiles * sizeof(int) + 255) / 256) * 256 + (size_t)max_ksplit * m * n_out * sizeof(float);
+  return kGemmCounterBytes + (size_t)max_ksplit * m * n_out * sizeof(float);
 }
 
 extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
@@ -620,6 +626,7 @@ extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
     ksplit = std::max(1, std::min(ksplit, p.n_kb / 8));
     ksplit = std::min(ksplit, 8);                                           // what pt_gemm_workspace_bytes is usually asked for ...
     while (ksplit > 1 && pt_gemm_workspace_bytes(a->m, a->n_out, ksplit) > a->workspace_bytes) --ksplit;   // ... and never more than the caller's workspace holds
+    if ((size_t)n_tiles * m_tiles > kGemmMaxCounters) ksplit = 1;
   }
   ksplit = std::max(1, std::min(ksplit, p.n_kb));
   p.kb_per_split = ceil_div(p.n_kb, ksplit);
@@ -634,9 +641,10 @@ extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
   if (p.ksplit > 1) {
     const size_t need = pt_gemm_workspace_bytes(a->m, a->n_out, p.ksplit);
     PT_REQUIRE(a->workspace && a->workspace_bytes >= need, "pt_gemm: %d k-slices need %zu workspace bytes, got %zu", p.ksplit, need, a->workspace_bytes);
-    const size_t tiles = (size_t)ceil_div(a->n_out, tc::BM) * (size_t)ceil_div(a->m, 16);
+    PT_REQUIRE((size_t)n_tiles * m_tiles <= kGemmMaxCounters, "pt_gemm: %d x %d tiles exceed the %zu arrival counters of a k-slice workspace", n_tiles,
+               m_tiles, kGemmMaxCounters);
     p.counters = (int *)a->workspace;
-    p.partial = (float *)((char *)a->workspace + ((tiles * sizeof(int) + 255) / 256) * 256);
+    p.partial = (float *)((char *)a->workspace + kGemmCounterBytes);
   }
 
   const uint32_t b_bytes = (uint32_t)p.mb * tc::BKB;

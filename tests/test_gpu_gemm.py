@@ -69,6 +69,29 @@ def test_gemm_int4(cuda, n, k, group, m):
         _check(got, exp)
 
 
+def test_gemm_widths_share_one_workspace(cuda):
+    """GEMMs of different widths take their k-slice counters from one workspace, as the layers of a decoder do: a narrow one (32
+    weight tiles, eight k-slices), then a wide one (96 tiles, three k-slices), twice over.  The narrow GEMM's partial sums must not
+    land where the wide one counts its arrivals."""
+    from poptransformer_b200 import ops
+    r = np.random.default_rng(77)
+    m, k = 16, 4096
+    x = r.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    cases = []
+    for n in (4096, 12288):
+        packed = r.integers(-128, 128, size=(n, k // 2), dtype=np.int8)
+        scale = (r.random((n, k // 128), dtype=np.float32) * 0.004 + 0.004).astype(np.float16)
+        exp = x.astype(np.float32) @ O.int4_to_half(packed, scale, axis=1, group=128).astype(np.float32)
+        cases.append((ops.GemmWeight(ops.W_INT4, dev(packed, cuda), dev(scale, cuda), group=128), exp))
+    ws = ops.gemm_workspace(m, 12288, 8, cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for _ in range(2):
+        for gw, exp in cases:
+            got = ops.gemm(dev(x, cuda), gw, workspace=ws, error_flag=err).cpu().numpy().astype(np.float32)
+            assert int(err.item()) == 0
+            _check(got, exp)
+
+
 def test_gemm_more_rows_than_one_tile_and_residual(cuda):
     """300 activation rows (two row tiles of the kernel, the second ragged), a width that is no multiple of 128, residual epilogue."""
     from poptransformer_b200 import ops
