@@ -197,6 +197,18 @@ int pt_kv_cache(const int32_t *step_dev, const void *kv_new, void *cache, void *
 int pt_kv_cache_pipeline(const int32_t *step_dev, const void *kv_new, void *caches, void *out,
                          int max_bps, int64_t outer, int max_len, int step_len, int64_t inner,
                          void *stream);
+/* The two ops with 8-bit storage, the `fp8` attribute (customized.py:32; CastToUint8 / CastUint8ToFP16,
+ * custom_ops/kv_cache.cpp:43-75, applied at :100-104 and :183-185; kv_cache_pipeline.cpp:386-388,
+ * :437-439): kv_new (fp16) is cast to bytes before the shifted insert, the persistent caches hold bytes
+ * ([outer, max_len, inner] / [max_bps, outer, max_len, inner] uint8) and `out` is the selected cache
+ * cast back to fp16 [outer, max_len, inner].  The reference casts with Graphcore's F143 format; here the
+ * bytes are OCP E4M3 (round to nearest even, saturating) of kv_new / scale, and out = fp16(decode * scale).
+ * Bit-exact against that definition.  The shift is done in place: no scratch. */
+int pt_kv_cache_fp8(const int32_t *step_dev, const void *kv_new, void *cache, void *out, float scale,
+                    int64_t outer, int max_len, int step_len, int64_t inner, void *stream);
+int pt_kv_cache_pipeline_fp8(const int32_t *step_dev, const void *kv_new, void *caches, void *out,
+                             float scale, int max_bps, int64_t outer, int max_len, int step_len,
+                             int64_t inner, void *stream);
 
 /* ---- paged KV cache + fused decode attention ---------------------------------------------
  * Replaces, for one new token per sequence, the chain RoPE -> ops.kv_cache -> matmul(q,K^T) ->

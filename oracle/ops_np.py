@@ -114,11 +114,17 @@ class KVCacheState:
         self.cache = None
 
 
-def kv_cache(state, step, kv, max_len, sequence_axis, step_len=1):
+def kv_cache(state, step, kv, max_len, sequence_axis, step_len=1, fp8=False, fp8_scale=1.0):
     """KVCacheOpx::grow (custom_ops/kv_cache.cpp:94-187): clone = 0 if step == 0
     else cache (:118-124); cache = concat(input, clone[: max_len - step_len])
-    along sequence_axis (:126-132); returns the whole cache (newest first)."""
+    along sequence_axis (:126-132); returns the whole cache (newest first).
+    fp8: the input is cast to 8-bit floats first (:100-104), the cache holds the
+    bytes and the result is cast back to fp16 (:183-185) -- here E4M3 bytes of
+    kv / fp8_scale and fp16(decode * fp8_scale) in place of the F143 format."""
     kv = np.asarray(kv)
+    if fp8:
+        bits = kv_cache(state, step, cast_fp8(kv, fp8_scale), max_len, sequence_axis, step_len)
+        return f16(e4m3_decode(bits) * F32(fp8_scale))
     shape = list(kv.shape)
     assert shape[sequence_axis] == step_len
     shape[sequence_axis] = max_len
@@ -137,7 +143,7 @@ class KVCachePipelineState:
         self.caches = None
 
 
-def kv_cache_pipeline(state, step, kv, max_len, max_bps, sequence_axis, step_len=1):
+def kv_cache_pipeline(state, step, kv, max_len, max_bps, sequence_axis, step_len=1, fp8=False, fp8_scale=1.0):
     """KVCachePipelineOpx::grow (custom_ops/kv_cache_pipeline.cpp:374-451):
     max_bps caches, all zeroed when step == 0 (GetkvCachesInit,
     custom_ops/kv_cache_codelet.cpp:38-94, given `step` at :403-404); the cache
@@ -147,6 +153,9 @@ def kv_cache_pipeline(state, step, kv, max_len, max_bps, sequence_axis, step_len
     layout; the returned tensor is transposed back (:441-446), so the logical
     result is identical."""
     kv = np.asarray(kv)
+    if fp8:   # save_fp8 (:386-388, :437-439): bytes in, bytes kept, fp16 out; E4M3 with a scale in place of F143
+        bits = kv_cache_pipeline(state, step, cast_fp8(kv, fp8_scale), max_len, max_bps, sequence_axis, step_len)
+        return f16(e4m3_decode(bits) * F32(fp8_scale))
     shape = list(kv.shape)
     shape[sequence_axis] = max_len
     if state.caches is None or int(step) == 0:

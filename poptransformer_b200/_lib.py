@@ -87,6 +87,8 @@ SIGNATURES = {
     "pt_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "pt_kv_cache": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p]),
     "pt_kv_cache_pipeline": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_void_p]),
+    "pt_kv_cache_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int, c_int, c_int64, c_void_p]),
+    "pt_kv_cache_pipeline_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int64, c_int, c_int, c_int64, c_void_p]),
     "pt_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "pt_kv_append_attn": (c_int, [ctypes.POINTER(AttnArgs), c_void_p]),
     "pt_prefill_attn": (c_int, [ctypes.POINTER(PrefillAttnArgs), c_void_p]),

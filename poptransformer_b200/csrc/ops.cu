@@ -179,6 +179,46 @@ __global__ void kv_pipe_commit_kernel(const int *step_dev, const uint16_t *__res
   }
 }
 
+// ---- the same ops with 8-bit storage (`fp8` attribute, kv_cache.cpp:43-75, 100-104, 183-185; kv_cache_pipeline.cpp:386-388, 437-439):
+// the update is cast to E4M3 before the insert, the cache lives as bytes and the op returns it cast back to fp16.  One thread per
+// (outer, inner) column walks the sequence from its far end, so the shift happens in place and needs no clone.
+__device__ __forceinline__ uint8_t kv_to_e4m3(__half v, float inv_scale) {
+  return (uint8_t)__nv_cvt_float_to_fp8(__half2float(v) * inv_scale, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ __half kv_from_e4m3(uint8_t b, float scale) {
+  return __float2half_rn(__half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3))) * scale);
+}
+// caches: [n_caches][outer][max_len][inner] bytes.  Cache `sel` (step % n_caches) takes the insert and is decoded into `out`;
+// at step 0 every cache starts from zeros.
+__global__ void kv_fp8_kernel(const int *step_dev, const __half *__restrict__ kv_new, uint8_t *__restrict__ caches, __half *__restrict__ out,
+                              float scale, int n_caches, size_t outer, int max_len, int step_len, size_t inner) {
+  const int step = *step_dev;
+  const int sel = step % n_caches;
+  const size_t cols = outer * inner, per = outer * (size_t)max_len * inner;
+  const float inv_scale = 1.0f / scale;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < cols * n_caches; idx += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(idx / cols);
+    const size_t col = idx - (size_t)c * cols, o = col / inner, i = col - o * inner;
+    uint8_t *cache = caches + (size_t)c * per + o * (size_t)max_len * inner + i;
+    if (c != sel) {
+      if (step == 0)
+        for (int l = 0; l < max_len; ++l) cache[(size_t)l * inner] = 0;
+      continue;
+    }
+    __half *dst = out + o * (size_t)max_len * inner + i;
+    for (int l = max_len - 1; l >= step_len; --l) {
+      const uint8_t b = step == 0 ? (uint8_t)0 : cache[(size_t)(l - step_len) * inner];
+      cache[(size_t)l * inner] = b;
+      dst[(size_t)l * inner] = kv_from_e4m3(b, scale);
+    }
+    for (int l = 0; l < step_len && l < max_len; ++l) {
+      const uint8_t b = kv_to_e4m3(kv_new[(o * step_len + l) * inner + i], inv_scale);
+      cache[(size_t)l * inner] = b;
+      dst[(size_t)l * inner] = kv_from_e4m3(b, scale);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ top-k
 // One block per row, k <= 32: k rounds of arg-max with the already chosen indices masked out.  The key orders
 // by value descending, then by index ascending, so ties resolve to the lowest index.
@@ -533,6 +573,28 @@ extern "C" int pt_kv_cache_pipeline(const int32_t *step_dev, const void *kv_new,
   PT_LAUNCH_CHECK("pt_kv_cache_pipeline(shift)");
   kv_pipe_commit_kernel<<<grid_for(per * max_bps), 256, 0, st>>>(step_dev, (const uint16_t *)out, (uint16_t *)caches, max_bps, per);
   PT_LAUNCH_CHECK("pt_kv_cache_pipeline(commit)");
+  return PT_OK;
+}
+
+extern "C" int pt_kv_cache_fp8(const int32_t *step_dev, const void *kv_new, void *cache, void *out, float scale, int64_t outer, int max_len,
+                               int step_len, int64_t inner, void *stream) {
+  PT_REQUIRE(step_dev && kv_new && cache && out, "pt_kv_cache_fp8: null pointer argument");
+  PT_REQUIRE(outer > 0 && inner > 0 && max_len > 0 && step_len > 0 && step_len <= max_len, "pt_kv_cache_fp8: bad shape");
+  PT_REQUIRE(scale > 0.f, "pt_kv_cache_fp8: scale must be > 0");
+  kv_fp8_kernel<<<grid_for((size_t)(outer * inner)), 256, 0, as_stream(stream)>>>(step_dev, (const __half *)kv_new, (uint8_t *)cache, (__half *)out, scale,
+                                                                                    1, (size_t)outer, max_len, step_len, (size_t)inner);
+  PT_LAUNCH_CHECK("pt_kv_cache_fp8");
+  return PT_OK;
+}
+
+extern "C" int pt_kv_cache_pipeline_fp8(const int32_t *step_dev, const void *kv_new, void *caches, void *out, float scale, int max_bps,
+                                        int64_t outer, int max_len, int step_len, int64_t inner, void *stream) {
+  PT_REQUIRE(step_dev && kv_new && caches && out, "pt_kv_cache_pipeline_fp8: null pointer argument");
+  PT_REQUIRE(max_bps > 0 && outer > 0 && inner > 0 && max_len > 0 && step_len > 0 && step_len <= max_len, "pt_kv_cache_pipeline_fp8: bad shape");
+  PT_REQUIRE(scale > 0.f, "pt_kv_cache_pipeline_fp8: scale must be > 0");
+  kv_fp8_kernel<<<grid_for((size_t)(outer * inner * max_bps)), 256, 0, as_stream(stream)>>>(
+      step_dev, (const __half *)kv_new, (uint8_t *)caches, (__half *)out, scale, max_bps, (size_t)outer, max_len, step_len, (size_t)inner);
+  PT_LAUNCH_CHECK("pt_kv_cache_pipeline_fp8");
   return PT_OK;
 }
 

@@ -156,7 +156,29 @@ class LlamaDecoder(DecodeLoop):
         self.head = ops.PackedLinear(ops.W_FP16, head.contiguous())
         self.sin, self.cos = rope_tables(c.max_len, c.head_dim, dev)
         self.score_scale = float(np.float16(1 / math.sqrt(c.head_dim)))
+        self._state_opts = dict(page_size=page_size, persistent=persistent, keep_logits=keep_logits, tp_buffers=tp_buffers, wait_limit=wait_limit)
+        self._weights_in_stream_order = False
+        self._alloc_state()
 
+    def new_stream(self):
+        """A second decode stream over the SAME weights: its own id container, step, KV caches, activations, workspaces and (once
+        `capture()` is called on it) CUDA graph.  This is what KVCachePipeline's `max_bps` caches are for in the reference
+        (custom_ops/kv_cache_pipeline.cpp:392-439): several independent generations share one model and take turns."""
+        import copy
+        s = copy.copy(self)
+        s._init_loop(self.device, self.early_stop)
+        if self.pf_layers is not None:
+            s._pf_bufs = {}
+        s._alloc_state()
+        return s
+
+    def _alloc_state(self):
+        """Everything a decode stream owns (nothing here depends on the checkpoint values)."""
+        c, dev, batch = self.cfg, self.device, self.batch
+        tp, r, group = self.tp, self.rank, self.group
+        d, f = c.d_model, c.ffn
+        page_size, persistent, keep_logits = self._state_opts["page_size"], self._state_opts["persistent"], self._state_opts["keep_logits"]
+        tp_buffers, wait_limit = self._state_opts["tp_buffers"], self._state_opts["wait_limit"]
         B = batch
         f16 = dict(dtype=torch.float16, device=dev)
         self.ids = torch.full((B, c.max_len), self.pad_id, dtype=torch.int32, device=dev)
@@ -205,10 +227,12 @@ class LlamaDecoder(DecodeLoop):
                           "pt_llama_stream_permute")
                 pl.packed_w = out
 
-            for lay in self.layers:
-                for k in ("qkv", "o", "gu", "down"):
-                    to_stream(lay[k])
-            to_stream(self.head)
+            if not self._weights_in_stream_order:     # once per set of weights; further streams share the permuted tiles
+                for lay in self.layers:
+                    for k in ("qkv", "o", "gu", "down"):
+                        to_stream(lay[k])
+                to_stream(self.head)
+                self._weights_in_stream_order = True
             arr = (ops._lib.LlamaLayer * c.n_layer)()
             for i, lay in enumerate(self.layers):
                 arr[i].qkv, arr[i].o = lay["qkv"].packed_w.data_ptr(), lay["o"].packed_w.data_ptr()

@@ -50,3 +50,74 @@ class DecodeLoop:
         if err != 0:
             raise PtError(f"device-side error flag {err} during decode (a bounded wait gave up, or the step left the id container)")
         return out
+
+
+class MultiStreamLoop:
+    """`max_bps` decode streams over ONE set of weights, served in turn (continuous decode).
+
+    Global iteration s runs one loop iteration of stream s % max_bps, which is that stream's own step s // max_bps: the
+    (bpsIdx, stepTrue) pair the reference's GetStepBps vertex derives from the loop counter (custom_ops/kv_cache_codelet.cpp:18-36)
+    and by which KVCachePipeline picks one of its `max_bps` caches (custom_ops/kv_cache_pipeline.cpp:392-439).  Each stream owns
+    its id container, step, stop mask, KV caches and CUDA graph (`decoder.new_stream()`); the weights exist once.  A stream whose
+    generation has ended (its `max_loop` iterations are done, or with `early_stop` every sequence has produced its eos id) takes
+    the next waiting request while the other streams keep going, so the device never idles behind the longest generation."""
+
+    def __init__(self, decoder, max_bps, capture=True):
+        if max_bps < 1:
+            raise PtError(f"max_bps={max_bps}")
+        if not hasattr(decoder, "new_stream"):
+            raise PtError(f"{type(decoder).__name__} has no new_stream(): its weights cannot be shared between streams")
+        self.streams = [decoder] + [decoder.new_stream() for _ in range(max_bps - 1)]
+        if capture:
+            for s in self.streams:
+                if s.graph is None:
+                    s.capture()
+        self.max_bps = max_bps
+
+    def run(self, requests, max_loop=None, poll_every=16):
+        """requests: a list of id containers ([batch, max_len] int32 each).  Returns one {'Loop:0', 'Loop:1'} per request, each
+        identical to what `decoder.run(request, max_loop)` returns on its own."""
+        first = self.streams[0]
+        max_len = first.cfg.max_len
+        n = max_len if max_loop is None else int(max_loop)
+        if n < 0 or n > max_len:
+            raise PtError(f"max_loop={n} outside 0..max_length={max_len}")
+        results = [None] * len(requests)
+        waiting = list(range(len(requests)))
+        serving = [None] * self.max_bps         # request index each stream is working on
+        done_steps = [0] * self.max_bps         # stepTrue of each stream
+
+        def start(k):
+            serving[k] = waiting.pop(0) if waiting else None
+            if serving[k] is not None:
+                st = self.streams[k]
+                st.reset(requests[serving[k]])
+                if st.done_flag is not None:
+                    st.done_flag.zero_()
+                done_steps[k] = 0
+
+        def finish(k):
+            st = self.streams[k]
+            results[serving[k]] = {"Loop:0": st.ids.cpu().numpy(), "Loop:1": st.step_t.cpu().numpy()}
+            err = int(st.error_flag.item())
+            if err != 0:
+                raise PtError(f"device-side error flag {err} on stream {k}")
+
+        for k in range(self.max_bps):
+            start(k)
+        s = 0
+        while any(r is not None for r in serving):
+            k = s % self.max_bps               # bpsIdx
+            s += 1
+            if serving[k] is None:
+                continue
+            st = self.streams[k]
+            ended = done_steps[k] >= n
+            if not ended:
+                st.step()
+                done_steps[k] += 1
+                ended = done_steps[k] >= n or (st.early_stop and done_steps[k] % poll_every == 0 and int(st.done_flag.item()))
+            if ended:
+                finish(k)
+                start(k)
+        return results

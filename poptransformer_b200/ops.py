@@ -212,8 +212,11 @@ class KVCacheOp:
     """One `KVCache` call site: owns the persistent cache like the reference op instance
     (custom_ops/kv_cache.cpp:108-116), re-zeroed when step == 0."""
 
-    def __init__(self, max_len, sequence_axis, step_len=1):
+    def __init__(self, max_len, sequence_axis, step_len=1, fp8=False, fp8_scale=1.0):
+        """fp8=True is the op's `fp8` attribute (customized.py:32; kv_cache.cpp:100-104, :183-185): the cache is kept as 8-bit floats
+        (E4M3 bytes of updater / fp8_scale) and returned cast back to fp16."""
         self.max_len, self.axis, self.step_len = max_len, sequence_axis, step_len
+        self.fp8, self.fp8_scale = bool(fp8), float(fp8_scale)
         self.cache = self.scratch = None
 
     def __call__(self, step, updater):
@@ -227,6 +230,13 @@ class KVCacheOp:
         for d in shape[self.axis + 1:]:
             inner *= d
         shape[self.axis] = self.max_len
+        if self.fp8:
+            if self.cache is None:
+                self.cache = torch.zeros(shape, dtype=torch.uint8, device=updater.device)
+            out = torch.empty(shape, dtype=torch.float16, device=updater.device)
+            check(_lib.lib().pt_kv_cache_fp8(_ptr(step), _ptr(updater), _ptr(self.cache), _ptr(out), self.fp8_scale, outer, self.max_len,
+                                             self.step_len, inner, _stream()), "KVCache")
+            return out
         if self.cache is None:
             self.cache = torch.zeros(shape, dtype=updater.dtype, device=updater.device)
             self.scratch = torch.empty_like(self.cache)
@@ -246,8 +256,10 @@ class KVCachePipelineOp:
     GetBpsKvCacheLastDim, kv_cache_codelet.cpp:170-212): the caches are kept as [..., H, max_len] and shifted along their LAST
     dimension; the op returns the tensor transposed back (kv_cache_pipeline.cpp:441-446), so callers see the same values."""
 
-    def __init__(self, max_len, max_bps, sequence_axis, step_len=1, transpose=0):
+    def __init__(self, max_len, max_bps, sequence_axis, step_len=1, transpose=0, fp8=False, fp8_scale=1.0):
+        """fp8=True: the caches hold E4M3 bytes of updater / fp8_scale and the op returns fp16 (kv_cache_pipeline.cpp:386-388, :437-439)."""
         self.max_len, self.max_bps, self.axis, self.step_len, self.transpose = max_len, max_bps, sequence_axis, step_len, int(transpose)
+        self.fp8, self.fp8_scale = bool(fp8), float(fp8_scale)
         self.caches = None
 
     def __call__(self, step, updater):
@@ -268,10 +280,14 @@ class KVCachePipelineOp:
             inner = shape[-1]
             store = shape[: self.axis] + [self.max_len, shape[-1]]
         if self.caches is None:
-            self.caches = torch.zeros([self.max_bps] + store, dtype=updater.dtype, device=updater.device)
+            self.caches = torch.zeros([self.max_bps] + store, dtype=torch.uint8 if self.fp8 else updater.dtype, device=updater.device)
         out = torch.empty(store, dtype=updater.dtype, device=updater.device)
-        check(_lib.lib().pt_kv_cache_pipeline(_ptr(step), _ptr(upd), _ptr(self.caches), _ptr(out), self.max_bps, outer, self.max_len,
-                                              self.step_len, inner, _stream()), "KVCachePipeline")
+        if self.fp8:
+            check(_lib.lib().pt_kv_cache_pipeline_fp8(_ptr(step), _ptr(upd), _ptr(self.caches), _ptr(out), self.fp8_scale, self.max_bps, outer,
+                                                      self.max_len, self.step_len, inner, _stream()), "KVCachePipeline")
+        else:
+            check(_lib.lib().pt_kv_cache_pipeline(_ptr(step), _ptr(upd), _ptr(self.caches), _ptr(out), self.max_bps, outer, self.max_len,
+                                                  self.step_len, inner, _stream()), "KVCachePipeline")
         return out.transpose(-1, -2).contiguous() if self.transpose else out
 
 

@@ -14,7 +14,7 @@ def declared_symbols():
 
 def test_header_declares_the_op_surface():
     syms = declared_symbols()
-    for name in ["pt_int4_to_half", "pt_linear", "pt_norm_ce", "pt_rms_norm", "pt_softmax", "pt_kv_cache", "pt_kv_cache_pipeline",
+    for name in ["pt_int4_to_half", "pt_linear", "pt_norm_ce", "pt_rms_norm", "pt_softmax", "pt_kv_cache", "pt_kv_cache_pipeline", "pt_kv_cache_fp8", "pt_kv_cache_pipeline_fp8",
                  "pt_kv_append_attn", "pt_kv_export", "pt_kv_reorder_pages", "pt_kv_reorder_table", "pt_topk", "pt_beam_search",
                  "pt_cast_fp8", "pt_fp8_matmul", "pt_wkv", "pt_embedding", "pt_step_containers"]:
         assert name in syms

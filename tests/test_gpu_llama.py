@@ -155,3 +155,20 @@ def test_step_past_the_container_is_refused_on_the_device(cuda):
         torch.cuda.synchronize()
         assert int(dec.error_flag.item()) == 12
         assert torch.equal(dec.ids, before)
+
+
+@pytest.mark.parametrize("persistent", [True, False])
+def test_multi_stream_continuous_decode(cuda, persistent):
+    """Three streams over one set of weights serve five requests in turn (stream s % 3 at its own step s // 3, as KVCachePipeline's
+    caches are selected): every request's id container equals what the same decoder produces for it alone."""
+    from poptransformer_b200 import loop, synth
+    dec, _ = _setup(cuda, 2, 72 if persistent else 40, 128, persistent=persistent)
+    max_len, vocab = dec.cfg.max_len, dec.cfg.vocab
+    reqs = [synth.prompt_ids(2, 3 + 2 * i, max_len, vocab, dec.pad_id, seed=20 + i) for i in range(5)]
+    alone = [dec.run(r, max_loop=24)["Loop:0"].copy() for r in reqs]
+    ms = loop.MultiStreamLoop(dec, 3)
+    assert ms.streams[1].layers is dec.layers and ms.streams[1].caches[0].pool.data_ptr() != dec.caches[0].pool.data_ptr()
+    outs = ms.run(reqs, max_loop=24)
+    for i, (o, a) in enumerate(zip(outs, alone)):
+        assert np.array_equal(o["Loop:0"], a), f"request {i}"
+        assert int(o["Loop:1"][0]) == 24

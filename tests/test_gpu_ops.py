@@ -297,6 +297,30 @@ def test_kv_cache_pipeline(cuda):
         assert np.array_equal(got.view(np.uint16), exp.view(np.uint16)), f"step {step}"
 
 
+@pytest.mark.parametrize("scale", [1.0, 0.03125, 0.013])
+def test_kv_cache_fp8_storage(cuda, scale):
+    """The `fp8` attribute of KVCache and KVCachePipeline: bytes in the cache, fp16 out; bit-exact against the restatement, through
+    the zeroing at step 0, more steps than the cache holds, and values beyond the E4M3 range (saturating cast)."""
+    from poptransformer_b200 import ops
+    r = rng(12)
+    B, N, L, H, bps = 2, 3, 7, 16, 3
+    st_o, st_p = O.KVCacheState(), O.KVCachePipelineState()
+    op = ops.KVCacheOp(max_len=L, sequence_axis=3, fp8=True, fp8_scale=scale)
+    pipe = ops.KVCachePipelineOp(max_len=L, max_bps=bps, sequence_axis=2, fp8=True, fp8_scale=scale)
+    step_t = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for step in list(range(L + 3)) + [0, 1, 2]:
+        kv = (r.standard_normal((2, B, N, 1, H)) * (600.0 * scale if step == 2 else 3.0 * scale)).astype(np.float16)
+        step_t.fill_(step)
+        got = ops.kv_cache(op, step_t, dev(kv, cuda)).cpu().numpy()
+        exp = O.kv_cache(st_o, step, kv, L, 3, 1, fp8=True, fp8_scale=scale)
+        assert got.dtype == np.float16 and np.array_equal(got.view(np.uint16), exp.view(np.uint16)), f"KVCache step {step}"
+        assert np.array_equal(op.cache.cpu().numpy(), st_o.cache), f"KVCache bytes, step {step}"
+        got = ops.kv_cache_pipeline(pipe, step_t, dev(kv[0], cuda)).cpu().numpy()
+        exp = O.kv_cache_pipeline(st_p, step, kv[0], L, bps, 2, 1, fp8=True, fp8_scale=scale)
+        assert np.array_equal(got.view(np.uint16), exp.view(np.uint16)), f"KVCachePipeline step {step}"
+        assert np.array_equal(pipe.caches.cpu().numpy(), np.stack(st_p.caches)), f"KVCachePipeline bytes, step {step}"
+
+
 def test_kv_cache_pipeline_last_dim_layout(cuda):
     """transpose=1: the caches are stored [..., H, L] and shifted along the last dimension (GetBpsKvCacheLastDim); the op hands the
     result back transposed, so the values equal the plain layout's."""

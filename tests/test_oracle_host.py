@@ -19,6 +19,20 @@ def test_int4_lut_matches_reference_table():
     assert np.array_equal(rt, np.arange(-8, 8).reshape(1, 16))
 
 
+def test_kv_cache_fp8_storage_is_the_fp16_cache_of_the_rounded_values():
+    """fp8 storage = the fp16 op applied to values that were rounded to E4M3 once, on the way in (kv_cache.cpp:100-104, :183-185)."""
+    r = np.random.default_rng(3)
+    st8, st16 = O.KVCacheState(), O.KVCacheState()
+    p8, p16 = O.KVCachePipelineState(), O.KVCachePipelineState()
+    for step in [0, 1, 2, 3, 4, 5, 0, 1]:
+        kv = (r.standard_normal((2, 3, 1, 8)) * 2).astype(np.float16)
+        rounded = O.f16(O.e4m3_decode(O.cast_fp8(kv, 0.25)) * np.float32(0.25))
+        assert np.array_equal(O.kv_cache(st8, step, kv, 4, 2, 1, fp8=True, fp8_scale=0.25), O.kv_cache(st16, step, rounded, 4, 2, 1))
+        assert st8.cache.dtype == np.uint8
+        assert np.array_equal(O.kv_cache_pipeline(p8, step, kv, 4, 2, 2, 1, fp8=True, fp8_scale=0.25),
+                              O.kv_cache_pipeline(p16, step, rounded, 4, 2, 2, 1))
+
+
 def test_kv_cache_is_shift_right_newest_first():
     st = O.KVCacheState()
     for step in range(5):
