@@ -146,7 +146,7 @@ typedef struct pt_gemm_args {
   int wfmt;               /* PT_W_FP8 or PT_W_INT4                                  */
   int m, n_out, k_in;
   int group;              /* INT4: scale group along k (a multiple of 128)          */
-  int epilogue;           /* PT_EPI_STORE or PT_EPI_RESIDUAL                         */
+  int epilogue;           /* PT_EPI_STORE, PT_EPI_RESIDUAL or PT_EPI_BIAS            */
   int ksplit;             /* 0 = let the library choose                             */
   int w_tiled;            /* 1: w was tiled by pt_gemm_repack; 0: row-major (FP8 only) */
   const void *x, *w;
@@ -158,6 +158,7 @@ typedef struct pt_gemm_args {
   void *workspace;        /* pt_gemm_workspace_bytes                                 */
   size_t workspace_bytes;
   int32_t *error_flag;    /* optional device int, set non-zero (21..24) if a bounded wait gave up */
+  const void *bias;       /* fp16 [n_out] (PT_EPI_BIAS)                              */
 } pt_gemm_args;
 size_t pt_gemm_workspace_bytes(int m, int n_out, int max_ksplit);
 int pt_gemm(const pt_gemm_args *args, void *stream);
@@ -409,6 +410,13 @@ int pt_step_containers_early_stop(int32_t *ids, int batch, int max_len, int32_t 
 /* SwiGLU behind a fused gate|up linear (llama2/mlp.py:20-28, chatglm2/mlp.py:51-59): gate_up fp16 [rows, 2 f] with the gate
  * features first; out[r, j] = fp16(up[r, j] * swish(gate[r, j])), swish in float32 rounded once.  out_ld: row stride (0 = f). */
 int pt_swiglu(const void *gate_up, int rows, int f, void *out, int out_ld, void *stream);
+/* The activation side of an FP8 linear as its own kernel, for the layers that run on pt_gemm (the FP8 linear casts its
+ * input with the scale stored beside the weight, utils/param_handler/precision_strategy.py:62-66):
+ * pt_rms_norm_fp8: out bytes = e4m3(RMSNorm(x) / act_scale), the RMSNorm with the reference's fp16 roundings
+ * (layers/rms_layer_norm.py:26-36); pt_swiglu_fp8: out bytes = e4m3(fp16(up * swish(gate)) / act_scale) from the fused
+ * [gate features | up features] rows (chatglm2/mlp.py:51-59). */
+int pt_rms_norm_fp8(const void *x, const void *gamma, int rows, int dim, float eps, float act_scale, void *out, void *stream);
+int pt_swiglu_fp8(const void *gate_up, int rows, int f, float act_scale, void *out, int out_ld, void *stream);
 /* Elementwise fp16: out = fp16(a + b) (ops.add). */
 int pt_add_f16(const void *a, const void *b, int64_t n, void *out, void *stream);
 

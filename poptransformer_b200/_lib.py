@@ -43,7 +43,7 @@ class GemmArgs(ctypes.Structure):
         ("wfmt", c_int), ("m", c_int), ("n_out", c_int), ("k_in", c_int), ("group", c_int), ("epilogue", c_int), ("ksplit", c_int),
         ("w_tiled", c_int), ("x", c_void_p), ("w", c_void_p), ("scales", c_void_p), ("x_scale", c_float), ("w_scale", c_float),
         ("residual", c_void_p), ("out", c_void_p), ("out_ld", c_int), ("workspace", c_void_p), ("workspace_bytes", c_size_t),
-        ("error_flag", c_void_p),
+        ("error_flag", c_void_p), ("bias", c_void_p),
     ]
 
 
@@ -115,6 +115,8 @@ SIGNATURES = {
     "pt_step_containers": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "pt_step_containers_early_stop": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_swiglu": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "pt_rms_norm_fp8": (c_int, [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_void_p]),
+    "pt_swiglu_fp8": (c_int, [c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p]),
     "pt_add_f16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
 }
 

@@ -50,11 +50,12 @@ struct GemmParams {
   int kb_per_split, n_kb; // k blocks (of 128 bytes of operand row) per k-slice / in total
   int ksplit, stages, raw_stages;
   int w_tiled;            // weights tiled by pt_gemm_repack (one contiguous tile per stage) instead of row-major
-  int epilogue;           // PT_EPI_STORE or PT_EPI_RESIDUAL
+  int epilogue;           // PT_EPI_STORE, PT_EPI_RESIDUAL or PT_EPI_BIAS
   float out_scale;
   const unsigned char *w; // tiled weights (w_tiled)
   const __half *scales;   // INT4: [N][K / group]
   const __half *residual;
+  const __half *bias;
   __half *out;
   int out_ld;
   float *partial;         // [ksplit][M][N] (ksplit > 1)
@@ -190,6 +191,7 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, uint32_t tmem, int
         } else {
           __half y = __float2half_rn(acc * p.out_scale);
           if (p.epilogue == PT_EPI_RESIDUAL) y = h_add(__ldcg(p.residual + (size_t)m * p.N + n), y);
+          else if (p.epilogue == PT_EPI_BIAS) y = h_add(y, p.bias[n]);
           p.out[(size_t)m * p.out_ld + n] = y;
         }
       }
@@ -225,6 +227,7 @@ __device__ __forceinline__ void reduce_slices(const GemmParams &p, SharedCtl &ct
       }
       __half y = __float2half_rn(acc * p.out_scale);
       if (p.epilogue == PT_EPI_RESIDUAL) y = h_add(__ldcg(p.residual + (size_t)m * p.N + n), y);
+      else if (p.epilogue == PT_EPI_BIAS) y = h_add(y, p.bias[n]);
       p.out[(size_t)m * p.out_ld + n] = y;
     }
   }
@@ -602,8 +605,10 @@ extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
              a->m, a->n_out, a->k_in);
   PT_REQUIRE(a->x && a->w && a->out, "pt_gemm: null x / w / out");
   PT_REQUIRE(((uintptr_t)a->x & 15) == 0 && ((uintptr_t)a->w & 15) == 0, "pt_gemm: x and w must be 16-byte aligned");
-  PT_REQUIRE(a->epilogue == PT_EPI_STORE || a->epilogue == PT_EPI_RESIDUAL, "pt_gemm: epilogue %d (store or residual)", a->epilogue);
+  PT_REQUIRE(a->epilogue == PT_EPI_STORE || a->epilogue == PT_EPI_RESIDUAL || a->epilogue == PT_EPI_BIAS, "pt_gemm: epilogue %d (store, residual or bias)",
+             a->epilogue);
   PT_REQUIRE(a->epilogue != PT_EPI_RESIDUAL || a->residual, "pt_gemm: residual epilogue needs residual");
+  PT_REQUIRE(a->epilogue != PT_EPI_BIAS || a->bias, "pt_gemm: bias epilogue needs bias");
   PT_REQUIRE(!int4 || a->w_tiled, "pt_gemm: INT4 weights must be tiled with pt_gemm_repack");
   if (int4)
     PT_REQUIRE(a->scales && a->group >= 128 && a->group % 128 == 0 && a->k_in % a->group == 0,
@@ -619,11 +624,14 @@ extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
   const int m_tiles = ceil_div(a->m, p.mb);
   const int n_tiles = ceil_div(a->n_out, tc::BM);
   p.n_kb = int4 ? a->k_in / 64 : a->k_in / 128;
-  // k-slices: fill the GPU when there are few tiles, but keep at least 8 k-blocks per CTA
+  // k-slices: fill the GPU when there are few tiles, but keep at least PT_TC_MIN_KB k-blocks per CTA
+#ifndef PT_TC_MIN_KB
+#define PT_TC_MIN_KB 8
+#endif
   int ksplit = a->ksplit;
   if (ksplit <= 0) {
     ksplit = std::max(1, (p.mb <= 64 ? 2 : 1) * sm_count() / (n_tiles * m_tiles));   // two CTAs fit an SM up to 64 activation rows
-    ksplit = std::max(1, std::min(ksplit, p.n_kb / 8));
+    ksplit = std::max(1, std::min(ksplit, p.n_kb / PT_TC_MIN_KB));
     ksplit = std::min(ksplit, 8);                                           // what pt_gemm_workspace_bytes is usually asked for ...
     while (ksplit > 1 && pt_gemm_workspace_bytes(a->m, a->n_out, ksplit) > a->workspace_bytes) --ksplit;   // ... and never more than the caller's workspace holds
     if ((size_t)n_tiles * m_tiles > kGemmMaxCounters) ksplit = 1;
@@ -635,6 +643,7 @@ extern "C" int pt_gemm(const pt_gemm_args *a, void *stream) {
   p.out_scale = int4 ? 1.0f : (a->x_scale > 0.f ? a->x_scale : 1.0f) * (a->w_scale > 0.f ? a->w_scale : 1.0f);
   p.scales = (const __half *)a->scales;
   p.residual = (const __half *)a->residual;
+  p.bias = (const __half *)a->bias;
   p.out = (__half *)a->out;
   p.out_ld = a->out_ld > 0 ? a->out_ld : a->n_out;
   p.error_flag = a->error_flag;

@@ -155,7 +155,7 @@ def gemm_workspace(m, n_out_max, max_ksplit=8, device="cuda"):
     return torch.zeros(_lib.lib().pt_gemm_workspace_bytes(m, n_out_max, max_ksplit), dtype=torch.uint8, device=device)
 
 
-def gemm(x, gw, out=None, x_scale=1.0, epilogue=EPI_STORE, residual=None, workspace=None, ksplit=0, error_flag=None):
+def gemm(x, gw, out=None, x_scale=1.0, epilogue=EPI_STORE, residual=None, workspace=None, ksplit=0, error_flag=None, bias=None):
     """y = x @ W^T on the tcgen05 GEMM.  INT4: x fp16 [m, k]; FP8: x E4M3 bytes [m, k] quantised with `x_scale`."""
     m = x.shape[0]
     if x.shape[1] != gw.k_in:
@@ -169,7 +169,7 @@ def gemm(x, gw, out=None, x_scale=1.0, epilogue=EPI_STORE, residual=None, worksp
     a.x_scale, a.w_scale = float(x_scale), gw.w_scale
     a.residual, a.out, a.out_ld = _ptr(residual), _ptr(out), 0
     a.workspace, a.workspace_bytes = _ptr(workspace), (workspace.numel() if workspace is not None else 0)
-    a.error_flag = _ptr(error_flag)
+    a.error_flag, a.bias = _ptr(error_flag), _ptr(bias)
     check(_lib.lib().pt_gemm(ctypes.byref(a), _stream()), "pt_gemm")
     return out
 

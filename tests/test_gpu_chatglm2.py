@@ -21,11 +21,13 @@ def _setup(cuda, batch, max_len, precision, seed=0):
     return dec, orc
 
 
-@pytest.mark.parametrize("batch,precision,tol", [(1, "fp16", 2e-2), (8, "fp16", 2e-2), (2, "fp8", 5e-2)])
+@pytest.mark.parametrize("batch,precision,tol", [(1, "fp16", 2e-2), (8, "fp16", 2e-2), (2, "fp8", 5e-2), (8, "fp8", 5e-2)])
 def test_chatglm2_logits_teacher_forced(cuda, batch, precision, tol):
+    """fp8 at 8 rows takes the tcgen05 GEMM path (RMSNorm / SwiGLU / casts as their own kernels), at 2 rows the skinny-matmul kernels."""
     from poptransformer_b200 import synth
     max_len = 70
     dec, orc = _setup(cuda, batch, max_len, precision)
+    assert dec.use_gemm == (precision == "fp8" and batch >= 8)
     ids = synth.prompt_ids(batch, max_len, max_len, SMALL["vocab"], dec.pad_id, seed=1)
     dec.reset(ids)
     orc.reset()

@@ -109,6 +109,27 @@ def test_gemm_more_rows_than_one_tile_and_residual(cuda):
     np.testing.assert_allclose(got.astype(np.float32), exp, rtol=4e-3, atol=4e-3 * np.abs(exp).max())
 
 
+def test_gemm_bias_epilogue(cuda):
+    """y = fp16(fp16(acc * scales) + bias) (layers/linear.py:42-46), with and without k-slices."""
+    from poptransformer_b200 import ops
+    r = np.random.default_rng(9)
+    m, n, k = 8, 4608, 4096
+    w = r.standard_normal((n, k), dtype=np.float32) * 0.02
+    ws_ = float(np.abs(w).max() / 448.0)
+    wb = O.e4m3_encode(w / ws_)
+    x = r.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    xs_ = float(np.abs(x.astype(np.float32)).max() / 448.0)
+    xb = O.cast_fp8(x, xs_)
+    bias = r.standard_normal(n).astype(np.float16)
+    acc = O.fp8_matmul(xb, np.ascontiguousarray(wb.T), xs_, ws_)
+    exp = O.add_f16(acc, bias[None, :]).astype(np.float32)
+    gw = ops.GemmWeight(ops.W_FP8, dev(wb, cuda), w_scale=ws_)
+    ws = ops.gemm_workspace(m, n, 8, cuda)
+    for ksplit in (0, 1):
+        got = ops.gemm(dev(xb, cuda), gw, x_scale=xs_, workspace=ws, ksplit=ksplit, epilogue=ops.EPI_BIAS, bias=dev(bias, cuda)).cpu().numpy()
+        np.testing.assert_allclose(got.astype(np.float32), exp, rtol=2e-3, atol=2e-3 * np.abs(exp).max())
+
+
 def test_gemm_rejects_bad_shapes(cuda):
     from poptransformer_b200 import ops
     gw = ops.GemmWeight(ops.W_FP8, torch.zeros((64, 256), dtype=torch.uint8, device=cuda))

@@ -265,6 +265,33 @@ def test_softmax_v3(cuda, dtype, stable):
     np.testing.assert_allclose(got.astype(np.float32), exp.astype(np.float32), rtol=tol, atol=tol * 1e-2)
 
 
+def test_fp8_activation_kernels(cuda):
+    """pt_rms_norm_fp8 and pt_swiglu_fp8 (the activation side of the FP8 linears that run on the GEMM) against the restatements:
+    the casts are exact, so bytes only differ where the fp16 value in front of the cast differs by its last bit (the RMSNorm
+    statistic is summed in another order)."""
+    import ctypes
+    from poptransformer_b200 import _lib, ops
+    L = _lib.lib()
+    r = rng(21)
+    rows, d, f, scale = 8, 4096, 13696, 8.0 / 448.0
+    x = r.standard_normal((rows, d)).astype(np.float16)
+    g = (1 + 0.1 * r.standard_normal(d)).astype(np.float16)
+    out = torch.empty((rows, d), dtype=torch.uint8, device=cuda)
+    xd, gd = dev(x, cuda), dev(g, cuda)
+    _lib.check(L.pt_rms_norm_fp8(ops._ptr(xd), ops._ptr(gd), rows, d, 1e-5, scale, ops._ptr(out), ops._stream()), "pt_rms_norm_fp8")
+    exp = O.cast_fp8(O.rms_norm(x, g, 1e-5), scale)
+    got = out.cpu().numpy()
+    assert (got == exp).mean() > 0.99
+    assert np.abs(O.e4m3_decode(got) - O.e4m3_decode(exp)).max() <= 0.13 * np.abs(O.e4m3_decode(exp)).max()      # one E4M3 step at most
+    gu = r.standard_normal((rows, 2 * f)).astype(np.float16)
+    out2 = torch.empty((rows, f), dtype=torch.uint8, device=cuda)
+    gud = dev(gu, cuda)
+    _lib.check(L.pt_swiglu_fp8(ops._ptr(gud), rows, f, 1.0 / 448.0, ops._ptr(out2), f, ops._stream()), "pt_swiglu_fp8")
+    act = O.mul_f16(gu[:, f:], O.swish_f16(gu[:, :f]))
+    exp2 = O.cast_fp8(act, 1.0 / 448.0)
+    assert (out2.cpu().numpy() == exp2).mean() > 0.999        # expf differs from numpy's by an ulp now and then
+
+
 # ------------------------------------------------------------------ KV cache (bit-exact)
 def test_kv_cache_dense(cuda):
     from poptransformer_b200 import ops
