@@ -51,6 +51,7 @@ uint64_t pt_launch_count(void);
 #define PT_PRO_RMSNORM 1   /* poptransformer/layers/rms_layer_norm.py:26-36 */
 #define PT_PRO_CAST_FP8 2  /* activations quantised to E4M3 with `act_scale` first */
 #define PT_PRO_RMSNORM_CAST_FP8 3
+#define PT_PRO_NORMCE 4    /* LayerNorm with the NormCE arithmetic (customized.py:69-102; custom_ops/NormCE.cpp), norm_gamma / norm_beta */
 
 /* Epilogues fused behind a linear layer. */
 #define PT_EPI_STORE 0        /* y = fp16(acc)                                         */
@@ -108,6 +109,7 @@ typedef struct pt_linear_args {
                             leaves the counters at zero), pt_linear_workspace_bytes             */
   size_t workspace_bytes;
   int32_t *error_flag;   /* optional device int, set non-zero if a bounded wait gave up        */
+  const void *norm_beta; /* fp16 [k_in]   (PT_PRO_NORMCE)                           */
 } pt_linear_args;
 
 size_t pt_linear_workspace_bytes(int batch, int n_out, int max_ksplit);

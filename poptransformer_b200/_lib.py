@@ -23,7 +23,7 @@ class LinearArgs(ctypes.Structure):
         ("x", c_void_p), ("packed_w", c_void_p), ("norm_gamma", c_void_p),
         ("norm_eps", c_float), ("act_scale", c_float), ("w_scale", c_float),
         ("bias", c_void_p), ("residual", c_void_p), ("out", c_void_p), ("out_ld", c_int), ("pdl", c_int),
-        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("norm_beta", c_void_p),
     ]
 
 

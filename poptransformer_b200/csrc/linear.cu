@@ -41,7 +41,7 @@ constexpr int kRingStages = 4;
 
 struct LinearParams {
   const unsigned char *w;
-  const __half *x, *gamma, *bias, *residual;
+  const __half *x, *gamma, *beta, *bias, *residual;
   __half *out;
   float *partial;
   int *counters, *error_flag;
@@ -81,8 +81,8 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
   float *corr = reinterpret_cast<float *>(smem + xs_bytes);  // [slice chunks][BP] (INT4 only)
   const size_t corr_bytes = WFMT == PT_W_INT4 ? ((size_t)p.chunks_per_split * BP * sizeof(float) + 127) / 128 * 128 : 0;
   unsigned char *ring = smem + xs_bytes + corr_bytes + (size_t)warp * kStages * TILE;
-  __shared__ float s_stat[32];
-  __shared__ float s_part[32 * kWarps];
+  __shared__ float s_stat[32], s_mean[32];
+  __shared__ float s_part[32 * kWarps], s_part1[32 * kWarps];
   __shared__ int s_last;
 
   // ---- start streaming this warp's tiles before anything else (they do not depend on the previous kernel)
@@ -108,7 +108,8 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
 
   // ---- prologue: stage (and optionally normalise / quantise) the activation slice
   const int slice_units = nslice * 4 * UNITS;  // 16-byte units per batch row
-  const bool do_norm = (p.pro == PT_PRO_RMSNORM || p.pro == PT_PRO_RMSNORM_CAST_FP8);
+  const bool norm_ce = p.pro == PT_PRO_NORMCE;   // LayerNorm with the NormCE arithmetic instead of RMSNorm
+  const bool do_norm = (p.pro == PT_PRO_RMSNORM || p.pro == PT_PRO_RMSNORM_CAST_FP8 || norm_ce);
   const bool do_cast = (p.pro == PT_PRO_CAST_FP8 || p.pro == PT_PRO_RMSNORM_CAST_FP8);
   // Activations come from the previous kernel of the stream: read them through L2 (ld.cg) so that a line another
   // block of this SM cached earlier can never be served stale when kernels overlap.  The slice this block stages is
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
     const int wpr = p.B >= kWarps ? 1 : kWarps / p.B;           // warps per row
     const int part = warp % wpr;
     for (int b = warp / wpr; b < p.B; b += kWarps / wpr) {
-      float ss = 0.f;
+      float ss = 0.f, s1 = 0.f;
       const uint4 *xr = reinterpret_cast<const uint4 *>(p.x + (size_t)b * p.K);
       for (int i0 = part * 32 + lane; i0 < units; i0 += 4 * 32 * wpr) {
         uint4 v[4];
@@ -147,18 +148,44 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
           for (int j = 0; j < 4; ++j) {
             float2 f = __half22float2(h[j]);
             ss += f.x * f.x + f.y * f.y;
+            s1 += f.x + f.y;
           }
         }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) s_part[b * kWarps + part] = ss;
+      if (norm_ce) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      }
+      if (lane == 0) {
+        s_part[b * kWarps + part] = ss;
+        s_part1[b * kWarps + part] = s1;
+      }
     }
     __syncthreads();
     if (tid < p.B) {
-      float ss = 0.f;
-      for (int q = 0; q < wpr; ++q) ss += s_part[tid * kWarps + q];
-      s_stat[tid] = __half2float(__float2half_rn(1.0f / sqrtf(ss / (float)p.K + p.eps)));
+      float ss = 0.f, s1 = 0.f;
+      for (int q = 0; q < wpr; ++q) {
+        ss += s_part[tid * kWarps + q];
+        s1 += s_part1[tid * kWarps + q];
+      }
+      if (norm_ce) {
+        // one row: GetInPlaceNorm's arithmetic (fp32 mean inside the variance, no clamp); several rows: normInfKernel's (the
+        // fp16-rounded mean inside the variance, clamped at zero) -- custom_ops/NormCECodelets.cpp:65-112, NormCE.S:243-427
+        const float inv_n = 1.0f / (float)p.K;
+        if (p.B == 1) {
+          const float mean = s1 * inv_n;
+          s_mean[tid] = __half2float(__float2half_rn(mean));
+          s_stat[tid] = __half2float(__float2half_rn(1.0f / sqrtf(ss * inv_n - mean * mean + p.eps)));
+        } else {
+          const float mf = __half2float(__float2half_rn(s1 * inv_n));
+          s_mean[tid] = mf;
+          s_stat[tid] = __half2float(__float2half_rn(1.0f / sqrtf(fmaxf(ss * inv_n - mf * mf, 0.f) + p.eps)));
+        }
+      } else {
+        s_stat[tid] = __half2float(__float2half_rn(1.0f / sqrtf(ss / (float)p.K + p.eps)));
+      }
     }
     __syncthreads();
   }
@@ -170,12 +197,15 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(const LinearParams p) 
       const size_t k = (size_t)c_begin * CHUNK_K + (size_t)u * 8;
       __half *h = reinterpret_cast<__half *>(&v);
       const __half rb = do_norm ? __float2half_rn(s_stat[b]) : __half(0);
+      const __half mb = norm_ce ? __float2half_rn(s_mean[b]) : __half(0);
       uint4 gv = do_norm ? __ldg(reinterpret_cast<const uint4 *>(p.gamma + k)) : make_uint4(0, 0, 0, 0);
-      const __half *gh = reinterpret_cast<const __half *>(&gv);
+      uint4 bv = norm_ce ? __ldg(reinterpret_cast<const uint4 *>(p.beta + k)) : make_uint4(0, 0, 0, 0);
+      const __half *gh = reinterpret_cast<const __half *>(&gv), *bh = reinterpret_cast<const __half *>(&bv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         __half e = h[j];
-        if (do_norm) e = h_mul(h_mul(e, rb), gh[j]);
+        if (norm_ce) e = h_add(h_mul(h_mul(h_sub(e, mb), rb), gh[j]), bh[j]);
+        else if (do_norm) e = h_mul(h_mul(e, rb), gh[j]);
         if (do_cast) e = e4m3_round_h(__half2float(e) * p.inv_act_scale);
         h[j] = e;
       }
@@ -541,9 +571,10 @@ extern "C" int pt_linear(const pt_linear_args *a, void *stream) {
   const int ck = chunk_k(a->wfmt);
   PT_REQUIRE(a->n_out > 0 && a->k_in > 0 && a->k_in % ck == 0, "pt_linear: k_in=%d must be a positive multiple of %d", a->k_in, ck);
   PT_REQUIRE(a->x && a->packed_w && a->out, "pt_linear: null x / packed_w / out");
-  PT_REQUIRE(a->prologue >= PT_PRO_NONE && a->prologue <= PT_PRO_RMSNORM_CAST_FP8, "pt_linear: bad prologue %d", a->prologue);
+  PT_REQUIRE(a->prologue >= PT_PRO_NONE && a->prologue <= PT_PRO_NORMCE, "pt_linear: bad prologue %d", a->prologue);
   PT_REQUIRE(a->epilogue >= PT_EPI_STORE && a->epilogue <= PT_EPI_BIAS_RESIDUAL, "pt_linear: bad epilogue %d", a->epilogue);
-  const bool norm = a->prologue == PT_PRO_RMSNORM || a->prologue == PT_PRO_RMSNORM_CAST_FP8;
+  const bool norm = a->prologue == PT_PRO_RMSNORM || a->prologue == PT_PRO_RMSNORM_CAST_FP8 || a->prologue == PT_PRO_NORMCE;
+  PT_REQUIRE(a->prologue != PT_PRO_NORMCE || a->norm_beta, "pt_linear: NormCE prologue needs norm_beta");
   const bool cast = a->prologue == PT_PRO_CAST_FP8 || a->prologue == PT_PRO_RMSNORM_CAST_FP8;
   PT_REQUIRE(!norm || a->norm_gamma, "pt_linear: RMSNorm prologue needs norm_gamma");
   PT_REQUIRE(!cast || a->act_scale > 0.f, "pt_linear: FP8 activation cast needs act_scale > 0");
@@ -558,6 +589,7 @@ extern "C" int pt_linear(const pt_linear_args *a, void *stream) {
   p.w = (const unsigned char *)a->packed_w;
   p.x = (const __half *)a->x;
   p.gamma = (const __half *)a->norm_gamma;
+  p.beta = (const __half *)a->norm_beta;
   p.bias = (const __half *)a->bias;
   p.residual = (const __half *)a->residual;
   p.out = (__half *)a->out;

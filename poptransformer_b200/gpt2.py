@@ -104,9 +104,19 @@ class GPT2Decoder(DecodeLoop):
         self.graph = None
         torch.cuda.synchronize()
 
-    def _linear(self, x, pl, out, epilogue, bias, residual=None):
+    def _linear(self, x, pl, out, epilogue, bias, residual=None, norm=None):
+        """norm = (gamma, beta): the LayerNorm in front of the linear (ops.layer_norm_ce, NormCE arithmetic) runs as the kernel's
+        prologue instead of as a launch of its own."""
+        pro = {}
+        if norm is not None and self.batch <= 8:
+            pro = dict(prologue=ops.PRO_NORMCE, gamma=norm[0], beta=norm[1], eps=self.cfg.eps)
+        elif norm is not None:
+            # every block of the linear repeats the row statistics: from 16 rows on a launch of its own is faster
+            # (measured on B200, GPT-2 XL, 16 rows: 4.12 ms per step against 4.36 fused)
+            self._norm(x, norm, self.h)
+            x = self.h
         a = ops.linear_args(x, pl, out, epilogue=epilogue, bias=bias, residual=residual, workspace=self.lin_ws, error_flag=self.error_flag,
-                            pdl=self.pdl_linear)
+                            pdl=self.pdl_linear, **pro)
         ops.check(ops._lib.lib().pt_linear(ctypes.byref(a), ops._stream()), "pt_linear")
 
     def _norm(self, x, gb, out):
@@ -135,17 +145,14 @@ class GPT2Decoder(DecodeLoop):
         ops.embedding(self.wpe, self.pos, self.step_t, out=self.pe)
         ops.check(L_.pt_add_f16(ops._ptr(self.tok), ops._ptr(self.pe), self.tok.numel(), ops._ptr(self.x), ops._stream()), "pt_add_f16")
         for li, L in enumerate(self.layers):
-            self._norm(self.x, L["ln1"], self.h)
-            self._linear(self.h, L["c_attn"], self.qkv, ops.EPI_BIAS, L["b_attn"])
+            self._linear(self.x, L["c_attn"], self.qkv, ops.EPI_BIAS, L["b_attn"], norm=L["ln1"])
             a = ops.attn_args(self.qkv, self.step_t, self.caches[li], self.attn, self.h_loc, ops.ROPE_NONE, ops.SOFTMAX_F16, 1.0, None, None,
                               self.attn_ws, self.error_flag, pdl=self.pdl_attn)
             ops.check(L_.pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
             self._row_parallel(self.attn, L["c_proj"], L["b_proj"])
-            self._norm(self.x, L["ln2"], self.h)
-            self._linear(self.h, L["c_fc"], self.act, ops.EPI_BIAS_GELU, L["b_fc"])
+            self._linear(self.x, L["c_fc"], self.act, ops.EPI_BIAS_GELU, L["b_fc"], norm=L["ln2"])
             self._row_parallel(self.act, L["m_proj"], L["b_mproj"])
-        self._norm(self.x, self.ln_f, self.h)
-        self._linear(self.h, self.head, self.logits, ops.EPI_STORE, None)
+        self._linear(self.x, self.head, self.logits, ops.EPI_STORE, None, norm=self.ln_f)
 
     def enqueue_next(self):
         """Greedy head and the loop carry (layers/lm_head.py:47-57, models/base_model.py:313-335)."""

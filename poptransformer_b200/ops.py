@@ -23,7 +23,7 @@ from . import _lib
 from ._lib import AttnArgs, GemmArgs, LinearArgs, PtError, check
 
 W_INT4, W_FP16, W_FP8 = 0, 1, 2
-PRO_NONE, PRO_RMSNORM, PRO_CAST_FP8, PRO_RMSNORM_CAST_FP8 = 0, 1, 2, 3
+PRO_NONE, PRO_RMSNORM, PRO_CAST_FP8, PRO_RMSNORM_CAST_FP8, PRO_NORMCE = 0, 1, 2, 3, 4
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL = 0, 1, 2, 3, 4, 5
 ROPE_NONE, ROPE_LLAMA, ROPE_CHATGLM2 = 0, 1, 2
 SOFTMAX_F32, SOFTMAX_F16 = 0, 1
@@ -100,14 +100,14 @@ def linear_workspace(batch, n_out_max, max_ksplit=16, device="cuda"):
 
 
 def linear_args(x, pl, out, prologue=PRO_NONE, epilogue=EPI_STORE, gamma=None, eps=0.0, act_scale=0.0, bias=None,
-                residual=None, workspace=None, ksplit=0, out_ld=0, pdl=0, error_flag=None):
+                residual=None, workspace=None, ksplit=0, out_ld=0, pdl=0, error_flag=None, beta=None):
     a = LinearArgs()
     a.wfmt, a.batch, a.n_out, a.k_in, a.group = pl.wfmt, x.shape[0], pl.n_out, pl.k_in, pl.group
     a.prologue, a.epilogue, a.ksplit = prologue, epilogue, ksplit
     a.x, a.packed_w = _ptr(x), _ptr(pl.packed_w)
     a.norm_gamma, a.norm_eps, a.act_scale, a.w_scale = _ptr(gamma), eps, act_scale, pl.w_scale
     a.bias, a.residual, a.out, a.out_ld, a.pdl = _ptr(bias), _ptr(residual), _ptr(out), out_ld, pdl
-    a.error_flag = _ptr(error_flag)
+    a.error_flag, a.norm_beta = _ptr(error_flag), _ptr(beta)
     a.workspace = _ptr(workspace)
     a.workspace_bytes = workspace.numel() if workspace is not None else 0
     return a

@@ -265,6 +265,30 @@ def test_softmax_v3(cuda, dtype, stable):
     np.testing.assert_allclose(got.astype(np.float32), exp.astype(np.float32), rtol=tol, atol=tol * 1e-2)
 
 
+@pytest.mark.parametrize("rows,dim", [(1, 768), (16, 1600), (4, 2048)])
+def test_linear_normce_prologue(cuda, rows, dim):
+    """LayerNorm (NormCE arithmetic, one-row and many-row forms) as the prologue of the linear kernel against the op followed by
+    the plain linear: the normalised activations differ at most in the last fp16 bit of a few elements (statistics summed in
+    another order), so the outputs agree to the linear-layer tolerance."""
+    from poptransformer_b200 import ops
+    r = rng(30 + rows)
+    n = 1024
+    x = (r.standard_normal((rows, dim)) * 1.5 + 0.3).astype(np.float16)
+    g = (1 + 0.1 * r.standard_normal(dim)).astype(np.float16)
+    bt = (0.1 * r.standard_normal(dim)).astype(np.float16)
+    w = (r.standard_normal((n, dim)) * 0.02).astype(np.float16)
+    bias = r.standard_normal(n).astype(np.float16)
+    pl = ops.PackedLinear(ops.W_FP16, dev(w, cuda))
+    ws = ops.linear_workspace(rows, n, 16, cuda)
+    got = ops.linear(dev(x, cuda), pl, prologue=ops.PRO_NORMCE, gamma=dev(g, cuda), beta=dev(bt, cuda), eps=1e-5, epilogue=ops.EPI_BIAS,
+                     bias=dev(bias, cuda), workspace=ws).cpu().numpy().astype(np.float32)
+    h = O.norm_ce(x, g, bt, 1e-5)
+    exp = O.add_f16(O.matmul_f16(h, np.ascontiguousarray(w.T)), bias[None, :]).astype(np.float32)
+    np.testing.assert_allclose(got, exp, rtol=4e-3, atol=4e-3 * np.abs(exp).max())
+    with pytest.raises(ops.PtError, match="norm_beta"):
+        ops.linear(dev(x, cuda), pl, prologue=ops.PRO_NORMCE, gamma=dev(g, cuda), eps=1e-5, workspace=ws)
+
+
 def test_fp8_activation_kernels(cuda):
     """pt_rms_norm_fp8 and pt_swiglu_fp8 (the activation side of the FP8 linears that run on the GEMM) against the restatements:
     the casts are exact, so bytes only differ where the fp16 value in front of the cast differs by its last bit (the RMSNorm
