@@ -557,7 +557,7 @@ def run_secondary(args):
     e2e_s = min(e2e_t[1:])
 
     def packed(o):
-        if isinstance(o, ops.PackedLinear):
+        if isinstance(o, (ops.PackedLinear, ops.GemmWeight)):
             return o.nbytes
         if isinstance(o, dict):
             return sum(packed(v) for v in o.values())

@@ -339,13 +339,36 @@ __global__ void topk_kernel(const T *__restrict__ x, int dim, int k, T *__restri
   for (int r = 0; r < k; ++r) {
     float bv = -INFINITY;
     int bi = INT_MAX;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-      bool skip = false;
-      for (int c = 0; c < r; ++c) skip |= (chosen[c] == i);
-      if (skip) continue;
-      float v = to_f(xr[i]);
-      if (zero_sub && v == 0.f) v = -10000.f;
-      if (better(v, i, bv, bi) || bi == INT_MAX) { bv = v; bi = i; }
+    if (r == 0) {
+      // first round (the only one of the greedy head): nothing is masked yet, so eight loads of a thread can be in flight together
+      // (one dependent 2-byte load per trip made this kernel 29 us for 50257 logits)
+      constexpr int U = 8;
+      for (int i0 = threadIdx.x; i0 < dim; i0 += U * blockDim.x) {
+        float v[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          const int i = i0 + j * blockDim.x;
+          v[j] = i < dim ? to_f(xr[i]) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          const int i = i0 + j * blockDim.x;
+          if (i < dim) {
+            float w = v[j];
+            if (zero_sub && w == 0.f) w = -10000.f;
+            if (better(w, i, bv, bi) || bi == INT_MAX) { bv = w; bi = i; }
+          }
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        bool skip = false;
+        for (int c = 0; c < r; ++c) skip |= (chosen[c] == i);
+        if (skip) continue;
+        float v = to_f(xr[i]);
+        if (zero_sub && v == 0.f) v = -10000.f;
+        if (better(v, i, bv, bi) || bi == INT_MAX) { bv = v; bi = i; }
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
