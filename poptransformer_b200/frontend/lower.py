@@ -2,10 +2,11 @@
 
 `lower(builder)` takes the main graph recorded by `frontend/popart.py` from the reference's unmodified model code,
 checks that it is the decode loop this backend implements, reads the model's shapes and its checkpoint out of the graph, and
-returns (plan, decoder).  The check is structural: the loop body must consist of the embedding gather, `n_layer` blocks whose
-sequence of significant ops is exactly that of the reference's block (models/llama2/model.py:28-46, llama2/attention.py:64-122,
-llama2/mlp.py:20-28), the final norm + LM head + top-1 (layers/lm_head.py:47-57) and the loop carry
-(models/base_model.py:313-355); anything else is refused, as PopART refuses a graph it has no lowering for.
+returns (plan, decoder).  The check is structural: the loop body must consist of the embedding gather(s), `n_layer` blocks whose
+sequence of significant ops is exactly that of the reference's block (Llama-2: models/llama2/model.py:28-46,
+llama2/attention.py:64-122, llama2/mlp.py:20-28; GPT-2: models/gpt2/model.py:28-49, gpt2/attention.py:42-86, layers/mlp.py:34-41),
+the final norm + LM head + top-1 (layers/lm_head.py:47-57) and the loop carry (models/base_model.py:313-355); anything else is
+refused, as PopART refuses a graph it has no lowering for.
 """
 import re
 from types import SimpleNamespace
@@ -62,13 +63,113 @@ def _find_loop(main):
     return loop, loop.attrs["body"], int(_const_of(main, main, loop.inputs[0]))
 
 
+# the loop carry every decode model ends with: step_containers + step_loop_cond (models/base_model.py:313-355)
+_CARRY = ["onnx.add", "gc.dynamicupdate", "gc.dynamicslice", "onnx.equal", "onnx.where", "gc.dynamicupdate", "onnx.equal", "gc.bitwiseor"]
+
+# the significant ops of one GPT-2 block (models/gpt2/model.py:28-49, gpt2/attention.py:42-86, layers/mlp.py:34-41)
+_GPT2_BLOCK = [
+    "custom.NormCE", "onnx.matmul", "onnx.add",                                            # ln_1, c_attn + bias
+    "custom.KVCache", "onnx.matmul", "onnx.add", "custom.SoftmaxV3", "onnx.matmul",        # cache, scores, mask, softmax, P.V
+    "onnx.matmul", "onnx.add", "onnx.add",                                                 # c_proj + bias, residual
+    "custom.NormCE", "onnx.matmul", "onnx.add", "gc.gelu", "onnx.matmul", "onnx.add", "onnx.add",   # ln_2, MLP, residual
+]
+_GPT2_TAIL = ["custom.NormCE", "onnx.matmul", "onnx.topk"] + _CARRY                        # ln_f, tied head, k = 1, loop carry
+
+
+def _common_fields(main, body, nodes, max_loop):
+    """What every family's plan reads the same way: cache length, greedy head, pad / eos ids, early stop."""
+    kv = [n for n in nodes if n.op == "custom.KVCache"]
+    if any(n.attrs.get("fp8") for n in kv) or any(n.attrs["step_len"] != 1 or n.attrs["sequence_axis"] != 3 for n in kv):
+        raise UnsupportedGraph("expected fp16 KVCache ops with step_len 1 on axis 3")
+    if any(n.attrs.get("stable_mode") for n in nodes if n.op == "custom.SoftmaxV3"):
+        raise UnsupportedGraph("decode softmax is expected without max subtraction (stable_mode False)")
+    topk = next(n for n in nodes if n.op == "onnx.topk")
+    if int(_const_of(body, main, topk.inputs[1])) != 1:
+        raise UnsupportedGraph("only greedy decoding (top-k 1) is lowered")
+    equals = [n for n in nodes if n.op == "onnx.equal"]
+    cond = body.outputs[0]
+    return dict(n_kv_ops=len(kv), max_len=int(kv[0].attrs["max_len"]), max_loop=max_loop,
+                pad_id=int(_const_of(body, main, equals[0].inputs[1])), eos_id=int(_const_of(body, main, equals[1].inputs[1])),
+                early_stop=not any(n.op == "onnx.constant" and n.outputs[0] == cond for n in nodes))
+
+
+def _check_tail(nodes, start, want, what):
+    tail = _skeleton(nodes[start:])
+    if tail[len(want):] == ["onnx.reducesum", "onnx.less"]:      # early_stop: keep_going = sum(stop_mask) < batch (base_model.py:348-352)
+        tail = tail[:len(want)]
+    if tail != want:
+        raise UnsupportedGraph(f"the graph after the last block is not {what}: " + " ".join(_skeleton(nodes[start:])))
+
+
+def _analyze_gpt2(main, body, max_loop):
+    """GPT2DecModel (models/gpt2/model.py): token + position embedding, blocks of NormCE / fused c_attn / KVCache attention with the
+    fp16 softmax / c_proj / NormCE / GELU MLP, final NormCE and the head tied to the token embedding."""
+    names = list(main.initializers)
+    layer_ids = sorted({int(m.group(1)) for k in names for m in [re.match(r"transformer\.h\.(\d+)\.attn\.c_attn\.weight$", k)] if m})
+    n_layer = len(layer_ids)
+    if layer_ids != list(range(n_layer)) or "transformer.wpe.weight" not in main.initializers:
+        raise UnsupportedGraph("GPT-2 blocks are not numbered 0 .. n-1, or the position embedding is missing")
+    nodes = body.nodes
+    gathers = [i for i, n in enumerate(nodes) if n.op == "onnx.gather"]
+    if len(gathers) != 2 or [nodes[i].inputs[0] for i in gathers] != ["transformer.wte.weight", "transformer.wpe.weight"]:
+        raise UnsupportedGraph("expected the token and the position embedding gathers")
+    start = next(i for i in range(gathers[1] + 1, len(nodes)) if nodes[i].op == "onnx.add") + 1     # x = wte[id] + wpe[step]
+
+    def weight_matmul(key):
+        for i, n in enumerate(nodes):
+            if n.op == "onnx.matmul" and key in n.inputs:
+                return i
+        raise UnsupportedGraph(f"no matmul with {key}")
+    for l in range(n_layer):
+        j, adds = weight_matmul(f"transformer.h.{l}.mlp.c_proj.weight") + 1, 0
+        while j < len(nodes):                      # the block ends with the residual add, the second add behind the last matmul
+            adds += nodes[j].op == "onnx.add"
+            if adds == 2:
+                break
+            j += 1
+        sk = _skeleton(nodes[start:j + 1])
+        if sk != _GPT2_BLOCK:
+            diff = next((i for i, (a, b) in enumerate(zip(sk, _GPT2_BLOCK)) if a != b), min(len(sk), len(_GPT2_BLOCK)))
+            raise UnsupportedGraph(f"block {l} is not the reference's GPT-2 block (differs at significant op {diff}: "
+                                   f"{sk[diff] if diff < len(sk) else 'end'} vs {_GPT2_BLOCK[diff] if diff < len(_GPT2_BLOCK) else 'end'})")
+        start = j + 1
+    _check_tail(nodes, start, _GPT2_TAIL, "final LayerNorm + tied head + top-1 + loop carry")
+    head = next(n for n in nodes[start:] if n.op == "onnx.matmul")
+    tr = next((n for n in nodes if n.op == "onnx.transpose" and n.outputs[0] in head.inputs), None)
+    if tr is None or tr.inputs[0] != "transformer.wte.weight":
+        raise UnsupportedGraph("the head is expected to be tied to transformer.wte.weight (layers/lm_head.py:47-57)")
+
+    def shape_of(key):
+        a = main.initializers[key]
+        return tuple(a.shape) if a is not None else tuple(main.initializer_info[key]["shape"])
+    vocab, d_model = shape_of("transformer.wte.weight")
+    n_positions = shape_of("transformer.wpe.weight")[0]
+    split = next(n for n in nodes if n.op == "onnx.split")                      # q | (k, v) of block 0
+    reshape = next(n for n in nodes if n.op == "onnx.reshape" and n.inputs[0] == split.outputs[0])
+    batch, seq, n_head, head_dim = (int(v) for v in _const_of(body, main, reshape.inputs[1]))
+    if seq != 1 or n_head * head_dim != d_model:
+        raise UnsupportedGraph(f"q is reshaped to [{batch}, {seq}, {n_head}, {head_dim}]: expected one new token per step and n_head * head_dim = d_model")
+    norms = [n for n in nodes if n.op == "custom.NormCE"]
+    eps = {float(n.attrs["epsilon"]) for n in norms}
+    if len(norms) != 2 * n_layer + 1 or len(eps) != 1:
+        raise UnsupportedGraph("expected two NormCE ops per block plus the final one, with one epsilon")
+    common = _common_fields(main, body, nodes, max_loop)
+    if common.pop("n_kv_ops") != n_layer:
+        raise UnsupportedGraph("expected one KVCache op per block")
+    return SimpleNamespace(family="gpt2", n_layer=n_layer, d_model=int(d_model), n_head=n_head, head_dim=head_dim, ffn=4 * int(d_model), vocab=int(vocab),
+                           n_positions=int(n_positions), eps=eps.pop(), batch=batch, int4=False, **common)
+
+
 def analyze(main):
     """Recognises the recorded graph; returns a plan (family, shapes, ids, state_dict as numpy arrays in checkpoint layout)."""
     loop, body, max_loop = _find_loop(main)
     names = list(main.initializers)
+    if "transformer.wte.weight" in main.initializers and any(k.endswith("attn.c_attn.weight") for k in names):
+        return _analyze_gpt2(main, body, max_loop)
     layer_ids = sorted({int(m.group(1)) for k in names for m in [re.match(r"model\.layers\.(\d+)\.self_attn\.q_proj\.weight$", k)] if m})
     if not layer_ids or "model.embed_tokens.weight" not in main.initializers or "lm_head.weight" not in main.initializers:
-        raise UnsupportedGraph("no Llama-2 decode graph found (this front end lowers LLAMA2DecModel); initializers: " + ", ".join(names[:6]))
+        raise UnsupportedGraph("no Llama-2 or GPT-2 decode graph found (this front end lowers LLAMA2DecModel and GPT2DecModel); initializers: "
+                               + ", ".join(names[:6]))
     n_layer = len(layer_ids)
     if layer_ids != list(range(n_layer)):
         raise UnsupportedGraph("transformer blocks are not numbered 0 .. n-1")
@@ -150,9 +251,16 @@ def state_dict_from_initializers(main, plan):
     sd = {}
     for key, arr in main.initializers.items():
         if arr is None:
+            if plan.family == "gpt2" and key == "lm_head.weight":
+                continue
             raise UnsupportedGraph(f"initializer {key} has no data attached")
         a = np.asarray(arr)
-        is_linear = key.endswith(("_proj.weight", "lm_head.weight"))
+        if plan.family == "gpt2":
+            if key == "lm_head.weight":           # registered by the LM head layer but unused: the head multiplies by the transposed
+                continue                          # token embedding (analyze checked that), so this is not a checkpoint tensor
+            is_linear = a.ndim == 2 and key.endswith((".c_attn.weight", ".c_proj.weight", ".c_fc.weight"))
+        else:
+            is_linear = key.endswith(("_proj.weight", "lm_head.weight"))
         if is_linear and a.dtype != np.int8:
             a = np.ascontiguousarray(a.T)
         sd[key] = torch.from_numpy(np.ascontiguousarray(a))
@@ -163,11 +271,17 @@ def lower(main, device=None, **decoder_kwargs):
     """(plan, decoder) for the recorded graph, the decoder built on `device` (default: the current CUDA device)."""
     import torch
 
-    from poptransformer_b200 import llama
+    from poptransformer_b200 import gpt2, llama
     plan = analyze(main)
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
     sd = state_dict_from_initializers(main, plan)
+    if plan.family == "gpt2":
+        cfg = gpt2.GPT2Config(n_layer=plan.n_layer, d_model=plan.d_model, n_head=plan.n_head, vocab=plan.vocab, n_positions=plan.n_positions,
+                              max_len=plan.max_len, eps=plan.eps)
+        dec = gpt2.GPT2Decoder(cfg, sd, plan.batch, device=device, pad_id=plan.pad_id, eos_id=plan.eos_id, early_stop=plan.early_stop,
+                               **decoder_kwargs)
+        return plan, dec
     group = 0
     if plan.int4:
         w = sd["model.layers.0.self_attn.q_proj.weight"]

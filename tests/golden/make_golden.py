@@ -97,6 +97,8 @@ def run_graph_case(name, out_path):
     """Records the graph the reference's unmodified LLAMA2DecModel emits for case `name` with the PRODUCT's recorder
     (poptransformer_b200/frontend/popart.py) and stores it without weights: the fixture the GPU front-end test lowers on a machine
     that has no reference checkout.  Same checkpoint seeds as the golden id streams of the same case."""
+    if name in OTHER:
+        return run_graph_case_gpt2(name, out_path)
     dims, precision, group, batch, max_len, prompt, seed = CASES[name]
     sys.path[:0] = [os.path.join(ROOT, "poptransformer_b200", "frontend")]      # popart / poprt = the front end; hydra = the test stub
     import popart
@@ -137,6 +139,49 @@ def run_graph_case(name, out_path):
     plan = lower.analyze(model.graph)
     back = lower.state_dict_from_initializers(model.graph, plan)
     assert set(back) == set(sd) and all(np.array_equal(back[k].numpy().reshape(-1), sd[k].numpy().reshape(-1)) for k in sd)
+    print(name, "graph recorded:", len(model.graph.nodes), "main nodes,", plan)
+
+
+def run_graph_case_gpt2(name, out_path):
+    """The same for the reference's unmodified GPT2DecModel (case `gpt2_tiny_fp16`): its graph recorded by the product's recorder,
+    stored without weights, and the lowering's view of the checkpoint compared with the synthetic one."""
+    kind, dims, batch, max_len, prompt, seed = OTHER[name]
+    assert kind == "gpt2"
+    sys.path[:0] = [os.path.join(ROOT, "poptransformer_b200", "frontend")]
+    import popart
+    assert "frontend" in popart.__file__
+    from poptransformer_b200 import synth
+    from poptransformer_b200 import build as _b
+    tmp = tempfile.mkdtemp()
+    os.makedirs(os.path.join(tmp, "examples", kind))
+    os.symlink(_b.build(), os.path.join(tmp, "custom_ops.so"))
+    os.chdir(os.path.join(tmp, "examples", kind))
+    from poptransformer.utils.registry import REGISTRY
+    from poptransformer.utils.tensor_type import TensorType
+    for k, v in dict(num_replicas=1, batch_size=batch, batch_per_step=1, model_type="shard", enable_pipeline=False, precision="fp16").items():
+        REGISTRY.register(k, v)
+    REGISTRY.register("tensor_type", TensorType("fp16"))
+    REGISTRY.register("logger", logging.getLogger("poptransformer"))
+    from poptransformer.models.gpt2.model import GPT2DecModel
+    pad_id = dims["vocab"] - 1
+    sd = synth.gpt2_state_dict(**dims, seed=seed)
+    cfg = types.SimpleNamespace(vocab_size=dims["vocab"], n_embd=dims["d_model"], layer_norm_epsilon=1e-5, n_head=dims["n_head"],
+                                n_layer=dims["n_layer"], n_positions=dims["n_positions"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+
+    class GoldenGPT2(GPT2DecModel):
+        def prepare_state_dict(self):
+            self.hf_tokenizer, self.hf_config = types.SimpleNamespace(pad_token_id=pad_id, eos_token_id=pad_id - 1), cfg
+            self.state_dict = sd
+            self.register_state_dict()
+
+    model = GoldenGPT2(max_length=max_len, max_loop=max_len - 1, layer_per_ipu=[dims["n_layer"]], early_stop=False, topk=1, outline_blocks=None)
+    model.build_graph()
+    os.chdir(ROOT)
+    model.graph.save(out_path)
+    from poptransformer_b200.frontend import lower
+    plan = lower.analyze(model.graph)
+    back = lower.state_dict_from_initializers(model.graph, plan)
+    assert set(back) == set(sd) and all(np.array_equal(back[k].numpy(), sd[k].numpy()) for k in sd)
     print(name, "graph recorded:", len(model.graph.nodes), "main nodes,", plan)
 
 
@@ -327,5 +372,5 @@ if __name__ == "__main__":
         (run_tp_strategies if sys.argv[2] == "tp_strategies" else run_checkpoint_preprocess if sys.argv[2] == "checkpoint_preprocess"
          else run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
     else:
-        for case in list(CASES) + list(OTHER) + ["tp_strategies", "checkpoint_preprocess", "llama_tiny_int4:graph", "llama_tiny_fp16:graph"]:
+        for case in list(CASES) + list(OTHER) + ["tp_strategies", "checkpoint_preprocess", "llama_tiny_int4:graph", "llama_tiny_fp16:graph", "gpt2_tiny_fp16:graph"]:
             subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)
