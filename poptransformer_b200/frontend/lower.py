@@ -4,7 +4,8 @@
 checks that it is the decode loop this backend implements, reads the model's shapes and its checkpoint out of the graph, and
 returns (plan, decoder).  The check is structural: the loop body must consist of the embedding gather(s), `n_layer` blocks whose
 sequence of significant ops is exactly that of the reference's block (Llama-2: models/llama2/model.py:28-46,
-llama2/attention.py:64-122, llama2/mlp.py:20-28; GPT-2: models/gpt2/model.py:28-49, gpt2/attention.py:42-86, layers/mlp.py:34-41),
+llama2/attention.py:64-122, llama2/mlp.py:20-28; GPT-2: models/gpt2/model.py:28-49, gpt2/attention.py:42-86, layers/mlp.py:34-41;
+ChatGLM2: models/chatglm2/model.py:95-117, chatglm2/attention.py:98-302, chatglm2/mlp.py:51-59),
 the final norm + LM head + top-1 (layers/lm_head.py:47-57) and the loop carry (models/base_model.py:313-355); anything else is
 refused, as PopART refuses a graph it has no lowering for.
 """
@@ -20,7 +21,7 @@ class UnsupportedGraph(RuntimeError):
 
 # ops that only move / reshape / retype data, or produce constants: not part of a block's skeleton
 _LAYOUT_OPS = {"onnx.constant", "onnx.reshape", "onnx.transpose", "onnx.cast", "onnx.unsqueeze", "onnx.squeeze", "onnx.split", "onnx.concat",
-               "custom.Remap", "custom.Int4ToHalf"}
+               "onnx.expand", "custom.Remap", "custom.Int4ToHalf"}
 
 # the significant ops of one Llama-2 block, in the order the reference emits them
 _LLAMA_BLOCK = [
@@ -74,6 +75,20 @@ _GPT2_BLOCK = [
     "custom.NormCE", "onnx.matmul", "onnx.add", "gc.gelu", "onnx.matmul", "onnx.add", "onnx.add",   # ln_2, MLP, residual
 ]
 _GPT2_TAIL = ["custom.NormCE", "onnx.matmul", "onnx.topk"] + _CARRY                        # ln_f, tied head, k = 1, loop carry
+
+
+_RMSNORM = ["onnx.mul", "onnx.reducemean", "onnx.add", "onnx.sqrt", "onnx.reciprocal", "onnx.mul", "onnx.mul"]   # layers/rms_layer_norm.py:26-36
+# the significant ops of one ChatGLM2 block (models/chatglm2/model.py:95-117, chatglm2/attention.py:98-302, chatglm2/mlp.py:51-59)
+_CHATGLM2_BLOCK = _RMSNORM + [
+    "onnx.matmul", "onnx.add", "onnx.matmul", "onnx.add",                                   # query, key_value (+bias)
+    "onnx.matmul", "onnx.cos", "onnx.sin",                                                  # RoPE angle = step x inv_freq
+    "onnx.mul", "onnx.mul", "onnx.mul", "onnx.add",                                         # rotate the first half of q (interleaved pairs)
+    "onnx.mul", "onnx.mul", "onnx.mul", "onnx.add",                                         # rotate the first half of k
+    "custom.KVCache",
+    "onnx.matmul", "onnx.mul", "onnx.add", "custom.SoftmaxV3", "onnx.matmul",               # scores, scale, mask, softmax, P.V
+    "onnx.matmul", "onnx.add",                                                              # dense + residual
+] + _RMSNORM + ["onnx.matmul", "gc.swish", "onnx.matmul", "onnx.mul", "onnx.matmul", "onnx.add"]   # SwiGLU MLP + residual
+_CHATGLM2_TAIL = _RMSNORM + ["onnx.matmul", "onnx.topk"] + _CARRY
 
 
 def _common_fields(main, body, nodes, max_loop):
@@ -160,15 +175,71 @@ def _analyze_gpt2(main, body, max_loop):
                            n_positions=int(n_positions), eps=eps.pop(), batch=batch, int4=False, **common)
 
 
+def _analyze_chatglm2(main, body, max_loop):
+    """ChatGLM2DecModel (models/chatglm2/model.py): RMSNorm, query + key_value with bias, interleaved RoPE on half of each head,
+    multi-query KVCache attention with the fp16 softmax, dense, RMSNorm, SwiGLU MLP; final RMSNorm and the output layer."""
+    pre = "transformer.encoder.layers."
+    names = list(main.initializers)
+    layer_ids = sorted({int(m.group(1)) for k in names for m in [re.match(r"transformer\.encoder\.layers\.(\d+)\.self_attention\.query\.weight$", k)] if m})
+    n_layer = len(layer_ids)
+    if layer_ids != list(range(n_layer)) or "transformer.output_layer.weight" not in main.initializers:
+        raise UnsupportedGraph("ChatGLM2 blocks are not numbered 0 .. n-1, or the output layer is missing")
+    nodes = body.nodes
+    gathers = [i for i, n in enumerate(nodes) if n.op == "onnx.gather"]
+    if len(gathers) != 1 or nodes[gathers[0]].inputs[0] != "transformer.embedding.word_embeddings.weight":
+        raise UnsupportedGraph("expected one embedding gather from transformer.embedding.word_embeddings.weight")
+
+    def weight_matmul(key):
+        for i, n in enumerate(nodes):
+            if n.op == "onnx.matmul" and key in n.inputs:
+                return i
+        raise UnsupportedGraph(f"no matmul with {key}")
+    start = gathers[0] + 1
+    for l in range(n_layer):
+        j = weight_matmul(f"{pre}{l}.mlp.dense_4h_to_h.weight") + 1
+        while j < len(nodes) and nodes[j].op != "onnx.add":
+            j += 1
+        sk = _skeleton(nodes[start:j + 1])
+        if sk != _CHATGLM2_BLOCK:
+            diff = next((i for i, (a, b) in enumerate(zip(sk, _CHATGLM2_BLOCK)) if a != b), min(len(sk), len(_CHATGLM2_BLOCK)))
+            raise UnsupportedGraph(f"block {l} is not the reference's ChatGLM2 block (differs at significant op {diff}: "
+                                   f"{sk[diff] if diff < len(sk) else 'end'} vs {_CHATGLM2_BLOCK[diff] if diff < len(_CHATGLM2_BLOCK) else 'end'})")
+        start = j + 1
+    _check_tail(nodes, start, _CHATGLM2_TAIL, "final RMSNorm + output layer + top-1 + loop carry")
+
+    def shape_of(key):
+        a = main.initializers[key]
+        return tuple(a.shape) if a is not None else tuple(main.initializer_info[key]["shape"])
+    vocab, d_model = shape_of("transformer.embedding.word_embeddings.weight")
+    ffn = shape_of(f"{pre}0.mlp.dense_h_to_4h_1.weight")[1]                    # fp16 linears are stored [in, out]
+    q_add = nodes[weight_matmul(f"{pre}0.self_attention.query.weight") + 1]
+    q_reshape = next(n for n in nodes if n.op == "onnx.reshape" and n.inputs[0] == q_add.outputs[0])
+    batch, seq, n_head, head_dim = (int(v) for v in _const_of(body, main, q_reshape.inputs[1]))
+    kv_width = shape_of(f"{pre}0.self_attention.key_value.weight")[1]
+    n_group = kv_width // (2 * head_dim)
+    if seq != 1 or n_head * head_dim != d_model or n_group * 2 * head_dim != kv_width or n_head % max(n_group, 1):
+        raise UnsupportedGraph(f"q is reshaped to [{batch}, {seq}, {n_head}, {head_dim}] and key_value has {kv_width} features: expected one new "
+                               "token per step, n_head * head_dim = d_model and whole key / value groups")
+    first_norm_add = next(n for n in nodes[gathers[0]:] if n.op == "onnx.add")
+    eps = float(_const_of(body, main, first_norm_add.inputs[1]))
+    common = _common_fields(main, body, nodes, max_loop)
+    if common.pop("n_kv_ops") != n_layer:
+        raise UnsupportedGraph("expected one KVCache op per block")
+    return SimpleNamespace(family="chatglm2", n_layer=n_layer, d_model=int(d_model), n_head=n_head, n_group=int(n_group), head_dim=head_dim, ffn=int(ffn),
+                           vocab=int(vocab), eps=eps, batch=batch, int4=False, **common)
+
+
 def analyze(main):
     """Recognises the recorded graph; returns a plan (family, shapes, ids, state_dict as numpy arrays in checkpoint layout)."""
     loop, body, max_loop = _find_loop(main)
     names = list(main.initializers)
+    if "transformer.embedding.word_embeddings.weight" in main.initializers and any(k.endswith("self_attention.key_value.weight") for k in names):
+        return _analyze_chatglm2(main, body, max_loop)
     if "transformer.wte.weight" in main.initializers and any(k.endswith("attn.c_attn.weight") for k in names):
         return _analyze_gpt2(main, body, max_loop)
     layer_ids = sorted({int(m.group(1)) for k in names for m in [re.match(r"model\.layers\.(\d+)\.self_attn\.q_proj\.weight$", k)] if m})
     if not layer_ids or "model.embed_tokens.weight" not in main.initializers or "lm_head.weight" not in main.initializers:
-        raise UnsupportedGraph("no Llama-2 or GPT-2 decode graph found (this front end lowers LLAMA2DecModel and GPT2DecModel); initializers: "
+        raise UnsupportedGraph("no Llama-2, GPT-2 or ChatGLM2 decode graph found (this front end lowers LLAMA2DecModel, GPT2DecModel and ChatGLM2DecModel); initializers: "
                                + ", ".join(names[:6]))
     n_layer = len(layer_ids)
     if layer_ids != list(range(n_layer)):
@@ -259,6 +330,8 @@ def state_dict_from_initializers(main, plan):
             if key == "lm_head.weight":           # registered by the LM head layer but unused: the head multiplies by the transposed
                 continue                          # token embedding (analyze checked that), so this is not a checkpoint tensor
             is_linear = a.ndim == 2 and key.endswith((".c_attn.weight", ".c_proj.weight", ".c_fc.weight"))
+        elif plan.family == "chatglm2":
+            is_linear = a.ndim == 2 and "word_embeddings" not in key
         else:
             is_linear = key.endswith(("_proj.weight", "lm_head.weight"))
         if is_linear and a.dtype != np.int8:
@@ -271,7 +344,7 @@ def lower(main, device=None, **decoder_kwargs):
     """(plan, decoder) for the recorded graph, the decoder built on `device` (default: the current CUDA device)."""
     import torch
 
-    from poptransformer_b200 import gpt2, llama
+    from poptransformer_b200 import chatglm2, gpt2, llama
     plan = analyze(main)
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
@@ -281,6 +354,12 @@ def lower(main, device=None, **decoder_kwargs):
                               max_len=plan.max_len, eps=plan.eps)
         dec = gpt2.GPT2Decoder(cfg, sd, plan.batch, device=device, pad_id=plan.pad_id, eos_id=plan.eos_id, early_stop=plan.early_stop,
                                **decoder_kwargs)
+        return plan, dec
+    if plan.family == "chatglm2":
+        cfg = chatglm2.ChatGLM2Config(n_layer=plan.n_layer, d_model=plan.d_model, n_head=plan.n_head, n_group=plan.n_group, ffn=plan.ffn,
+                                      vocab=plan.vocab, max_len=plan.max_len, eps=plan.eps, precision="fp16")
+        dec = chatglm2.ChatGLM2Decoder(cfg, sd, plan.batch, device=device, pad_id=plan.pad_id, eos_id=plan.eos_id, early_stop=plan.early_stop,
+                                       **decoder_kwargs)
         return plan, dec
     group = 0
     if plan.int4:

@@ -98,7 +98,7 @@ def run_graph_case(name, out_path):
     (poptransformer_b200/frontend/popart.py) and stores it without weights: the fixture the GPU front-end test lowers on a machine
     that has no reference checkout.  Same checkpoint seeds as the golden id streams of the same case."""
     if name in OTHER:
-        return run_graph_case_gpt2(name, out_path)
+        return run_graph_case_other(name, out_path)
     dims, precision, group, batch, max_len, prompt, seed = CASES[name]
     sys.path[:0] = [os.path.join(ROOT, "poptransformer_b200", "frontend")]      # popart / poprt = the front end; hydra = the test stub
     import popart
@@ -142,11 +142,12 @@ def run_graph_case(name, out_path):
     print(name, "graph recorded:", len(model.graph.nodes), "main nodes,", plan)
 
 
-def run_graph_case_gpt2(name, out_path):
-    """The same for the reference's unmodified GPT2DecModel (case `gpt2_tiny_fp16`): its graph recorded by the product's recorder,
-    stored without weights, and the lowering's view of the checkpoint compared with the synthetic one."""
+def run_graph_case_other(name, out_path):
+    """The same for the reference's unmodified GPT2DecModel / ChatGLM2DecModel (cases `gpt2_tiny_fp16`, `chatglm2_tiny_fp16`): the
+    graph recorded by the product's recorder, stored without weights, and the lowering's view of the checkpoint compared with
+    the synthetic one."""
     kind, dims, batch, max_len, prompt, seed = OTHER[name]
-    assert kind == "gpt2"
+    assert kind in ("gpt2", "chatglm2")
     sys.path[:0] = [os.path.join(ROOT, "poptransformer_b200", "frontend")]
     import popart
     assert "frontend" in popart.__file__
@@ -162,13 +163,20 @@ def run_graph_case_gpt2(name, out_path):
         REGISTRY.register(k, v)
     REGISTRY.register("tensor_type", TensorType("fp16"))
     REGISTRY.register("logger", logging.getLogger("poptransformer"))
-    from poptransformer.models.gpt2.model import GPT2DecModel
     pad_id = dims["vocab"] - 1
-    sd = synth.gpt2_state_dict(**dims, seed=seed)
-    cfg = types.SimpleNamespace(vocab_size=dims["vocab"], n_embd=dims["d_model"], layer_norm_epsilon=1e-5, n_head=dims["n_head"],
-                                n_layer=dims["n_layer"], n_positions=dims["n_positions"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+    if kind == "gpt2":
+        from poptransformer.models.gpt2.model import GPT2DecModel as Base
+        sd = synth.gpt2_state_dict(**dims, seed=seed)
+        cfg = types.SimpleNamespace(vocab_size=dims["vocab"], n_embd=dims["d_model"], layer_norm_epsilon=1e-5, n_head=dims["n_head"],
+                                    n_layer=dims["n_layer"], n_positions=dims["n_positions"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+    else:
+        from poptransformer.models.chatglm2.model import ChatGLM2DecModel as Base
+        sd = synth.chatglm2_state_dict(**dims, seed=seed)
+        cfg = types.SimpleNamespace(padded_vocab_size=dims["vocab"], hidden_size=dims["d_model"], layernorm_epsilon=1e-5,
+                                    multi_query_group_num=dims["n_group"], num_attention_heads=dims["n_head"], ffn_hidden_size=dims["ffn"],
+                                    num_layers=dims["n_layer"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
 
-    class GoldenGPT2(GPT2DecModel):
+    class GoldenGPT2(Base):
         def prepare_state_dict(self):
             self.hf_tokenizer, self.hf_config = types.SimpleNamespace(pad_token_id=pad_id, eos_token_id=pad_id - 1), cfg
             self.state_dict = sd
@@ -372,5 +380,5 @@ if __name__ == "__main__":
         (run_tp_strategies if sys.argv[2] == "tp_strategies" else run_checkpoint_preprocess if sys.argv[2] == "checkpoint_preprocess"
          else run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
     else:
-        for case in list(CASES) + list(OTHER) + ["tp_strategies", "checkpoint_preprocess", "llama_tiny_int4:graph", "llama_tiny_fp16:graph", "gpt2_tiny_fp16:graph"]:
+        for case in list(CASES) + list(OTHER) + ["tp_strategies", "checkpoint_preprocess", "llama_tiny_int4:graph", "llama_tiny_fp16:graph", "gpt2_tiny_fp16:graph", "chatglm2_tiny_fp16:graph"]:
             subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)

@@ -42,18 +42,30 @@ def test_fixture_graph_is_recognised(case):
     assert plan.int4 == (int(z["group"]) != 0) and not plan.early_stop and abs(plan.eps - 1e-5) < 1e-9
 
 
-def test_gpt2_fixture_graph_is_recognised():
+OTHER = {"gpt2_tiny_fp16": "gpt2", "chatglm2_tiny_fp16": "chatglm2"}
+
+
+def _other_dims(case):
+    z = np.load(os.path.join(HERE, "golden", case + ".npz"))
+    return z, dict(zip((str(k) for k in z["dims_keys"]), (int(v) for v in z["dims_vals"])))
+
+
+@pytest.mark.parametrize("case", list(OTHER))
+def test_other_family_fixture_graph_is_recognised(case):
     from poptransformer_b200.frontend import lower
-    z = np.load(os.path.join(HERE, "golden", "gpt2_tiny_fp16.npz"))
-    dims = dict(zip((str(k) for k in z["dims_keys"]), (int(v) for v in z["dims_vals"])))
-    plan = lower.analyze(_fixture("gpt2_tiny_fp16"))
-    assert (plan.family, plan.n_layer, plan.d_model, plan.n_head, plan.vocab, plan.n_positions) == (
-        "gpt2", dims["n_layer"], dims["d_model"], dims["n_head"], dims["vocab"], dims["n_positions"])
+    z, dims = _other_dims(case)
+    plan = lower.analyze(_fixture(case))
+    assert (plan.family, plan.n_layer, plan.d_model, plan.n_head, plan.vocab) == (OTHER[case], dims["n_layer"], dims["d_model"], dims["n_head"], dims["vocab"])
+    if plan.family == "gpt2":
+        assert plan.n_positions == dims["n_positions"]
+    else:
+        assert (plan.n_group, plan.ffn) == (dims["n_group"], dims["ffn"])
     assert (plan.batch, plan.max_len, plan.max_loop, plan.pad_id) == (int(z["batch"]), int(z["max_len"]), int(z["max_len"]) - 1, int(z["pad_id"]))
     assert not plan.early_stop and abs(plan.eps - 1e-5) < 1e-9
-    g = _fixture("gpt2_tiny_fp16")
+    g = _fixture(case)
     body = next(n for n in g.nodes if n.op == "onnx.loop").attrs["body"]
-    next(n for n in body.nodes if n.op == "gc.gelu").op = "gc.swish"          # not the reference's GPT-2 block any more
+    act = next(n for n in body.nodes if n.op in ("gc.gelu", "gc.swish"))
+    act.op = "gc.swish" if act.op == "gc.gelu" else "gc.gelu"                 # not the reference's block any more
     with pytest.raises(lower.UnsupportedGraph, match="block 0"):
         lower.analyze(g)
 
@@ -68,12 +80,12 @@ def test_other_graphs_are_refused():
         lower.analyze(g)
     g2 = _fixture("llama_tiny_fp16")
     g2.initializers = {k.replace("model.layers", "transformer.h"): v for k, v in g2.initializers.items()}
-    with pytest.raises(lower.UnsupportedGraph, match="no Llama-2 or GPT-2 decode graph"):
+    with pytest.raises(lower.UnsupportedGraph, match="no Llama-2, GPT-2 or ChatGLM2 decode graph"):
         lower.analyze(g2)
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "poptransformer")), reason="reference checkout not present")
-@pytest.mark.parametrize("case", CASES + ["gpt2_tiny_fp16"])
+@pytest.mark.parametrize("case", CASES + ["gpt2_tiny_fp16", "chatglm2_tiny_fp16"])
 def test_reference_model_code_records_the_fixture(case, tmp_path):
     out = str(tmp_path / "graph.json")
     subprocess.run([sys.executable, os.path.join(HERE, "golden", "make_golden.py"), REFERENCE, case + ":graph", out], check=True, capture_output=True)
@@ -123,23 +135,25 @@ def test_session_runs_the_recorded_graph_on_the_gpu(case, cuda):
 
 
 @pytest.mark.gpu
-def test_session_runs_the_recorded_gpt2_graph_on_the_gpu(cuda):
-    """The graph the reference's unmodified GPT2DecModel recorded, its initializers filled with the synthetic checkpoint in the
-    reference's storage layout, through InferenceSession: the id stream of the reference's own run (tests/golden/gpt2_tiny_fp16.npz)
-    up to numerical ties of the restatement's top two logits."""
-    from oracle import gpt2_np
+@pytest.mark.parametrize("case", list(OTHER))
+def test_session_runs_the_recorded_graph_of_another_family_on_the_gpu(case, cuda):
+    """The graph the reference's unmodified GPT2DecModel / ChatGLM2DecModel recorded, its initializers filled with the synthetic
+    checkpoint in the reference's storage layout, through InferenceSession: the id stream of the reference's own run
+    (tests/golden/<case>.npz) up to numerical ties of the restatement's top two logits."""
+    from oracle import chatglm2_np, gpt2_np
     from poptransformer_b200 import synth
     popart = _frontend()
-    z = np.load(os.path.join(HERE, "golden", "gpt2_tiny_fp16.npz"))
-    dims = dict(zip((str(k) for k in z["dims_keys"]), (int(v) for v in z["dims_vals"])))
+    z, dims = _other_dims(case)
+    fam = OTHER[case]
     batch, max_len, prompt = int(z["batch"]), int(z["max_len"]), int(z["prompt"])
-    sd = synth.gpt2_state_dict(**dims, seed=int(z["seed"]))
-    g = _fixture("gpt2_tiny_fp16")
+    sd = (synth.gpt2_state_dict if fam == "gpt2" else synth.chatglm2_state_dict)(**dims, seed=int(z["seed"]))
+    linear = (".c_attn.weight", ".c_proj.weight", ".c_fc.weight") if fam == "gpt2" else (".weight",)
+    g = _fixture(case)
     for key in g.initializers:
-        if key == "lm_head.weight":
+        if fam == "gpt2" and key == "lm_head.weight":
             continue                  # unused: the head is tied to the token embedding
         a = sd[key].numpy()
-        if a.ndim == 2 and key.endswith((".c_attn.weight", ".c_proj.weight", ".c_fc.weight")):
+        if a.ndim == 2 and key.endswith(linear) and "word_embeddings" not in key and "wte" not in key and "wpe" not in key:
             a = np.ascontiguousarray(a.T)            # layers/linear.py:32 stores [in, out]
         g.initializers[key] = a.reshape(g.initializer_info[key]["shape"])
     session = popart.InferenceSession(fnModel=g.getModelProto(), dataFlow=popart.DataFlow(1, {"Loop:0": popart.AnchorReturnType("ALL"),
@@ -148,13 +162,17 @@ def test_session_runs_the_recorded_gpt2_graph_on_the_gpu(cuda):
     session.prepareDevice()
     session.weightsFromHost()
     anchors = session.initAnchorArrays()
-    assert session.plan.family == "gpt2"
+    assert session.plan.family == fam
     for _ in range(2):
         session.run(popart.PyStepIO({"input_ids": z["input_ids"]}, anchors))
     got, exp = anchors["Loop:0"], z["output_ids"]
     assert int(anchors["Loop:1"]) == max_len - 1
     assert np.array_equal(got[:, :prompt], exp[:, :prompt])
-    orc = gpt2_np.GPT2Oracle(gpt2_np.GPT2Config(**dims, max_len=max_len), {k: v.numpy() for k, v in sd.items()}, batch)
+    sd_np = {k: v.numpy() for k, v in sd.items()}
+    if fam == "gpt2":
+        orc = gpt2_np.GPT2Oracle(gpt2_np.GPT2Config(**dims, max_len=max_len), sd_np, batch)
+    else:
+        orc = chatglm2_np.ChatGLM2Oracle(chatglm2_np.ChatGLM2Config(**dims, max_len=max_len), sd_np, batch)
     orc.reset()
     logits = [orc.logits(exp[:, t], t)[0].astype(np.float32) for t in range(max_len - 1)]
     for b in range(batch):
