@@ -5,7 +5,8 @@ checks that it is the decode loop this backend implements, reads the model's sha
 returns (plan, decoder).  The check is structural: the loop body must consist of the embedding gather(s), `n_layer` blocks whose
 sequence of significant ops is exactly that of the reference's block (Llama-2: models/llama2/model.py:28-46,
 llama2/attention.py:64-122, llama2/mlp.py:20-28; GPT-2: models/gpt2/model.py:28-49, gpt2/attention.py:42-86, layers/mlp.py:34-41;
-ChatGLM2: models/chatglm2/model.py:95-117, chatglm2/attention.py:98-302, chatglm2/mlp.py:51-59),
+ChatGLM2: models/chatglm2/model.py:95-117, chatglm2/attention.py:98-302, chatglm2/mlp.py:51-59; RWKV-4: models/rwkv/model.py:189-213,
+rwkv/attention.py:46-105, rwkv/ffn.py:36-59),
 the final norm + LM head + top-1 (layers/lm_head.py:47-57) and the loop carry (models/base_model.py:313-355); anything else is
 refused, as PopART refuses a graph it has no lowering for.
 """
@@ -229,17 +230,90 @@ def _analyze_chatglm2(main, body, max_loop):
                            vocab=int(vocab), eps=eps, batch=batch, int4=False, **common)
 
 
+# RWKV-4 (models/rwkv/model.py:189-213, rwkv/attention.py:46-105, rwkv/ffn.py:36-59): token-shift mix, the WKV recurrence written
+# out in elementary ops, receptance gates, relu^2 channel mixing; every `rescale_every` blocks the hidden state is halved
+_RWKV_MIX = ["onnx.mul", "onnx.sub", "onnx.mul", "onnx.add"]                 # x * mix + (1 - mix) * previous x
+_RWKV_WKV = ["onnx.add", "onnx.greater", "onnx.where", "onnx.sub", "onnx.exp", "onnx.sub", "onnx.exp", "onnx.mul", "onnx.mul", "onnx.add", "onnx.mul",
+             "onnx.add", "onnx.div",                                          # output = numerator / denominator with the running maximum
+             "onnx.exp", "onnx.sub", "onnx.greater", "onnx.where", "onnx.sub", "onnx.exp", "onnx.sub", "onnx.exp", "onnx.mul", "onnx.mul", "onnx.add",
+             "onnx.mul", "onnx.add"]                                          # the three new states
+_RWKV_ATT = ["custom.NormCE"] + 3 * _RWKV_MIX + 3 * ["onnx.matmul"] + ["onnx.sigmoid"] + _RWKV_WKV + ["onnx.mul", "onnx.matmul", "onnx.add"]
+_RWKV_FFN = ["custom.NormCE"] + 2 * _RWKV_MIX + ["onnx.matmul", "onnx.relu", "onnx.mul", "onnx.matmul", "onnx.matmul", "onnx.sigmoid", "onnx.mul", "onnx.add"]
+_RWKV_CARRY = ["onnx.add", "gc.dynamicslice", "onnx.equal", "onnx.where", "gc.dynamicupdate", "onnx.equal", "gc.bitwiseor"]   # no attention mask to update
+_RWKV_TAIL = ["custom.NormCE", "onnx.matmul", "onnx.topk"] + _RWKV_CARRY
+
+
+def _analyze_rwkv(main, body, max_loop, loop):
+    """RWKVDecodeModel (models/rwkv/model.py): the recurrent states travel as loop-carried tensors, five per block."""
+    names = list(main.initializers)
+    layer_ids = sorted({int(m.group(1)) for k in names for m in [re.match(r"rwkv\.blocks\.(\d+)\.ln1\.weight$", k)] if m})
+    n_layer = len(layer_ids)
+    if layer_ids != list(range(n_layer)) or "head.weight" not in main.initializers:
+        raise UnsupportedGraph("RWKV blocks are not numbered 0 .. n-1, or the head is missing")
+    nodes = body.nodes
+    gathers = [i for i, n in enumerate(nodes) if n.op == "onnx.gather"]
+    if len(gathers) != 1 or nodes[gathers[0]].inputs[0] != "rwkv.embeddings.weight":
+        raise UnsupportedGraph("expected one embedding gather from rwkv.embeddings.weight")
+    head = [i for i, n in enumerate(nodes) if n.op == "onnx.matmul" and "head.weight" in n.inputs]
+    if len(head) != 1:
+        raise UnsupportedGraph("expected one head matmul")
+    tail_start = max(i for i in range(head[0]) if nodes[i].op == "custom.NormCE")        # ln_out
+    got = _skeleton(nodes[gathers[0] + 1:tail_start])
+    rescale_every = None
+    for cand in range(0, n_layer + 1):
+        want = []
+        for l in range(n_layer):
+            want += (["custom.NormCE"] if l == 0 else []) + _RWKV_ATT + _RWKV_FFN + (["onnx.div"] if cand and (l + 1) % cand == 0 else [])
+        if want == got:
+            rescale_every = cand
+            break
+    if rescale_every is None:
+        raise UnsupportedGraph("block 0 .. n-1 are not the reference's RWKV-4 blocks (pre_ln, time mixing with the WKV recurrence, channel mixing, "
+                               "halving every rescale_every blocks)")
+    halvings = [n for n in nodes[:tail_start] if n.op == "onnx.div" and any(c.op == "onnx.constant" and c.outputs[0] == n.inputs[1] for c in nodes)]
+    if any(float(_const_of(body, main, n.inputs[1])) != 2.0 for n in halvings):
+        raise UnsupportedGraph("the hidden state is expected to be halved (divided by 2) at the rescale points")
+    _check_tail(nodes, tail_start, _RWKV_TAIL, "final LayerNorm + head + top-1 + loop carry")
+
+    def shape_of(key):
+        a = main.initializers[key]
+        return tuple(a.shape) if a is not None else tuple(main.initializer_info[key]["shape"])
+    vocab, d_model = shape_of("rwkv.embeddings.weight")
+    ffn = shape_of("rwkv.blocks.0.feed_forward.key.weight")[1]                 # fp16 linears are stored [in, out]
+    eps = {float(n.attrs["epsilon"]) for n in nodes if n.op == "custom.NormCE"}
+    if len(eps) != 1:
+        raise UnsupportedGraph("expected one epsilon for every NormCE")
+    info = main.input_info.get("input_ids")
+    if not info or len(info["shape"]) != 2:
+        raise UnsupportedGraph("input_ids is expected as a typed [batch, max_length] input of the main graph")
+    batch, max_len = (int(v) for v in info["shape"])
+    if len(loop.inputs) != 5 + 5 * n_layer:
+        raise UnsupportedGraph(f"expected five loop-carried states per block, the loop has {len(loop.inputs) - 5} state inputs")
+    topk = next(n for n in nodes if n.op == "onnx.topk")
+    if int(_const_of(body, main, topk.inputs[1])) != 1:
+        raise UnsupportedGraph("only greedy decoding (top-k 1) is lowered")
+    equals = [n for n in nodes if n.op == "onnx.equal"]
+    cond = body.outputs[0]
+    return SimpleNamespace(family="rwkv", n_layer=n_layer, d_model=int(d_model), ffn=int(ffn), vocab=int(vocab), rescale_every=rescale_every, eps=eps.pop(),
+                           batch=batch, max_len=max_len, max_loop=max_loop, int4=False,
+                           pad_id=int(_const_of(body, main, equals[0].inputs[1])), eos_id=int(_const_of(body, main, equals[1].inputs[1])),
+                           early_stop=not any(n.op == "onnx.constant" and n.outputs[0] == cond for n in nodes))
+
+
 def analyze(main):
     """Recognises the recorded graph; returns a plan (family, shapes, ids, state_dict as numpy arrays in checkpoint layout)."""
     loop, body, max_loop = _find_loop(main)
     names = list(main.initializers)
+    if "rwkv.embeddings.weight" in main.initializers:
+        return _analyze_rwkv(main, body, max_loop, loop)
     if "transformer.embedding.word_embeddings.weight" in main.initializers and any(k.endswith("self_attention.key_value.weight") for k in names):
         return _analyze_chatglm2(main, body, max_loop)
     if "transformer.wte.weight" in main.initializers and any(k.endswith("attn.c_attn.weight") for k in names):
         return _analyze_gpt2(main, body, max_loop)
     layer_ids = sorted({int(m.group(1)) for k in names for m in [re.match(r"model\.layers\.(\d+)\.self_attn\.q_proj\.weight$", k)] if m})
     if not layer_ids or "model.embed_tokens.weight" not in main.initializers or "lm_head.weight" not in main.initializers:
-        raise UnsupportedGraph("no Llama-2, GPT-2 or ChatGLM2 decode graph found (this front end lowers LLAMA2DecModel, GPT2DecModel and ChatGLM2DecModel); initializers: "
+        raise UnsupportedGraph("no Llama-2, GPT-2, ChatGLM2 or RWKV decode graph found (this front end lowers LLAMA2DecModel, GPT2DecModel, ChatGLM2DecModel and "
+                               "RWKVDecodeModel); initializers: "
                                + ", ".join(names[:6]))
     n_layer = len(layer_ids)
     if layer_ids != list(range(n_layer)):
@@ -332,6 +406,8 @@ def state_dict_from_initializers(main, plan):
             is_linear = a.ndim == 2 and key.endswith((".c_attn.weight", ".c_proj.weight", ".c_fc.weight"))
         elif plan.family == "chatglm2":
             is_linear = a.ndim == 2 and "word_embeddings" not in key
+        elif plan.family == "rwkv":
+            is_linear = a.ndim == 2 and key.endswith(".weight") and "embeddings" not in key
         else:
             is_linear = key.endswith(("_proj.weight", "lm_head.weight"))
         if is_linear and a.dtype != np.int8:
@@ -344,7 +420,7 @@ def lower(main, device=None, **decoder_kwargs):
     """(plan, decoder) for the recorded graph, the decoder built on `device` (default: the current CUDA device)."""
     import torch
 
-    from poptransformer_b200 import chatglm2, gpt2, llama
+    from poptransformer_b200 import chatglm2, gpt2, llama, rwkv
     plan = analyze(main)
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
@@ -354,6 +430,11 @@ def lower(main, device=None, **decoder_kwargs):
                               max_len=plan.max_len, eps=plan.eps)
         dec = gpt2.GPT2Decoder(cfg, sd, plan.batch, device=device, pad_id=plan.pad_id, eos_id=plan.eos_id, early_stop=plan.early_stop,
                                **decoder_kwargs)
+        return plan, dec
+    if plan.family == "rwkv":
+        cfg = rwkv.RWKVConfig(n_layer=plan.n_layer, d_model=plan.d_model, ffn=plan.ffn, vocab=plan.vocab, max_len=plan.max_len,
+                              rescale_every=plan.rescale_every, eps=plan.eps)
+        dec = rwkv.RWKVDecoder(cfg, sd, plan.batch, device=device, pad_id=plan.pad_id, eos_id=plan.eos_id, early_stop=plan.early_stop, **decoder_kwargs)
         return plan, dec
     if plan.family == "chatglm2":
         cfg = chatglm2.ChatGLM2Config(n_layer=plan.n_layer, d_model=plan.d_model, n_head=plan.n_head, n_group=plan.n_group, ffn=plan.ffn,

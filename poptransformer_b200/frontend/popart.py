@@ -115,6 +115,7 @@ class Builder:
         self.parent = parent
         self.root = parent.root if parent else self
         self.nodes, self.inputs, self.outputs, self.initializers = [], [], [], {}
+        self.input_info = {}       # shape and dtype of the inputs that were declared with a TensorInfo
         self._scope = []
         self.aiOnnx = _Namespace(self, "onnx")
         self.aiGraphcore = _Namespace(self, "gc")
@@ -155,6 +156,8 @@ class Builder:
         name = self._name(rest, debugContext, "input")
         tid = name if name not in self.inputs else self._new_id(name)
         self.inputs.append(tid)
+        if isinstance(info, TensorInfo):
+            self.input_info[tid] = {"shape": [int(v) for v in info.shape], "dtype": str(info.dtype)}
         return tid
 
     def addUntypedInputTensor(self, name="input"):
@@ -244,7 +247,7 @@ class Builder:
             if isinstance(v, (list, tuple)):
                 return [enc(x) for x in v]
             return v
-        return {"name": self.name, "inputs": self.inputs, "outputs": self.outputs,
+        return {"name": self.name, "inputs": self.inputs, "outputs": self.outputs, "input_info": self.input_info,
                 "initializers": {k: {"shape": list(v.shape), "dtype": str(v.dtype)} for k, v in self.initializers.items()},
                 "nodes": [{"op": n.op, "inputs": n.inputs, "outputs": n.outputs, "attrs": {k: enc(v) for k, v in n.attrs.items()}} for n in self.nodes]}
 
@@ -252,6 +255,7 @@ class Builder:
     def from_dict(cls, d, parent=None):
         b = cls(parent=parent)
         b.name, b.inputs, b.outputs = d["name"], list(d["inputs"]), list(d["outputs"])
+        b.input_info = dict(d.get("input_info", {}))
         b.initializers = {k: None for k in d["initializers"]}     # arrays are attached by the caller
         b.initializer_info = d["initializers"]
 

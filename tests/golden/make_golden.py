@@ -143,11 +143,10 @@ def run_graph_case(name, out_path):
 
 
 def run_graph_case_other(name, out_path):
-    """The same for the reference's unmodified GPT2DecModel / ChatGLM2DecModel (cases `gpt2_tiny_fp16`, `chatglm2_tiny_fp16`): the
-    graph recorded by the product's recorder, stored without weights, and the lowering's view of the checkpoint compared with
-    the synthetic one."""
+    """The same for the reference's unmodified GPT2DecModel / ChatGLM2DecModel / RWKVDecodeModel (cases `gpt2_tiny_fp16`,
+    `chatglm2_tiny_fp16`, `rwkv_tiny_fp16`): the graph recorded by the product's recorder, stored without weights, and the
+    lowering's view of the checkpoint compared with the synthetic one."""
     kind, dims, batch, max_len, prompt, seed = OTHER[name]
-    assert kind in ("gpt2", "chatglm2")
     sys.path[:0] = [os.path.join(ROOT, "poptransformer_b200", "frontend")]
     import popart
     assert "frontend" in popart.__file__
@@ -169,12 +168,18 @@ def run_graph_case_other(name, out_path):
         sd = synth.gpt2_state_dict(**dims, seed=seed)
         cfg = types.SimpleNamespace(vocab_size=dims["vocab"], n_embd=dims["d_model"], layer_norm_epsilon=1e-5, n_head=dims["n_head"],
                                     n_layer=dims["n_layer"], n_positions=dims["n_positions"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
-    else:
+    elif kind == "chatglm2":
         from poptransformer.models.chatglm2.model import ChatGLM2DecModel as Base
         sd = synth.chatglm2_state_dict(**dims, seed=seed)
         cfg = types.SimpleNamespace(padded_vocab_size=dims["vocab"], hidden_size=dims["d_model"], layernorm_epsilon=1e-5,
                                     multi_query_group_num=dims["n_group"], num_attention_heads=dims["n_head"], ffn_hidden_size=dims["ffn"],
                                     num_layers=dims["n_layer"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
+    else:
+        from poptransformer.models.rwkv.model import RWKVDecodeModel as Base
+        sd = synth.rwkv_state_dict(**dims, seed=seed)
+        cfg = types.SimpleNamespace(vocab_size=dims["vocab"], hidden_size=dims["d_model"], intermediate_size=dims["ffn"],
+                                    attention_hidden_size=dims["d_model"], layer_norm_epsilon=1e-5, num_hidden_layers=dims["n_layer"],
+                                    rescale_every=dims["rescale_every"], pad_token_id=pad_id, eos_token_id=pad_id - 1)
 
     class GoldenGPT2(Base):
         def prepare_state_dict(self):
@@ -380,5 +385,5 @@ if __name__ == "__main__":
         (run_tp_strategies if sys.argv[2] == "tp_strategies" else run_checkpoint_preprocess if sys.argv[2] == "checkpoint_preprocess"
          else run_case if sys.argv[2] in CASES else run_other)(sys.argv[2])
     else:
-        for case in list(CASES) + list(OTHER) + ["tp_strategies", "checkpoint_preprocess", "llama_tiny_int4:graph", "llama_tiny_fp16:graph", "gpt2_tiny_fp16:graph", "chatglm2_tiny_fp16:graph"]:
+        for case in list(CASES) + list(OTHER) + ["tp_strategies", "checkpoint_preprocess", "llama_tiny_int4:graph", "llama_tiny_fp16:graph", "gpt2_tiny_fp16:graph", "chatglm2_tiny_fp16:graph", "rwkv_tiny_fp16:graph"]:
             subprocess.run([sys.executable, os.path.abspath(__file__), REF, case], check=True)
