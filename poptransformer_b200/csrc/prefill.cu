@@ -5,17 +5,18 @@
 //
 //   prefill_rope_kv_kernel : RoPE (llama2/attention.py:28-56, same fp16 roundings as the decode kernels) on q and k of every
 //                            prompt token; k and v go to their slots of the paged cache, q is rotated in place.
-//   prefill_attn_kernel    : one block per (sequence, head, 16 query tokens); keys come page by page (64 tokens, contiguous
-//                            16 KB for K and for V) from the paged cache, which now also holds the prompt's own keys; scores
-//                            are rounded like the reference's fp16 matmul output and scaled in fp16, softmax statistics are
-//                            fp32 and online (running max / sum per query), P.V accumulates in fp32.
-// Compute-bound on the CUDA cores (2 x 128 FMA per (query, key)); the linears around it run on the tcgen05 GEMM.
+//   prefill_attn_kernel    : one block per (sequence, head, 64 query tokens), 16 queries per warp; keys come page by page (64
+//                            tokens, contiguous 16 KB for K and for V) from the paged cache, which now also holds the prompt's
+//                            own keys; Q K^T and P V run on the tensor cores (mma.sync m16n8k16, fp32 accumulation); scores are
+//                            rounded like the reference's fp16 matmul output and scaled in fp16, softmax statistics are fp32
+//                            and online (running max / sum per query), probabilities are fp16 like the reference's.
+// The linears around it run on the tcgen05 GEMM.
 #include "tile_math.cuh"
 
 namespace pt {
 namespace pf {
 
-constexpr int H = 128, PAGE = 64, QT = 16, THREADS = 128, KPAD = 136;   // key rows padded to 136 halfs: 8 lanes read 8 different rows
+constexpr int H = 128, PAGE = 64, BQ = 64, THREADS = 128, KPAD = 136;   // K / V rows padded to 136 halfs: fragment loads hit 32 different banks
 
 struct Params {
   int B, P, start, n_head, max_pages;
@@ -56,29 +57,51 @@ __global__ void __launch_bounds__(64) prefill_rope_kv_kernel(const Params p) {
   gV[i + 64] = v[i + 64];
 }
 
+// ldmatrix of four 8x8 b16 matrices, transposed on the way: from a row-major [key][channel] tile this yields the B fragments
+// (k = key, n = channel) of two adjacent channel tiles for one 16-key step.
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// One block per (sequence, head, 64 query tokens): warp w owns queries 16 w .. 16 w + 15 of the tile, their q fragments stay in
+// registers.  Per page of 64 keys: S = Q K^T as 8 x 8 m16n8k16 tensor-core steps per warp (fp32 sums of exact fp16 products,
+// rounded to fp16 and scaled in fp16 like the reference's matmul output times its fp16 constant), causal mask, online softmax
+// (running max / sum per query, fp32), the probabilities rounded to fp16 (the reference's softmax output is fp16) and used as
+// the A operand of O += P V (4 x 16 steps), fp32 accumulators.
 __global__ void __launch_bounds__(THREADS) prefill_attn_kernel(const Params p) {
-  __shared__ __align__(16) __half Qs[QT][H];
   __shared__ __align__(16) __half Ks[PAGE][KPAD];
-  __shared__ __align__(16) __half Vs[PAGE][H];
-  __shared__ float Ps[QT][PAGE + 1];
-  const int tid = threadIdx.x, qi = tid >> 3, l8 = tid & 7;           // 16 queries x 8 lanes
-  const int t0 = blockIdx.x * QT, head = blockIdx.y, b = blockIdx.z;
+  __shared__ __align__(16) __half Vs[PAGE][KPAD];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+  const int t0 = blockIdx.x * BQ, head = blockIdx.y, b = blockIdx.z;
   const int dq = p.n_head * H;
-  const int qt = t0 + qi;                                            // this thread's query token (may be beyond the prompt)
-  const bool q_ok = qt < p.P;
-  const int qpos = p.start + qt;
-  for (int e = tid; e < QT * (H / 8); e += THREADS) {                // Q tile (already rotated)
-    const int r = e / (H / 8), c8 = e - r * (H / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t0 + r < p.P) v = *reinterpret_cast<const uint4 *>(p.qkv + (size_t)(b * p.P + t0 + r) * 3 * dq + (size_t)head * H + c8 * 8);
-    *reinterpret_cast<uint4 *>(&Qs[r][c8 * 8]) = v;
-  }
-  float m_run = -INFINITY, l_run = 0.f, acc[16];
+  const int q0 = t0 + warp * 16 + g, q1 = q0 + 8;                     // this lane's two query tokens (rows g and g + 8 of the warp's tile)
+  const bool ok0 = q0 < p.P, ok1 = q1 < p.P;
+  const int pos0 = p.start + q0, pos1 = p.start + q1;
+  // Q fragments (already rotated by prefill_rope_kv_kernel): a0 / a2 = row g, a1 / a3 = row g + 8, channels 16 kk + 2 tig (+8)
+  uint32_t qa[H / 16][4];
+  {
+    const __half *r0 = p.qkv + (size_t)(b * p.P + (ok0 ? q0 : 0)) * 3 * dq + (size_t)head * H + 2 * tig;
+    const __half *r1 = p.qkv + (size_t)(b * p.P + (ok1 ? q1 : 0)) * 3 * dq + (size_t)head * H + 2 * tig;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-  const int last_pos = p.start + min(p.P, t0 + QT) - 1;               // newest key any query of the tile may see
+    for (int kk = 0; kk < H / 16; ++kk) {
+      qa[kk][0] = ok0 ? *reinterpret_cast<const uint32_t *>(r0 + kk * 16) : 0u;
+      qa[kk][1] = ok1 ? *reinterpret_cast<const uint32_t *>(r1 + kk * 16) : 0u;
+      qa[kk][2] = ok0 ? *reinterpret_cast<const uint32_t *>(r0 + kk * 16 + 8) : 0u;
+      qa[kk][3] = ok1 ? *reinterpret_cast<const uint32_t *>(r1 + kk * 16 + 8) : 0u;
+    }
+  }
+  float o[H / 8][4];
+#pragma unroll
+  for (int j = 0; j < H / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int last_pos = p.start + min(p.P, t0 + BQ) - 1;               // newest key any query of the tile may see
+  const int warp_last = p.start + min(p.P, t0 + warp * 16 + 16) - 1;  // ... and any query of this warp
   for (int pg = 0; pg * PAGE <= last_pos; ++pg) {
-    __syncthreads();                                                 // previous tile consumed (and Q staged)
+    __syncthreads();                                                 // previous tiles consumed
     const int phys = p.page_table[(size_t)b * p.max_pages + pg];
     const __half *gK = p.pool + (((size_t)phys * 2 + 0) * p.n_head + head) * PAGE * H;
     const __half *gV = p.pool + (((size_t)phys * 2 + 1) * p.n_head + head) * PAGE * H;
@@ -88,71 +111,81 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_kernel(const Params p) {
       *reinterpret_cast<uint4 *>(&Vs[r][c8 * 8]) = *reinterpret_cast<const uint4 *>(gV + (size_t)r * H + c8 * 8);
     }
     __syncthreads();
-    // scores of this thread's query against keys l8, l8 + 8, ...: fp32 dot, rounded to fp16, scaled in fp16 (the reference's fp16
-    // matmul output times its fp16 constant), causal mask
-    float s[8], m_tile = -INFINITY;
+    if (pg * PAGE > warp_last) continue;                             // nothing of this page is visible to this warp's queries (uniform per warp)
+    // ---- scores of the warp's 16 queries against the page's 64 keys
+    float sc[PAGE / 8][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int kr = l8 + 8 * j, kpos = pg * PAGE + kr;
-      float d = 0.f;
-#pragma unroll 4
-      for (int c8 = 0; c8 < H / 8; ++c8) {
-        const uint4 kq = *reinterpret_cast<const uint4 *>(&Ks[kr][c8 * 8]);
-        const uint4 qq = *reinterpret_cast<const uint4 *>(&Qs[qi][c8 * 8]);
-        const __half2 *kh = reinterpret_cast<const __half2 *>(&kq), *qh = reinterpret_cast<const __half2 *>(&qq);
+    for (int j = 0; j < PAGE / 8; ++j) {
+      sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+      const __half *kr = &Ks[j * 8 + g][2 * tig];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float2 a = __half22float2(kh[u]), q2 = __half22float2(qh[u]);
-          d = fmaf(a.x, q2.x, d);
-          d = fmaf(a.y, q2.y, d);
-        }
+      for (int kk = 0; kk < H / 16; ++kk)
+        mma16816(sc[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], *reinterpret_cast<const uint32_t *>(kr + kk * 16),
+                 *reinterpret_cast<const uint32_t *>(kr + kk * 16 + 8));
+    }
+    float m_tile[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < PAGE / 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kpos = pg * PAGE + j * 8 + 2 * tig + (e & 1);
+        const bool vis = (e < 2) ? (ok0 && kpos <= pos0) : (ok1 && kpos <= pos1);
+        const float v = vis ? __half2float(h_mul(__float2half_rn(sc[j][e]), p.scale_h)) : -INFINITY;
+        sc[j][e] = v;
+        m_tile[e >> 1] = fmaxf(m_tile[e >> 1], v);
       }
-      s[j] = (q_ok && kpos <= qpos) ? __half2float(h_mul(__float2half_rn(d), p.scale_h)) : -INFINITY;
-      m_tile = fmaxf(m_tile, s[j]);
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      m_tile[r] = fmaxf(m_tile[r], __shfl_xor_sync(0xffffffffu, m_tile[r], 1));
+      m_tile[r] = fmaxf(m_tile[r], __shfl_xor_sync(0xffffffffu, m_tile[r], 2));
+      const float m_new = fmaxf(m_run[r], m_tile[r]);
+      corr[r] = (m_new == -INFINITY) ? 1.f : expf(m_run[r] - m_new);    // exp(-inf) = 0 the first time
+      m_run[r] = m_new;
     }
-    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
-    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
-    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 4));
-    const float m_new = fmaxf(m_run, m_tile);
-    const float corr = (m_new == -INFINITY) ? 1.f : expf(m_run - m_new);   // exp(-inf) = 0 the first time
-    float l_tile = 0.f;
+    float l_tile[2] = {0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float e = (s[j] == -INFINITY) ? 0.f : expf(s[j] - m_new);
-      Ps[qi][l8 + 8 * j] = e;
-      l_tile += e;
+    for (int j = 0; j < PAGE / 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        // the probability as the reference holds it: fp16; the row sum adds the rounded values, like the division would see them
+        const float pe = (sc[j][e] == -INFINITY) ? 0.f : __half2float(__float2half_rn(expf(sc[j][e] - m_run[e >> 1])));
+        sc[j][e] = pe;
+        l_tile[e >> 1] += pe;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_tile[r] += __shfl_xor_sync(0xffffffffu, l_tile[r], 1);
+      l_tile[r] += __shfl_xor_sync(0xffffffffu, l_tile[r], 2);
+      l_run[r] = l_run[r] * corr[r] + l_tile[r];
     }
-    l_tile += __shfl_xor_sync(0xffffffffu, l_tile, 1);
-    l_tile += __shfl_xor_sync(0xffffffffu, l_tile, 2);
-    l_tile += __shfl_xor_sync(0xffffffffu, l_tile, 4);
-    l_run = l_run * corr + l_tile;
-    m_run = m_new;
-    __syncwarp();                                                    // the 8 lanes of a query sit in one warp: Ps[qi] is complete
-    // P.V: this thread owns channels [16 l8, 16 l8 + 16) of its query
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] *= corr;
-    for (int kr = 0; kr < PAGE; ++kr) {
-      const float e = Ps[qi][kr];
-      const uint4 v0 = *reinterpret_cast<const uint4 *>(&Vs[kr][l8 * 16]), v1 = *reinterpret_cast<const uint4 *>(&Vs[kr][l8 * 16 + 8]);
-      const __half2 *h0 = reinterpret_cast<const __half2 *>(&v0), *h1 = reinterpret_cast<const __half2 *>(&v1);
+    for (int j = 0; j < H / 8; ++j) {
+      o[j][0] *= corr[0]; o[j][1] *= corr[0];
+      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+    }
+    // ---- O += P V: the score accumulators of two adjacent key tiles are the A fragment of one 16-key step
+    const uint32_t v_lane = smem_addr(&Vs[lane & 15][(lane >> 4) * 8]);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float2 a = __half22float2(h0[u]), c2 = __half22float2(h1[u]);
-        acc[2 * u] = fmaf(e, a.x, acc[2 * u]);
-        acc[2 * u + 1] = fmaf(e, a.y, acc[2 * u + 1]);
-        acc[8 + 2 * u] = fmaf(e, c2.x, acc[8 + 2 * u]);
-        acc[8 + 2 * u + 1] = fmaf(e, c2.y, acc[8 + 2 * u + 1]);
+    for (int k2 = 0; k2 < PAGE / 16; ++k2) {
+      const uint32_t a0 = pack_h2(sc[2 * k2][0], sc[2 * k2][1]), a1 = pack_h2(sc[2 * k2][2], sc[2 * k2][3]);
+      const uint32_t a2 = pack_h2(sc[2 * k2 + 1][0], sc[2 * k2 + 1][1]), a3 = pack_h2(sc[2 * k2 + 1][2], sc[2 * k2 + 1][3]);
+#pragma unroll
+      for (int jn = 0; jn < H / 8; jn += 2) {
+        uint32_t b0, b1, b2, b3;   // keys 16 k2 .. +15: channels 8 jn .. +7 (b0, b1) and 8 jn + 8 .. +15 (b2, b3)
+        ldmatrix_x4_trans(v_lane + (uint32_t)(k2 * 16 * KPAD + jn * 8) * 2u, b0, b1, b2, b3);
+        mma16816(o[jn], a0, a1, a2, a3, b0, b1);
+        mma16816(o[jn + 1], a0, a1, a2, a3, b2, b3);
       }
     }
   }
-  if (q_ok) {
-    const float inv = 1.0f / l_run;
-    __half o[16];
+  const float inv0 = ok0 ? 1.0f / l_run[0] : 0.f, inv1 = ok1 ? 1.0f / l_run[1] : 0.f;
+  __half *d0 = p.out + (size_t)(b * p.P + (ok0 ? q0 : 0)) * dq + (size_t)head * H + 2 * tig;
+  __half *d1 = p.out + (size_t)(b * p.P + (ok1 ? q1 : 0)) * dq + (size_t)head * H + 2 * tig;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) o[j] = __float2half_rn(acc[j] * inv);
-    __half *dst = p.out + (size_t)(b * p.P + qt) * dq + (size_t)head * H + l8 * 16;
-    *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(&o[0]);
-    *reinterpret_cast<uint4 *>(dst + 8) = *reinterpret_cast<const uint4 *>(&o[8]);
+  for (int j = 0; j < H / 8; ++j) {
+    if (ok0) *reinterpret_cast<uint32_t *>(d0 + j * 8) = pack_h2(o[j][0] * inv0, o[j][1] * inv0);
+    if (ok1) *reinterpret_cast<uint32_t *>(d1 + j * 8) = pack_h2(o[j][2] * inv1, o[j][3] * inv1);
   }
 }
 
@@ -188,7 +221,7 @@ extern "C" int pt_prefill_attn(const pt_prefill_attn_args *a, void *stream) {
   p.scale_h = __float2half_rn(a->score_scale);
   pf::prefill_rope_kv_kernel<<<dim3(a->batch * a->n_tokens, a->n_head), 64, 0, as_stream(stream)>>>(p);
   PT_LAUNCH_CHECK("pt_prefill_attn");
-  pf::prefill_attn_kernel<<<dim3(ceil_div(a->n_tokens, pf::QT), a->n_head, a->batch), pf::THREADS, 0, as_stream(stream)>>>(p);
+  pf::prefill_attn_kernel<<<dim3(ceil_div(a->n_tokens, pf::BQ), a->n_head, a->batch), pf::THREADS, 0, as_stream(stream)>>>(p);
   PT_LAUNCH_CHECK("pt_prefill_attn");
   return PT_OK;
 }
