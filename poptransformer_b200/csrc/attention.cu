@@ -1,13 +1,10 @@
 // Paged KV cache: append of the new token fused with split flash-decode attention.
 //
-// One block handles one page (page_size cached tokens) of one (sequence, kv-head): its K and V tiles are
-// contiguous in the pool, so each is fetched with a single 1-D bulk async copy (TMA engine,
-// cp.async.bulk + mbarrier) while the threads apply RoPE to q (and to the new k).  The block that owns the
-// page holding position `step` writes the new k/v into the pool and into its shared-memory tile, so the
-// append costs no extra pass over the cache.  Scores use 8 lanes per cached token with warp-shuffle
-// reductions, the softmax statistics are warp-shuffle reductions, and P.V is one thread per output
-// channel.  Every block leaves (max, sum, partial output) in the workspace; the last block to arrive for
-// a (sequence, kv-head) combines the pages in a fixed order, which keeps the result deterministic.
+// One block handles one page (page_size cached tokens) of one (sequence, kv-head): its K and V tiles are contiguous in the
+// pool.  The block that owns the page holding position `step` writes the new k/v into the pool and takes them from shared
+// memory itself, so the append costs no extra pass over the cache.  Scores and P.V run on the tensor cores (see the kernel),
+// the softmax statistics are warp-shuffle reductions.  Every block leaves (max, sum, partial output) in the workspace; the
+// last block to arrive for a (sequence, kv-head) combines the pages in a fixed order, which keeps the result deterministic.
 //
 // HBM-bound: algorithmic bytes = 2 * (step + 1) * head_dim * 2 per (sequence, kv-head), read once.
 #include "common.cuh"
@@ -85,24 +82,49 @@ __device__ __forceinline__ void rope_pair(const AttnParams &p, const __half *x, 
 }
 
 constexpr int kAttnThreads = 128;
+constexpr int NQ_MAX = 8;   // q heads of one kv head per block: the n side of an m16n8 tensor-core tile (larger groups take several blocks)
 
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f2h2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// One block = one page of one (sequence, kv head, part of the group's q heads).  Both products run on the tensor cores
+// (mma.sync m16n8k16, fp32 accumulation of exact fp16 products):
+//   scores^T [keys x heads] = K [keys x H] . q^T: warp w takes keys 16 w .. 16 w + 15 of each 64-key pass.  Its K rows go from
+//     global memory STRAIGHT into the A fragments: a lane loads 16 bytes = channels 32 pp + 8 tig .. + 7 of its two key rows,
+//     which serve two k-steps whose k order is a permutation of the channels (a dot product does not care, and q, the B operand,
+//     is read from shared memory with the same permutation: the same 16 bytes of the head's row).  No shared-memory tile, no
+//     bank conflicts, no barrier wait for K.
+//   out [heads x H] += P [heads x keys] . V [keys x H]: P comes from the softmax weights in shared memory (rows = heads, padded
+//     to 16 with zeros), V is staged in shared memory with padded rows and read through ldmatrix.trans; warp w owns H / 4 channels.
+// The new token's key / value are staged in shared memory by the block that owns the last page and appended to the pool by one
+// block per kv head.
 template <int H>
-__global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads, 5) kv_append_attn_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  const int PAGE = p.page;
-  __half *Ks = reinterpret_cast<__half *>(smem);
-  __half *Vs = Ks + (size_t)PAGE * H;
-  const int nq_s = p.qpk / p.qsplit;                       // q heads handled by this block
-  __half *qs = Vs + (size_t)PAGE * H;                      // [nq][H]
-  float *ps = reinterpret_cast<float *>(qs + (size_t)nq_s * H);  // [nq][PAGE]
-  float *ml = ps + (size_t)nq_s * PAGE;                    // [nq][2]
-  __shared__ __align__(8) uint64_t bar;
+  constexpr int VLD = H + 8;                               // V rows padded: ldmatrix reads 8 rows in 8 different bank groups
+  constexpr int QLD = H + 32;                              // q rows: two heads read in one shared-memory phase sit 16 banks apart
+  const int PAGE = p.page, KP = (PAGE + 15) & ~15;         // keys padded to whole 16-key steps
+  const int PSLD = KP + 8;                                 // row stride of the score / weight rows
+  __half *Vs = reinterpret_cast<__half *>(smem);           // [KP][VLD]
+  __half *qs = Vs + (size_t)KP * VLD;                      // [NQ_MAX][QLD], rows >= nq are zero
+  __half *newk = qs + (size_t)NQ_MAX * QLD;                // [H]: the new token's rotated key (owner block)
+  float *ps = reinterpret_cast<float *>(newk + H);         // [NQ_MAX][PSLD]
+  float *ml = ps + (size_t)NQ_MAX * PSLD;                  // [NQ_MAX][2]
   __shared__ int s_last;
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   // With many q heads per kv head (multi-query attention) the heads of a group are shared out over `qsplit` blocks: each
-  // re-reads the group's K/V page (through L2) and handles nq of the group's heads, which shortens both the per-page work
-  // and the serial combine of the last block.
+  // re-reads the group's K/V page (through L2) and handles nq of the group's heads.
   const int pg = blockIdx.x, kvh = blockIdx.y / p.qsplit, qpart = blockIdx.y - kvh * p.qsplit, b = blockIdx.z;
   const int nq = p.qpk / p.qsplit, q_lo = qpart * nq;   // this block's heads of the group: q_lo .. q_lo + nq - 1
   if (p.pdl) {
@@ -120,95 +142,92 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
   const int n_valid = min(PAGE, step + 1 - pg * PAGE);
   const bool owner = (pg == n_active - 1);
   const int n_load = owner ? n_valid - 1 : n_valid;  // the newest token is not in the pool yet
+  const int slot = n_valid - 1;                      // owner: where the new token goes
 
   const int phys = p.page_table[(size_t)b * p.max_pages + pg];
   __half *gK = p.pool + (((size_t)phys * 2 + 0) * p.n_kv + kvh) * PAGE * H;
   __half *gV = p.pool + (((size_t)phys * 2 + 1) * p.n_kv + kvh) * PAGE * H;
 
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    if (n_load > 0) {
-      const uint32_t bytes = (uint32_t)n_load * H * sizeof(__half);
-      mbar_expect_tx(&bar, 2 * bytes);
-      bulk_g2s(Ks, gK, bytes, &bar);
-      bulk_g2s(Vs, gV, bytes, &bar);
+  // ---- this warp's K rows of the first 64-key pass, requested before anything else (keys 16 warp + g and + 8)
+  uint4 kf[2][H / 32];
+  auto load_k = [&](int kbase) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int key = kbase + g + 8 * r;
+#pragma unroll
+      for (int pp = 0; pp < H / 32; ++pp)
+        kf[r][pp] = key < n_load ? __ldcg(reinterpret_cast<const uint4 *>(gK + (size_t)key * H + pp * 32 + tig * 8)) : make_uint4(0, 0, 0, 0);
     }
-  }
-
-  // ---- RoPE on the group's q heads (and on the new k) while the tiles are in flight
+  };
+  load_k(warp * 16);
   const int row_elems = (p.n_head + 2 * p.n_kv) * H;
   const __half *qrow = p.qkv + (size_t)b * row_elems;
-  const __half *sin_r = p.sin_t + (size_t)step * p.rot_half;
-  const __half *cos_r = p.cos_t + (size_t)step * p.rot_half;
-  for (int i = tid; i < nq * (H / 2); i += kAttnThreads) {
-    const int qh = i / (H / 2), j = i - qh * (H / 2);
-    rope_pair(p, qrow + (size_t)(kvh * p.qpk + q_lo + qh) * H, sin_r, cos_r, j, qs + (size_t)qh * H);
-  }
-  if (owner) {
-    const int slot = n_valid - 1;
-    const __half *knew = qrow + (size_t)(p.n_head + kvh) * H;
-    const __half *vnew = qrow + (size_t)(p.n_head + p.n_kv + kvh) * H;
-    for (int j = tid; j < H / 2; j += kAttnThreads) rope_pair(p, knew, sin_r, cos_r, j, Ks + (size_t)slot * H);
-    for (int j = tid; j < H; j += kAttnThreads) Vs[(size_t)slot * H + j] = vnew[j];
-    __syncthreads();
-    if (qpart == 0) {   // one block of the group appends to the pool; the others only need the new token in their tile
-      for (int j = tid; j < H; j += kAttnThreads) {
-        gK[(size_t)slot * H + j] = Ks[(size_t)slot * H + j];
-        gV[(size_t)slot * H + j] = Vs[(size_t)slot * H + j];
-      }
+  // ---- V page -> shared memory as asynchronous 16-byte copies (no registers, in flight together with the K loads above)
+  const __half *vnew = qrow + (size_t)(p.n_head + p.n_kv + kvh) * H;
+  for (int e = tid; e < KP * (H / 8); e += kAttnThreads) {
+    const int r = e / (H / 8), c8 = e - r * (H / 8);
+    __half *dst = Vs + (size_t)r * VLD + c8 * 8;
+    if (r < n_load) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(gV + (size_t)r * H + c8 * 8) : "memory");
+    } else {   // rows beyond the valid tokens multiply weights of zero: keep them finite; the new token's row comes from qkv
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (owner && r == slot) v = *reinterpret_cast<const uint4 *>(vnew + c8 * 8);
+      *reinterpret_cast<uint4 *>(dst) = v;
     }
   }
-  __syncthreads();  // barrier initialised, q staged
-  if (n_load > 0 && !mbar_wait(&bar, 0)) {
-    if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
-    return;  // bounded wait gave up: report, do not hang
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  // ---- RoPE on the block's q heads (and on the new k)
+  const __half *sin_r = p.sin_t + (size_t)step * p.rot_half;
+  const __half *cos_r = p.cos_t + (size_t)step * p.rot_half;
+  for (int i = tid; i < (NQ_MAX - nq) * (H / 2); i += kAttnThreads) {   // unused head rows of the B operand: zeros
+    const int qh = nq + i / (H / 2), j = i - (qh - nq) * (H / 2);
+    reinterpret_cast<uint32_t *>(qs + (size_t)qh * QLD)[j] = 0u;
+  }
+  for (int i = tid; i < nq * (H / 2); i += kAttnThreads) {
+    const int qh = i / (H / 2), j = i - qh * (H / 2);
+    rope_pair(p, qrow + (size_t)(kvh * p.qpk + q_lo + qh) * H, sin_r, cos_r, j, qs + (size_t)qh * QLD);
+  }
+  if (owner) {
+    const __half *knew = qrow + (size_t)(p.n_head + kvh) * H;
+    for (int j = tid; j < H / 2; j += kAttnThreads) rope_pair(p, knew, sin_r, cos_r, j, newk);
+  }
+  for (int i = tid; i < NQ_MAX * PSLD; i += kAttnThreads) ps[i] = 0.f;   // weights of padded keys and unused heads
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncthreads();
+  if (owner && qpart == 0) {   // one block of the group appends to the pool
+    for (int j = tid; j < H; j += kAttnThreads) {
+      gK[(size_t)slot * H + j] = newk[j];
+      gV[(size_t)slot * H + j] = Vs[(size_t)slot * VLD + j];
+    }
   }
 
-  // ---- scores: 8 lanes per cached token
-  {
-    constexpr int EPL = H / 8;  // elements per lane: vector v of a lane covers channels v*64 + sub*8 .. +8,
-                                // so the 8 lanes of a token read 128 contiguous bytes (no bank conflicts)
-    const int sub = lane & 7, tgrp = tid >> 3;  // 16 token groups per pass
-    for (int t0 = 0; t0 < n_valid; t0 += kAttnThreads / 8) {
-      const int t = t0 + tgrp;
-      float kf[EPL];
-      if (t < n_valid) {
+  // ---- scores: keys 16 warp .. + 15 of every 64-key pass against the block's heads
+  for (int kbase = warp * 16; kbase < n_valid; kbase += 64) {
+    if (kbase != warp * 16) load_k(kbase);
+    if (owner) {   // the new token's key row comes from shared memory
 #pragma unroll
-        for (int v = 0; v < EPL / 8; ++v) {
-          uint4 raw = *reinterpret_cast<const uint4 *>(Ks + (size_t)t * H + v * 64 + sub * 8);
-          const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+      for (int r = 0; r < 2; ++r)
+        if (kbase + g + 8 * r == slot) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 f = __half22float2(h[j]);
-            kf[v * 8 + 2 * j] = f.x;
-            kf[v * 8 + 2 * j + 1] = f.y;
-          }
+          for (int pp = 0; pp < H / 32; ++pp) kf[r][pp] = *reinterpret_cast<const uint4 *>(newk + pp * 32 + tig * 8);
         }
-      } else {
+    }
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) kf[j] = 0.f;
-      }
-      for (int qh = 0; qh < nq; ++qh) {
-        float s = 0.f;
+    for (int pp = 0; pp < H / 32; ++pp) {
+      const uint4 qv = *reinterpret_cast<const uint4 *>(qs + (size_t)g * QLD + pp * 32 + tig * 8);
+      mma_f16(sc, kf[0][pp].x, kf[1][pp].x, kf[0][pp].y, kf[1][pp].y, qv.x, qv.y);
+      mma_f16(sc, kf[0][pp].z, kf[1][pp].z, kf[0][pp].w, kf[1][pp].w, qv.z, qv.w);
+    }
+    // lane (g, tig): keys kbase + g (sc[0], sc[1]) and kbase + g + 8 (sc[2], sc[3]) against heads 2 tig and 2 tig + 1
 #pragma unroll
-        for (int v = 0; v < EPL / 8; ++v) {
-          uint4 raw = *reinterpret_cast<const uint4 *>(qs + (size_t)qh * H + v * 64 + sub * 8);
-          const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 f = __half22float2(h[j]);
-            s += kf[v * 8 + 2 * j] * f.x;
-            s += kf[v * 8 + 2 * j + 1] * f.y;
-          }
-        }
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (sub == 0 && t < n_valid) {
-          __half s16 = __float2half_rn(s);               // fp16 matmul output
-          if (p.use_scale) s16 = h_mul(s16, p.scale_h);  // ops.mul by fp16(1/sqrt(H))
-          ps[(size_t)qh * PAGE + t] = __half2float(s16);
-        }
+    for (int e = 0; e < 4; ++e) {
+      const int key = kbase + g + 8 * (e >> 1), qh = 2 * tig + (e & 1);
+      if (key < n_valid && qh < nq) {
+        __half s16 = __float2half_rn(sc[e]);           // fp16 matmul output
+        if (p.use_scale) s16 = h_mul(s16, p.scale_h);  // ops.mul by fp16(1/sqrt(H))
+        ps[(size_t)qh * PSLD + key] = __half2float(s16);
       }
     }
   }
@@ -216,7 +235,7 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
 
   // ---- per-head softmax statistics (one warp per q head, warp-shuffle reductions)
   for (int qh = warp; qh < nq; qh += kAttnThreads / 32) {
-    float *pr = ps + (size_t)qh * PAGE;
+    float *pr = ps + (size_t)qh * PSLD;
     float m = -INFINITY;
     if (p.softmax_mode == PT_SOFTMAX_F32) {
       for (int t = lane; t < n_valid; t += 32) m = fmaxf(m, pr[t]);
@@ -236,24 +255,35 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
   }
   __syncthreads();
 
-  // ---- P.V: one thread per output channel, V element reused across the group's q heads
+  // ---- P.V: warp w owns channels [w H/4, (w + 1) H/4); rows of the A operand = heads (8 .. 15 are zero)
   const size_t head0 = (size_t)b * p.n_head + (size_t)kvh * p.qpk + q_lo;
-  if (tid < H) {
-    for (int q0 = 0; q0 < nq; q0 += 4) {
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
-      const int n4 = min(4, nq - q0);
-      for (int t = 0; t < n_valid; ++t) {
-        const float v = __half2float(Vs[(size_t)t * H + tid]);
+  {
+    constexpr int NT = H / 32;                 // 8-channel tiles per warp
+    float o[NT][4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (k < n4) o[k] += ps[(size_t)(q0 + k) * PAGE + t] * v;
+    for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const float *pr = ps + (size_t)g * PSLD + 2 * tig;      // g < NQ_MAX: rows of unused heads are zero
+    const uint32_t v_lane = smem_u32(Vs + (size_t)(lane & 15) * VLD + warp * (H / 4) + (lane >> 4) * 8);
+    for (int k2 = 0; k2 * 16 < n_valid; ++k2) {
+      // The weights are rounded to fp16 for the tensor core; they are at most 1 (max-subtracted mode) or fp16 values already
+      // (the reference's fp16 softmax mode), so this costs at most 2^-11 relative per weight.
+      const float2 p0 = *reinterpret_cast<const float2 *>(pr + k2 * 16), p1 = *reinterpret_cast<const float2 *>(pr + k2 * 16 + 8);
+      const uint32_t a0 = pack_f2h2(p0.x, p0.y), a2 = pack_f2h2(p1.x, p1.y);
+#pragma unroll
+      for (int j = 0; j < NT; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(v_lane + (uint32_t)(k2 * 16 * VLD + j * 8) * 2u, b0, b1, b2, b3);
+        mma_f16(o[j], a0, 0u, a2, 0u, b0, b1);
+        if (j + 1 < NT) mma_f16(o[j + 1], a0, 0u, a2, 0u, b2, b3);
       }
-      for (int k = 0; k < n4; ++k) p.ws_o[((head0 + q0 + k) * p.max_pages + pg) * H + tid] = o[k];
+    }
+    if (g < nq) {
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+        *reinterpret_cast<float2 *>(&p.ws_o[((head0 + g) * p.max_pages + pg) * H + warp * (H / 4) + j * 8 + 2 * tig]) = make_float2(o[j][0], o[j][1]);
     }
   }
   if (tid < nq) p.ws_ml[(head0 + tid) * p.max_pages + pg] = make_float2(ml[2 * tid], ml[2 * tid + 1]);
-  for (int qh = tid + kAttnThreads; qh < nq; qh += kAttnThreads)
-    p.ws_ml[(head0 + qh) * p.max_pages + pg] = make_float2(ml[2 * qh], ml[2 * qh + 1]);
 
   // ---- last block to arrive for this (sequence, kv-head) combines the pages in page order
   __threadfence();
@@ -264,13 +294,13 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
   if (!s_last) return;
   __threadfence();
   if (tid == 0) *ctr = 0;
-  // The K tile is no longer needed: its shared memory takes the pages' (max, sum) pairs, then their weights.  All loads of a
+  // The V tile is no longer needed: its shared memory takes the pages' (max, sum) pairs, then their weights.  All loads of a
   // stage are issued before the first is used, so the combine costs a handful of L2 round trips whatever the number of pages
   // and heads (a loop of dependent-looking loads per head and page made it the longest part of the kernel at 17 pages).
-  float *cw = reinterpret_cast<float *>(Ks);           // [nq][n_active] weights exp(m_i - M)
+  float *cw = reinterpret_cast<float *>(Vs);           // [nq][n_active] weights exp(m_i - M)
   float *cl = cw + (size_t)nq * n_active;              // [nq][n_active] page sums, then cl[qh * n_active] = L of the head
   // (worth its two extra barriers from about sixteen (head, page) pairs on: measured 1 % slower than the plain loop at 1 head x 6 pages)
-  const bool staged = nq * n_active >= 16 && (size_t)2 * nq * n_active * sizeof(float) <= (size_t)PAGE * H * sizeof(__half);
+  const bool staged = nq * n_active >= 16 && (size_t)2 * nq * n_active * sizeof(float) <= (size_t)KP * VLD * sizeof(__half);
   if (staged) {
     for (int idx = tid; idx < nq * n_active; idx += kAttnThreads) {
       const int qh = idx / n_active, i = idx - qh * n_active;
@@ -322,7 +352,7 @@ __global__ void __launch_bounds__(kAttnThreads) kv_append_attn_kernel(const Attn
     }
     return;
   }
-  if (tid < H) {   // more pages than the tile holds statistics for: the plain loop
+  if (tid < H) {   // few pages and heads: the plain loop
     for (int qh = 0; qh < nq; ++qh) {
       const size_t hd = head0 + qh;
       float M = -INFINITY;
@@ -420,7 +450,12 @@ extern "C" int pt_kv_append_attn(const pt_attn_args *a, void *stream) {
 
   AttnParams p{};
   p.B = a->batch; p.n_head = a->n_head; p.n_kv = a->n_kv; p.qpk = a->n_head / a->n_kv; p.H = a->head_dim;
-  p.qsplit = (p.qpk > 4 && p.qpk % 4 == 0) ? p.qpk / 4 : 1;   // four q heads per block for multi-query groups
+  {  // at most NQ_MAX q heads per block (the n side of the tensor-core tile): larger groups are shared out over several blocks
+    int nq_blk = p.qpk;
+    if (p.qpk > NQ_MAX)
+      for (nq_blk = NQ_MAX; p.qpk % nq_blk; --nq_blk) {}
+    p.qsplit = p.qpk / nq_blk;
+  }
   p.page = a->page_size; p.max_pages = a->max_pages; p.rope_mode = a->rope_mode; p.softmax_mode = a->softmax_mode;
   p.rot_half = a->rope_mode == PT_ROPE_CHATGLM2 ? a->head_dim / 4 : a->head_dim / 2;
   p.out_ld = a->out_ld > 0 ? a->out_ld : a->n_head * a->head_dim;
@@ -441,8 +476,10 @@ extern "C" int pt_kv_append_attn(const pt_attn_args *a, void *stream) {
   p.max_len = a->max_len > 0 ? a->max_len : a->page_size * a->max_pages;
 
   const int nq = p.qpk / p.qsplit;
-  const size_t smem = (size_t)2 * p.page * p.H * sizeof(__half) + (size_t)nq * p.H * sizeof(__half) +
-                      (size_t)nq * p.page * sizeof(float) + (size_t)nq * 2 * sizeof(float);
+  (void)nq;
+  const int kp = (p.page + 15) & ~15;
+  const size_t smem = ((size_t)kp * (p.H + 8) + (size_t)NQ_MAX * (p.H + 32) + p.H) * sizeof(__half) +
+                      ((size_t)NQ_MAX * (kp + 8) + (size_t)NQ_MAX * 2) * sizeof(float);
   PT_REQUIRE(smem <= 200 * 1024, "pt_kv_append_attn: tile needs %zu bytes of shared memory", smem);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(a->max_pages, a->n_kv * p.qsplit, a->batch);
