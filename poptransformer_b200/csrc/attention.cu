@@ -132,6 +132,8 @@ __global__ void __launch_bounds__(kAttnThreads, 5) kv_append_attn_kernel(const A
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
+  // the page-table entry does not depend on the step: both loads go out together (one round trip less before the K / V loads)
+  const int phys = p.page_table[(size_t)b * p.max_pages + pg];
   const int step = *p.step;
   if (step < 0 || step >= p.max_len) {  // no page / no RoPE row for this position: report it and leave the counters untouched
     if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 12);
@@ -144,7 +146,6 @@ __global__ void __launch_bounds__(kAttnThreads, 5) kv_append_attn_kernel(const A
   const int n_load = owner ? n_valid - 1 : n_valid;  // the newest token is not in the pool yet
   const int slot = n_valid - 1;                      // owner: where the new token goes
 
-  const int phys = p.page_table[(size_t)b * p.max_pages + pg];
   __half *gK = p.pool + (((size_t)phys * 2 + 0) * p.n_kv + kvh) * PAGE * H;
   __half *gV = p.pool + (((size_t)phys * 2 + 1) * p.n_kv + kvh) * PAGE * H;
 
