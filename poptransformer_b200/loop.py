@@ -98,7 +98,7 @@ class MultiStreamLoop:
 
         def finish(k):
             st = self.streams[k]
-            results[serving[k]] = {"Loop:0": st.ids.cpu().numpy(), "Loop:1": st.step_t.cpu().numpy()}
+            results[serving[k]] = {"Loop:0": st.ids.cpu().numpy().copy(), "Loop:1": st.step_t.cpu().numpy().copy()}   # the stream's buffers are reused
             err = int(st.error_flag.item())
             if err != 0:
                 raise PtError(f"device-side error flag {err} on stream {k}")

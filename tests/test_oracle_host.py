@@ -1,6 +1,7 @@
 """CPU checks: the oracle's known answers read off the reference sources, and the product's host-side
 logic (quantiser, RoPE tables, synthetic checkpoints) against the oracle."""
 import numpy as np
+import pytest
 import torch
 
 from oracle import llama_np
@@ -326,3 +327,52 @@ def test_gpt2_beam_oracle_width_one_is_greedy_and_scores_are_sorted():
     three = gpt2_np.GPT2Oracle(gpt2_np.GPT2Config(**dims, max_len=24), sd, 6)
     hyp, prob = three.generate_beam(prompt, 8, 3)
     assert hyp.shape == (2, 8, 3) and (np.diff(prob.astype(np.float32), axis=1) <= 0).all()
+
+
+def test_multi_stream_loop_serves_streams_in_turn():
+    """MultiStreamLoop on a stand-in decoder (no GPU): global iteration s goes to stream s % max_bps at that stream's own step
+    s // max_bps (GetStepBps, custom_ops/kv_cache_codelet.cpp:18-36), a stream that has finished takes the next waiting request, and
+    every request gets exactly max_loop iterations."""
+    import torch
+    from poptransformer_b200 import loop
+
+    order = []
+
+    class Fake(loop.DecodeLoop):
+        graph = object()                      # "already captured"
+
+        def __init__(self, sid=0, family=None):
+            self.sid, self.family = sid, family if family is not None else [self]
+            self.cfg = type("C", (), {"max_len": 8})()
+            self.ids = torch.zeros((1, 8), dtype=torch.int32)
+            self.step_t = torch.zeros(1, dtype=torch.int32)
+            self.error_flag = torch.zeros(1, dtype=torch.int32)
+            self._init_loop("cpu", False)
+
+        def new_stream(self):
+            s = Fake(len(self.family), self.family)
+            self.family.append(s)
+            return s
+
+        def reset(self, ids):
+            self.ids.copy_(torch.as_tensor(ids, dtype=torch.int32))
+            self.step_t.zero_()
+
+        def step(self):
+            order.append((self.sid, int(self.step_t.item()), int(self.ids[0, 0])))
+            self.ids[0, 1 + int(self.step_t.item())] = 100 * int(self.ids[0, 0]) + int(self.step_t.item())
+            self.step_t += 1
+
+    ms = loop.MultiStreamLoop(Fake(), 2, capture=False)
+    reqs = [np.full((1, 8), 0, np.int32) for _ in range(3)]
+    for i, r in enumerate(reqs):
+        r[0, 0] = i + 1                                     # request tag
+    outs = ms.run(reqs, max_loop=3)
+    # streams alternate; stream 0 finishes request 1 after three turns and picks up request 3 while stream 1 is still on request 2
+    assert order[:6] == [(0, 0, 1), (1, 0, 2), (0, 1, 1), (1, 1, 2), (0, 2, 1), (1, 2, 2)]
+    assert [o for o in order[6:]] == [(0, 0, 3), (0, 1, 3), (0, 2, 3)]
+    for i, o in enumerate(outs):
+        tag = i + 1
+        assert int(o["Loop:1"][0]) == 3 and o["Loop:0"][0, 1:4].tolist() == [100 * tag, 100 * tag + 1, 100 * tag + 2]
+    with pytest.raises(loop.PtError, match="new_stream"):
+        loop.MultiStreamLoop(object(), 2)
