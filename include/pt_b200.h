@@ -218,7 +218,10 @@ int pt_kv_cache_pipeline_fp8(const int32_t *step_dev, const void *kv_new, void *
  * scale/mask -> softmax_ce -> matmul(P,V) -> transpose/reshape
  * (llama2/attention.py:64-114; gpt2/attention.py:37-85; chatglm2/attention.py:166-312).
  * The cache is paged: pool[page][2][n_kv][page_size][head_dim] fp16, page_table[batch][max_pages].
- * Token t of sequence b lives in page page_table[b][t / page_size], slot t % page_size. */
+ * Token t of sequence b lives in page page_table[b][t / page_size], slot t % page_size.
+ * One block per (sequence, kv head, page): scores and P.V on the tensor cores (fp32 sums of exact fp16 products, scores rounded
+ * to fp16 like the reference's matmul output), softmax statistics in fp32 (or the reference's fp16 exp), the pages of a head
+ * combined in page order by the last block to arrive (deterministic). */
 #define PT_ROPE_NONE 0
 #define PT_ROPE_LLAMA 1    /* rotate_half, table [max_len, head_dim/2]  (llama2/attention.py:28-56) */
 #define PT_ROPE_CHATGLM2 2 /* interleaved pairs on the first half of each head (chatglm2/attention.py:110-164) */
@@ -239,7 +242,7 @@ typedef struct pt_attn_args {
   int out_ld;                        /* row stride of `out` in elements; 0 = dense             */
   void *workspace;                   /* pt_attn_workspace_bytes                               */
   size_t workspace_bytes;
-  int32_t *error_flag;               /* device int, set non-zero if a bounded wait gave up     */
+  int32_t *error_flag;               /* device int, set to 12 if *step_dev is out of range (the kernel has no waits) */
   int pdl;                           /* 1: programmatic dependent launch (see pt_linear_args.pdl) */
   int max_len;                       /* positions available: rows of rope_sin / rope_cos and of the id container; 0 = page_size *
                                         max_pages.  A launch that finds *step_dev outside [0, max_len) sets error_flag to 12 and

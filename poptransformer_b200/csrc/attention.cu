@@ -28,32 +28,6 @@ struct AttnParams {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-// Bounded wait: returns false if the phase did not complete within the iteration limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t phase) {
-  for (int it = 0; it < (1 << 22); ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(phase)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-
 // RoPE on one head vector x[H] (global, fp16) -> dst[H] (fp16), with the reference's fp16 roundings.
 // Llama (rotate_half): y_j = fp16(fp16(x_j c_j) + fp16(-x_{j+H/2} s_j)), y_{j+H/2} = fp16(fp16(x_{j+H/2} c_j) + fp16(x_j s_j)).
 // ChatGLM2: only the first H/2 channels rotate, as interleaved pairs (2i, 2i+1) with angle i:
