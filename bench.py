@@ -116,6 +116,19 @@ def cpu_baseline(steps, warmup, sample_layers=2, ctx=PROMPT):
             kc[:, :, :ctx] = (r.standard_normal((1, cfg.n_head, ctx, cfg.head_dim), dtype=np.float32) * 0.5).astype(np.float16)
     L = c_ref.lib()
     import ctypes
+    # All host cores, whatever the launcher exported: torch.distributed.run sets OMP_NUM_THREADS=1 for its workers, which would
+    # time this arm on one core.  OMP_NUM_THREADS set by the USER (PT_CPU_THREADS) is still honoured.
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count()
+    threads = int(os.environ.get("PT_CPU_THREADS", cores))
+    try:
+        omp = ctypes.CDLL("libgomp.so.1")
+        omp.omp_set_num_threads(int(threads))
+        threads = int(omp.omp_get_max_threads())
+    except OSError:
+        threads = int(os.environ.get("OMP_NUM_THREADS", threads))
     x = np.ascontiguousarray(orc.emb[[1]])
     t_layers, t_head = [], []
     for it in range(warmup + steps):
@@ -129,11 +142,7 @@ def cpu_baseline(steps, warmup, sample_layers=2, ctx=PROMPT):
         if it >= warmup:
             t_layers.append(t1 - t0); t_head.append(t2 - t1)
     per_token = np.mean(t_layers) / sample_layers * cfg.n_layer + np.mean(t_head)
-    try:
-        cores = len(os.sched_getaffinity(0))
-    except AttributeError:
-        cores = os.cpu_count()
-    return {"value": 1.0 / per_token, "unit": "tokens/s", "cores": int(os.environ.get("OMP_NUM_THREADS", cores)), "kind": "port",
+    return {"value": 1.0 / per_token, "unit": "tokens/s", "cores": threads, "kind": "port",
             "sample": f"{sample_layers} of 32 transformer blocks + final norm + LM head of the same shapes, {steps} decode steps at "
                       f"context {ctx}, block time scaled x{cfg.n_layer // sample_layers}",
             "ms_per_token": per_token * 1e3}
