@@ -247,6 +247,10 @@ typedef struct pt_attn_args {
   int max_len;                       /* positions available: rows of rope_sin / rope_cos and of the id container; 0 = page_size *
                                         max_pages.  A launch that finds *step_dev outside [0, max_len) sets error_flag to 12 and
                                         does nothing else                                                                  */
+  void *out_fp8;                     /* optional: E4M3 bytes [batch, n_head*head_dim] of out / out_fp8_scale, written beside `out`:
+                                        the cast an FP8 linear applies to its input (precision_strategy.py:62-66) without a launch
+                                        of its own                                                                          */
+  float out_fp8_scale;
 } pt_attn_args;
 
 size_t pt_attn_workspace_bytes(int batch, int n_head, int head_dim, int max_pages);

@@ -35,6 +35,7 @@ class AttnArgs(ctypes.Structure):
         ("step_dev", c_void_p), ("qkv", c_void_p), ("rope_sin", c_void_p), ("rope_cos", c_void_p),
         ("pool", c_void_p), ("page_table", c_void_p), ("out", c_void_p), ("out_ld", c_int),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("error_flag", c_void_p), ("pdl", c_int), ("max_len", c_int),
+        ("out_fp8", c_void_p), ("out_fp8_scale", c_float),
     ]
 
 

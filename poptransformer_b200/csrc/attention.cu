@@ -20,6 +20,8 @@ struct AttnParams {
   __half *pool;
   const int *page_table;
   __half *out;
+  uint8_t *out8;   // optional: the same output cast to E4M3 with inv_out_scale (the input of an FP8 linear), [B, n_head * H]
+  float inv_out_scale;
   float *ws_o;     // [B, n_head, max_pages, H]
   float2 *ws_ml;   // [B, n_head, max_pages]
   int *counters;   // [B, n_kv, qsplit]
@@ -321,8 +323,15 @@ __global__ void __launch_bounds__(kAttnThreads, 5) kv_append_attn_kernel(const A
             }
         }
         __half *dst = p.out + (size_t)b * p.out_ld + ((size_t)kvh * p.qpk + q_lo + q0) * H + tid;
-        dst[0] = __float2half_rn(o0 / cl[(size_t)q0 * n_active]);
-        if (two) dst[H] = __float2half_rn(o1 / cl[(size_t)(q0 + 1) * n_active]);
+        const __half y0 = __float2half_rn(o0 / cl[(size_t)q0 * n_active]);
+        dst[0] = y0;
+        uint8_t *dst8 = p.out8 ? p.out8 + (size_t)b * p.n_head * H + ((size_t)kvh * p.qpk + q_lo + q0) * H + tid : nullptr;
+        if (dst8) dst8[0] = (uint8_t)__nv_cvt_float_to_fp8(__half2float(y0) * p.inv_out_scale, __NV_SATFINITE, __NV_E4M3);
+        if (two) {
+          const __half y1 = __float2half_rn(o1 / cl[(size_t)(q0 + 1) * n_active]);
+          dst[H] = y1;
+          if (dst8) dst8[H] = (uint8_t)__nv_cvt_float_to_fp8(__half2float(y1) * p.inv_out_scale, __NV_SATFINITE, __NV_E4M3);
+        }
       }
     }
     return;
@@ -339,7 +348,11 @@ __global__ void __launch_bounds__(kAttnThreads, 5) kv_append_attn_kernel(const A
         L += v.y * w;
         o += __ldcg(&p.ws_o[(hd * p.max_pages + i) * H + tid]) * w;
       }
-      p.out[(size_t)b * p.out_ld + ((size_t)kvh * p.qpk + q_lo + qh) * H + tid] = __float2half_rn(o / L);
+      const __half y = __float2half_rn(o / L);
+      p.out[(size_t)b * p.out_ld + ((size_t)kvh * p.qpk + q_lo + qh) * H + tid] = y;
+      if (p.out8)
+        p.out8[(size_t)b * p.n_head * H + ((size_t)kvh * p.qpk + q_lo + qh) * H + tid] =
+            (uint8_t)__nv_cvt_float_to_fp8(__half2float(y) * p.inv_out_scale, __NV_SATFINITE, __NV_E4M3);
     }
   }
 }
@@ -439,6 +452,9 @@ extern "C" int pt_kv_append_attn(const pt_attn_args *a, void *stream) {
   p.step = a->step_dev;
   p.qkv = (const __half *)a->qkv; p.sin_t = (const __half *)a->rope_sin; p.cos_t = (const __half *)a->rope_cos;
   p.pool = (__half *)a->pool; p.page_table = a->page_table; p.out = (__half *)a->out;
+  p.out8 = (uint8_t *)a->out_fp8;
+  PT_REQUIRE(!a->out_fp8 || a->out_fp8_scale > 0.f, "pt_kv_append_attn: out_fp8 needs out_fp8_scale > 0");
+  p.inv_out_scale = a->out_fp8 ? 1.0f / a->out_fp8_scale : 0.f;
   const size_t heads = (size_t)a->batch * a->n_head;
   char *ws = (char *)a->workspace;
   p.counters = (int *)ws; ws += align256(heads * sizeof(int));

@@ -322,7 +322,8 @@ def attn_workspace(batch, n_head, head_dim, max_pages, device="cuda"):
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
-def attn_args(qkv, step, cache, out, n_head, rope_mode, softmax_mode, score_scale, rope_sin, rope_cos, workspace, error_flag, pdl=0):
+def attn_args(qkv, step, cache, out, n_head, rope_mode, softmax_mode, score_scale, rope_sin, rope_cos, workspace, error_flag, pdl=0,
+              out_fp8=None, out_fp8_scale=0.0):
     a = AttnArgs()
     a.batch, a.n_head, a.n_kv, a.head_dim = qkv.shape[0], n_head, cache.n_kv, cache.head_dim
     a.page_size, a.max_pages, a.rope_mode, a.softmax_mode = cache.page_size, cache.max_pages, rope_mode, softmax_mode
@@ -333,6 +334,7 @@ def attn_args(qkv, step, cache, out, n_head, rope_mode, softmax_mode, score_scal
     a.error_flag = _ptr(error_flag)
     a.pdl = pdl
     a.max_len = cache.max_len
+    a.out_fp8, a.out_fp8_scale = _ptr(out_fp8), float(out_fp8_scale)
     return a
 
 

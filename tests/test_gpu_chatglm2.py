@@ -86,3 +86,25 @@ def test_chatglm2_greedy_stream(cuda):
             top2 = np.sort(logits[t - 1][b].astype(np.float32))[-2:]
             assert top2[1] - top2[0] <= 2e-2, f"row {b}: streams diverge at {t} without a numerical tie"
     assert (got == exp).mean() > 0.9
+
+
+def test_attention_writes_the_fp8_copy_of_its_output(cuda):
+    """pt_kv_append_attn with out_fp8: the E4M3 bytes are exactly the cast (pt_cast_fp8) of the fp16 output it writes beside them."""
+    import ctypes
+    import torch
+    from poptransformer_b200 import ops
+    B, n_head, n_kv, H, max_len = 3, 8, 2, 128, 200
+    g = torch.Generator(device="cpu").manual_seed(4)
+    cache = ops.PagedKVCache(B, n_kv, H, max_len, 64, cuda)
+    cache.pool.copy_((torch.randn(cache.pool.shape, generator=g) * 0.5).half().to(cuda))
+    qkv = (torch.randn((B, (n_head + 2 * n_kv) * H), generator=g) * 0.7).half().to(cuda)
+    step = torch.full((1,), 150, dtype=torch.int32, device=cuda)
+    out = torch.empty((B, n_head * H), dtype=torch.float16, device=cuda)
+    out8 = torch.zeros((B, n_head * H), dtype=torch.uint8, device=cuda)
+    ws = ops.attn_workspace(B, n_head, H, cache.max_pages, cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    scale = 2.0 / 448.0
+    a = ops.attn_args(qkv, step, cache, out, n_head, ops.ROPE_NONE, ops.SOFTMAX_F32, 0.088, None, None, ws, err, out_fp8=out8, out_fp8_scale=scale)
+    ops.check(ops._lib.lib().pt_kv_append_attn(ctypes.byref(a), ops._stream()), "pt_kv_append_attn")
+    assert int(err.item()) == 0
+    assert torch.equal(out8, ops.half_to_uint8(out, scale))
